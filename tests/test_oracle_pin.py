@@ -1,0 +1,142 @@
+"""Pins the CPU oracle: known-answer vectors of the reference's own tests plus fixtures produced by
+the reference's torch implementations (tests/golden/make_golden.py).  No GPU needed."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle.mxfp import ROUND_DOWN, ROUND_UP
+
+MXFP_CASES = ["mxfp_bf16_last", "mxfp_bf16_axis1", "mxfp_fp16_axis0_down", "mxfp_fp32_last", "mxfp_bf16_outliers"]
+
+
+@pytest.mark.parametrize("name", MXFP_CASES)
+def test_quantiser_matches_reference_fixture(golden, name):
+    g = golden(name)
+    q, s = oracle.downcast_to_mxfp_oracle(g["x"], g["axis"], g["mode"])
+    assert torch.equal(q, g["q"])
+    assert torch.equal(s, g["scale"])
+    for tname, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16), ("fp32", torch.float32)):
+        d = oracle.upcast_from_mxfp_oracle(g["q"], g["scale"], dt, g["axis"])
+        ref = g["deq_" + tname]
+        assert torch.equal(d.view(torch.int16 if dt != torch.float32 else torch.int32),
+                           ref.view(torch.int16 if dt != torch.float32 else torch.int32))
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_rtne_known_answers(dt):
+    # reference tests/test_mxfp.py:92-121 -- tie cases of round-to-nearest-even at scale 1
+    just_above = {torch.bfloat16: 0.251953125, torch.float16: 0.250244140625, torch.float32: 0.2500000298023223877}[dt]
+    x = torch.tensor([6, 0, 0.24, 0.25, 0.75, 0.99, 1.2, 1.3, -1.25, just_above] + [0] * 22, dtype=dt).view(1, -1, 1)
+    q, s = oracle.downcast_to_mxfp_oracle(x, 1)
+    d = oracle.upcast_from_mxfp_oracle(q, s, dt, 1)
+    assert d.flatten().tolist() == [6, 0, 0, 0.0, 1.0, 1.0, 1.0, 1.5, -1.0, 0.5] + [0] * 22
+    assert s.item() == 127
+
+
+def test_round_down_known_answer():
+    # reference tests/test_mxfp.py:123-151 -- scale byte 127 + 3 for a block whose max is 33
+    x = torch.tensor([33.0, 24.0, 16.0, 8.0, 4.0, 0.0, -32.0, 0.0] + [0] * 24).bfloat16().view(1, -1, 1)
+    q, s = oracle.downcast_to_mxfp_oracle(x, 1, ROUND_DOWN)
+    assert s.item() == 127 + 3
+    d = oracle.upcast_from_mxfp_oracle(q, s, torch.bfloat16, 1)
+    assert torch.equal(d[0, 1:], x[0, 1:])
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_no_inf_at_extreme_values(dt):
+    # reference tests/test_mxfp.py:154-168
+    big = 65470 if dt == torch.float16 else 3.3895e38
+    x = torch.tensor([big, big] + [0] * 30, dtype=dt)
+    q, s = oracle.downcast_to_mxfp_oracle(x, -1)
+    d = oracle.upcast_from_mxfp_oracle(q, s, dt, -1)
+    assert not d.isinf().any()
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_exact_round_trip_of_representable_values(dt):
+    # reference tests/test_mxfp.py:171-205 -- every e2m1 value times 2^p survives the round trip
+    vals = torch.tensor(oracle.E2M1_VALUES, dtype=dt)
+    kdim = torch.cat([vals, -vals]).reshape(-1, 1)
+    scales = (2.0 ** torch.arange(-8, 8, dtype=dt)).reshape(1, -1)
+    w = (kdim * scales).repeat(9, 32).unsqueeze(0)
+    w = torch.nn.functional.pad(w, (0, 0, 0, 16))
+    q, s = oracle.downcast_to_mxfp_oracle(w, 1)
+    assert torch.equal(oracle.upcast_from_mxfp_oracle(q, s, dt, 1), w)
+
+
+@pytest.mark.parametrize("name", ["topk_T7_E13_k4", "topk_T256_E128_k4", "topk_T300_E200_k8", "topk_T33_E32_k2"])
+def test_routing_matches_reference_fixture(golden, name):
+    g = golden(name)
+    vals, indx, bm = oracle.topk_oracle(g["logits"], g["k"], bool(g["softmax"]))
+    assert torch.equal(indx, g["indx"].int())
+    assert torch.equal(bm, g["bitmatrix"])
+    assert torch.equal(vals, g["vals"])
+    cs, col, row = oracle.bitmatrix_metadata_oracle(indx, g["logits"].shape[1])
+    assert torch.equal(cs, g["col_sum"].int())
+    assert torch.equal(col, g["col_sorted"])
+    assert torch.equal(row, g["row_sorted"])
+
+
+def test_bitmatrix_docstring_example():
+    # reference tensor_details/bitmatrix.py:10-19
+    rows = [[2, 4, 5], [1, 5], [0, 1, 2, 6], [2, 4]]
+    # the example is not rectangular; pad every row with -1 at the tail of a flat list instead
+    flat = [c for r in rows for c in r]
+    indx = torch.tensor(flat).view(-1, 1)
+    cs, col, row = oracle.bitmatrix_metadata_oracle(indx, 7)
+    assert cs.tolist() == [1, 2, 3, 0, 2, 2, 1]
+    assert col.tolist() == [5, 3, 6, 0, 7, 9, 1, 10, 2, 4, 8]
+    assert row.tolist() == [3, 6, 8, 1, 9, 0, 2, 4, 10, 5, 7]
+
+
+def test_ragged_docstring_example():
+    # reference tensor_details/ragged_tensor.py:14-30 (its slice_offs line misprints 159 as 332)
+    sizes = torch.tensor([15, 17, 0, 127], dtype=torch.int32)
+    so, bo, bs = oracle.ragged_metadata_oracle(sizes, 159)
+    assert so.tolist() == [0, 15, 32, 32, 159]
+    assert bo.tolist() == [[0, 1, 3, 3, 11], [0, 1, 2, 2, 6], [0, 1, 2, 2, 4], [0, 1, 2, 2, 3]]
+    # the docstring's schedule rows are abbreviated (they list 4 blocks of 128 where block_offs gives 3);
+    # the schedule itself is pinned by the fixtures below.  Here: consistency with block_offs.
+    unpack = lambda v: (v >> 16, v & 0xFFFF)
+    assert [unpack(v) for v in bs[3, :3].tolist()] == [(0, 0), (0, 1), (0, 3)]
+    assert [unpack(v) for v in bs[0, :5].tolist()] == [(0, 0), (0, 1), (1, 1), (0, 3), (1, 3)]
+    assert bs[3, 3:].eq(-1).all()
+
+
+@pytest.mark.parametrize("name", ["ragged_E1", "ragged_E7", "ragged_E33", "ragged_E130"])
+def test_ragged_metadata_matches_reference_fixture(golden, name):
+    g = golden(name)
+    so, bo, bs = oracle.ragged_metadata_oracle(g["slice_sizes"], g["n_rows"])
+    assert torch.equal(so, g["slice_offs"])
+    assert torch.equal(bo, g["block_offs"])
+    assert torch.equal(bs, g["block_schedule"])
+    r = oracle.remap_ragged_metadata_oracle(g["slice_sizes"], so, bo, bs, g["slice_map"])
+    assert torch.equal(r[0], g["r_slice_sizes"])
+    assert torch.equal(r[1], g["r_slice_offs"])
+    assert torch.equal(r[2], g["r_block_offs"])
+    assert torch.equal(r[3], g["r_block_schedule"])
+
+
+def test_gemm_swiglu_reduce_match_reference_fixture(golden):
+    g = golden("gemm_small")
+    w = oracle.dequant_weight_oracle(g["wq"], g["ws"])
+    y = oracle.matmul_oracle(g["x"], w, g["bias"], g["slice_sizes"], g["gather"], g["scatter"], gammas=g["gammas"])
+    assert torch.equal(y, g["y"])
+    n = int(g["slice_sizes"].sum())
+    yp = oracle.matmul_oracle(g["x"][:n], w, g["bias"], g["slice_sizes"])
+    assert torch.equal(yp, g["y_plain"])
+    act = oracle.swiglu_oracle(yp, g["alpha"], g["limit"])
+    assert torch.equal(act, g["act"])
+    red = oracle.reduce_oracle(g["yk"], 1, mask=g["mask"])
+    assert torch.equal(red, g["red"])
+
+
+def test_layouts_match_reference_fixture(golden):
+    g = golden("layout_bw")
+    sw = oracle.swizzle_mx_scale_bw_oracle(g["scale"])
+    assert torch.equal(sw, g["scale_swizzled"])
+    assert torch.equal(oracle.unswizzle_mx_scale_bw_oracle(sw, g["scale"].shape), g["scale"])
+    vw = oracle.swizzle_mx_value_bw_oracle(g["value"])
+    assert torch.equal(vw, g["value_swizzled"])
+    assert torch.equal(oracle.unswizzle_mx_value_bw_oracle(vw, (2, 96, 40)), g["value"])
