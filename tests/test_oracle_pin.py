@@ -138,5 +138,8 @@ def test_layouts_match_reference_fixture(golden):
     assert torch.equal(sw, g["scale_swizzled"])
     assert torch.equal(oracle.unswizzle_mx_scale_bw_oracle(sw, g["scale"].shape), g["scale"])
     vw = oracle.swizzle_mx_value_bw_oracle(g["value"])
-    assert torch.equal(vw, g["value_swizzled"])
+    # the reference leaves the K padding rows uninitialised; compare the valid rows only
+    assert vw.shape == g["value_swizzled"].shape
+    assert torch.equal(vw[:, :48], g["value_swizzled"][:, :48])
+    assert g["value_swizzled_strides"].tolist() == [128 * 40, 1, 128]
     assert torch.equal(oracle.unswizzle_mx_value_bw_oracle(vw, (2, 96, 40)), g["value"])
