@@ -1,0 +1,173 @@
+/*
+ * moe_b200.h -- C ABI of libmoe_b200.so: the MoE hot path of triton_kernels as hand-written
+ * CUDA for sm_100a (B200).
+ *
+ * Conventions
+ *   - Every entry point returns 0 on success and a non-zero MOE_ERR_* code otherwise; it never
+ *     throws and never traps.  moe_last_error() returns a per-thread message for the last failure.
+ *   - All pointers are DEVICE pointers unless the name ends in _host.  Nothing here allocates
+ *     device memory: outputs and scratch are owned by the caller (the Python shim allocates them
+ *     through torch).  Work is enqueued on `stream` (a cudaStream_t passed as void*), without
+ *     host synchronisation, so calls can be captured in a CUDA graph.
+ *   - "Reference" citations are paths inside triton-lang/triton, python/triton_kernels/triton_kernels/.
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MOE_F32 = 0, MOE_F16 = 1, MOE_BF16 = 2 };
+enum { MOE_OK = 0, MOE_ERR_ARG = 1, MOE_ERR_CUDA = 2, MOE_ERR_UNSUPPORTED = 3, MOE_ERR_DEVICE_STATUS = 4 };
+enum { MOE_ROUND_UP = 0, MOE_ROUND_DOWN = 1 };
+enum { MOE_ACT_NONE = 0, MOE_ACT_SWIGLU = 1 };
+/* weight kinds understood by moe_grouped_gemm */
+enum { MOE_W_DENSE = 0,          /* w[e,k,n] in the activation dtype, arbitrary element strides */
+       MOE_W_MX4_CANONICAL = 1,  /* e2m1x2 bytes packed along K (K contiguous) + e8m0 scales, byte strides */
+       MOE_W_MX4_B200 = 2        /* tile-contiguous values + scales made by moe_weight_layout_to_b200 */ };
+enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2 };
+
+const char* moe_last_error(void);
+int moe_abi_version(void);
+
+/* Device facts used by the host-side heuristics (replaces target_info.py:73-74 num_sms()). */
+typedef struct {
+  int sm_count;
+  int cc_major, cc_minor;
+  size_t smem_per_block_optin;
+  size_t l2_bytes;
+  size_t total_mem;
+} MoeDeviceInfo;
+int moe_device_info(int device, MoeDeviceInfo* out_host);
+
+/* ---- MXFP4 quantiser / dequantiser -------------------------------------------------------------
+ * Replaces numerics_details/mxfp.py:25-88 (downcast_to_mxfp -> _downcast_to_mxfp kernel,
+ * mxfp_details/_downcast_to_mxfp.py:149-215) and mxfp.py:90-176 (upcast_from_mxfp ->
+ * mxfp_details/_upcast_from_mxfp.py:109-220) for e2m1 values with e8m0 scales per 32 elements.
+ * The source is viewed as [batch, outer, quant] with element strides; quant % 32 == 0.
+ * q is [batch, outer, quant/2] bytes and scale [batch, outer, quant/32] bytes, both dense.       */
+int moe_downcast_mxfp4(const void* x, int src_dtype, int64_t batch, int64_t outer, int64_t quant,
+                       int64_t sx_batch, int64_t sx_outer, int64_t sx_quant,
+                       uint8_t* q, uint8_t* scale, int rounding_mode, void* stream);
+/* out is viewed as [batch, outer, quant] with element strides; q/scale dense as above. */
+int moe_upcast_mxfp4(const uint8_t* q, const uint8_t* scale, void* out, int dst_dtype,
+                     int64_t batch, int64_t outer, int64_t quant,
+                     int64_t so_batch, int64_t so_outer, int64_t so_quant, void* stream);
+
+/* ---- routing -----------------------------------------------------------------------------------
+ * moe_topk_fwd replaces topk.py:25-73 (topk_forward -> topk_details/_topk_forward.py:91-150):
+ * per row the k largest logits (ties -> smaller index), sorted descending, optional fp32 softmax
+ * over the selected k, and the row of the expert bitmatrix.  indx is int16 [T,k]; bitmatrix word
+ * (t, w) lives at bitmatrix[t*bm_stride_row + w*bm_stride_word].  Rows >= *n_rows_dev (or >= T if
+ * NULL) are left untouched.  With use_provided_indx, indx is an input.                             */
+int moe_topk_fwd(const void* logits, int dtype, int64_t T, int E, int k, int apply_softmax,
+                 int64_t ld_logits, void* vals, int64_t ld_vals, int16_t* indx, int64_t ld_indx,
+                 uint32_t* bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,
+                 const int32_t* n_rows_dev, int use_provided_indx, void* stream);
+
+/* Replaces tensor_details/bitmatrix.py:110-150 (make_bitmatrix_metadata: sum_bitmatrix_rows +
+ * stage1 + stage2): histogram col_sum[E], col_sorted_indx[T*k], row_sorted_indx[T*k] (stable
+ * counting sort of the flat (token,slot) entries by expert; -1 padded).
+ * workspace: moe_bitmatrix_metadata_workspace(T, E, k) bytes of device scratch.                    */
+size_t moe_bitmatrix_metadata_workspace(int64_t T, int E, int k);
+int moe_bitmatrix_metadata(const int16_t* indx, int64_t ld_indx, int64_t T, int E, int k,
+                           const int32_t* n_rows_dev, int32_t* col_sum, int32_t* col_sorted,
+                           int32_t* row_sorted, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces tensor_details/ragged_tensor.py:183-210 (make_ragged_tensor_metadata: memset + compute
+ * kernels).  block_offs is [4][ld_block_offs] (block sizes 16,32,64,128), block_sched is
+ * [4][ld_sched] with n_sched valid columns each (= max_n_blocks), padded with -1.                  */
+int moe_ragged_metadata(const int32_t* slice_sizes, int E, int32_t* slice_offs, int32_t* block_offs,
+                        int64_t ld_block_offs, int32_t* block_sched, int64_t ld_sched, int64_t n_sched,
+                        void* stream);
+/* Replaces ragged_tensor.py:348-381 (remap_ragged_tensor_metadata). */
+int moe_ragged_metadata_remap(const int32_t* slice_sizes, const int32_t* slice_offs, const int32_t* block_offs,
+                              int64_t ld_block_offs, const int32_t* block_sched, int64_t ld_sched, int64_t n_sched,
+                              const int32_t* slice_map, int E, int32_t* out_slice_sizes, int32_t* out_slice_offs,
+                              int32_t* out_block_offs, int32_t* out_block_sched, void* stream);
+
+/* ---- SwiGLU and combine ------------------------------------------------------------------------
+ * Replaces swiglu.py:85-86 (swiglu -> swiglu_details/_swiglu.py:73-120): a is [M, 2*N] with gate
+ * and linear columns interleaved, out is [M, N].  n_rows_dev (nullable) bounds M on the device.    */
+int moe_swiglu(const void* a, int64_t ld_a, void* out, int64_t ld_out, int dtype, int64_t M, int64_t N,
+               float alpha, float limit, int has_limit, const int32_t* n_rows_dev, void* stream);
+/* Replaces reduce.py:1143-1165 (reduce -> _reduce_forward, reduce.py:505-650) without mx/flex
+ * features: y[s0,s1] = sum_r mask * scale * x[r,s0,s1], fp32 accumulation.  Strides are in
+ * elements, in the order (reduced, s0, s1); mask (any of 1/2/4/8-byte integers, 0 = skip) and
+ * scale (fp32) may be NULL and may broadcast through zero strides.                                 */
+int moe_reduce(const void* x, int dtype, int64_t R, int64_t S0, int64_t S1,
+               int64_t sx_r, int64_t sx_0, int64_t sx_1,
+               const void* mask, int mask_elem_bytes, int64_t sm_r, int64_t sm_0, int64_t sm_1,
+               const float* scale, int64_t ss_r, int64_t ss_0, int64_t ss_1,
+               void* y, int y_dtype, int64_t sy_0, int64_t sy_1, void* stream);
+
+/* ---- weight layout -----------------------------------------------------------------------------
+ * One-time re-layout of canonical MXFP4 weights (the output of moe_downcast_mxfp4 on w[E,K,N] along
+ * K: values [E][N][K/2], scales [E][N][K/32]) into the tile-contiguous layout the tensor-core kernel
+ * streams with bulk copies: tiles of 128 n x 128 k, ordered [E][n_tile][k_tile]; a value tile is
+ * 128 rows x 64 bytes with the nibbles of every 32-bit word reordered (k0,k2,k4,k6,k1,k3,k5,k7), a
+ * scale tile is 128 rows x 4 bytes; K and N are zero-padded to multiples of 128.  Plays the role of
+ * convert_layout(..., BlackwellMX4ValueShuffledLayout / BlackwellMXScaleLayout)
+ * (tensor_details/layout_details/blackwell_value_shuffled.py:203-261, blackwell_scale.py:505-533).
+ * Either half (values or scales) may be skipped by passing NULL for both its input and output.    */
+size_t moe_weight_b200_value_bytes(int E, int K, int N);
+size_t moe_weight_b200_scale_bytes(int E, int K, int N);
+int moe_weight_layout_to_b200(const uint8_t* q, int64_t q_stride_e, int64_t q_stride_n,
+                              const uint8_t* scale, int64_t s_stride_e, int64_t s_stride_k, int64_t s_stride_n,
+                              int E, int K, int N, uint8_t* out_values, uint8_t* out_scales, void* stream);
+int moe_weight_layout_from_b200(const uint8_t* values, const uint8_t* scales, int E, int K, int N,
+                                uint8_t* q /* [E][N][K/2] */, uint8_t* scale /* [E][N][K/32] */, void* stream);
+
+/* ---- ragged grouped GEMM -------------------------------------------------------------------------
+ * Replaces matmul.py:245-766 (matmul -> matmul_details/_p_matmul.py:62 / _matmul.py:43):
+ *   y[rows(e)] = act((x[gather(rows(e))] @ dequant(w[e]) + bias[e] * betas) * out_alpha) * gammas
+ * fp32 accumulation; rows(e) = [slice_offs[e], slice_offs[e] + slice_sizes[e]).  The epilogue order
+ * is that of _p_matmul.py:610-628.  Two kernels: a tcgen05 kernel (bf16 activations x
+ * MOE_W_MX4_B200 weights, TMEM accumulators) and a general SIMT kernel (any supported dtype/kind). */
+typedef struct {
+  /* activations: [rows_x, K], K contiguous, row stride in elements */
+  const void* x; int x_dtype; int64_t ld_x; int64_t rows_x;
+  /* weights */
+  int w_kind;
+  const void* w;
+  int64_t w_stride_e, w_stride_k, w_stride_n;     /* dense: elements. canonical MX4: bytes (k ignored) */
+  const uint8_t* w_scale;                          /* canonical / B200 scales */
+  int64_t ws_stride_e, ws_stride_k, ws_stride_n;   /* canonical scales: bytes */
+  int E, K, N;
+  /* ragged structure; slice_sizes == NULL means one slice holding all M rows (E must be 1) */
+  const int32_t* slice_sizes; const int32_t* slice_offs;
+  const int32_t* block_offs_16;                    /* block_offs_data, row for block size 16 */
+  const int32_t* block_sched_16;                   /* block_schedule_data, row for block size 16 */
+  int64_t ld_block_offs, ld_block_sched;           /* row pitch: row b serves block size 16 << b */
+  int64_t M;                                       /* rows of the (gathered) problem = upper bound on sum(slice_sizes) */
+  /* epilogue */
+  const void* bias; int bias_dtype; int64_t ld_bias; /* [E, N] */
+  const int32_t* gather_indx;                      /* [M] source rows of x, -1 = zero row */
+  const int32_t* scatter_indx;                     /* [M] destination rows of y, -1 = drop */
+  const float* betas; const float* gammas;         /* [M], expert-sorted order */
+  float out_alpha; int has_out_alpha;
+  int activation; float act_alpha; float act_limit; int act_has_limit;
+  void* y; int y_dtype; int64_t ld_y;              /* [M or len(scatter), N / (2 if swiglu)] */
+  /* tuning */
+  int kernel;                                      /* MOE_GEMM_* */
+  int32_t* status;                                 /* device word, set non-zero when a bounded wait expires */
+} MoeGemmArgs;
+int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
+
+/* ---- expert-parallel row movement ------------------------------------------------------------------
+ * Local halves of convert_dp_to_ep / convert_ep_to_dp (distributed.py:176-211, 256-283): the
+ * exchange itself is an NCCL all-to-all issued by the host shim; these kernels pack rows into
+ * per-destination contiguous, expert-sorted order and unpack them.                                 */
+int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
+                    void* dst, int64_t ld_dst, void* stream);
+int moe_scatter_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_in, int64_t row_bytes,
+                     void* dst, int64_t ld_dst, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H */

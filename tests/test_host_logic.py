@@ -1,0 +1,150 @@
+"""Host-side logic that needs no GPU: layouts (torch ops), block-count bounds, expert assignment, the
+expert-parallel exchange plan (also across two gloo ranks), tuning constraints."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+import triton_b200
+from triton_b200.distributed import make_exchange_plan, expert_owner
+from triton_b200.tensor import FP4, RaggedTensorMetadata, convert_layout, wrap_torch_tensor
+from triton_b200.tensor_details.layout import BlackwellMXScaleLayout, BlackwellMXValueLayout, StridedLayout
+
+
+def test_n_blocks_bound_matches_oracle():
+    for E in (1, 7, 128):
+        for rows in (0, 1, 5, 127, 128, 129, 4096, 65536):
+            for bs in (16, 32, 64, 128):
+                assert RaggedTensorMetadata.n_blocks(E, rows, bs) == oracle.n_blocks(E, rows, bs)
+
+
+def test_reference_layouts_round_trip_on_cpu(golden):
+    g = golden("layout_bw")
+    s = wrap_torch_tensor(g["scale"])
+    sw = convert_layout(s, BlackwellMXScaleLayout())
+    assert torch.equal(sw.storage.data, g["scale_swizzled"])
+    assert torch.equal(convert_layout(sw, StridedLayout()).storage.data, g["scale"])
+    v = wrap_torch_tensor(g["value"], dtype=FP4)                      # canonical: packed along N
+    assert v.shape == [2, 96, 40]
+    vw = convert_layout(v, BlackwellMXValueLayout())
+    assert list(vw.storage.data.shape) == [2, 128, 40] and vw.storage.data.stride(-2) == 1
+    assert torch.equal(vw.storage.data[:, :48], g["value_swizzled"][:, :48])
+    back = convert_layout(vw, StridedLayout())
+    assert torch.equal(back.storage.data, g["value"])
+    # K-major strided layout (what downcast_to_mxfp produces for weights)
+    km = convert_layout(v, StridedLayout(major_dim=-2))
+    assert list(km.storage.data.shape) == [2, 48, 40] and km.storage.data.stride(-2) == 1
+    assert torch.equal(km.storage.data, oracle.repack_fp4_oracle(g["value"], -1, -2))
+
+
+def test_storage_shapes_of_reference_layouts():
+    # values from the reference's tests/test_tensor.py:88-109 for the Blackwell layouts
+    assert BlackwellMXValueLayout().storage_shape([3, 258, 514], True) == [3, 256, 514]
+    assert BlackwellMXScaleLayout().storage_shape([3, 10, 200], False) == [1, 6, 4, 2, 256]
+
+
+def test_expert_assignment():
+    d = triton_b200.make_expt_dict_uniform(4, 128)
+    a = triton_b200.make_expt_assignment(4, 128, d, "cpu")
+    assert a.expt_boolmask.sum(0).eq(1).all() and a.n_expts_per_shard == [32] * 4
+    assert a.expt_map[1, 32:64].tolist() == list(range(32)) and a.expt_map[1, 0] == -1
+    assert (a.expt_bitmask[3, 3] & 0xFFFFFFFF) == 0xFFFFFFFF
+    r = triton_b200.make_expt_dict_random(4, 37)
+    assert sorted(sum(r.values(), [])) == list(range(37)) and all(len(v) for v in r.values())
+    with pytest.raises(ValueError):
+        triton_b200.make_expt_assignment(2, 4, {0: [0, 1], 1: [1, 2, 3]}, "cpu")
+    assert expert_owner(a).tolist() == [e // 32 for e in range(128)]
+
+
+def _plan_case(T_global=64, E=16, k=4, W=4, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T_global, E, generator=g)
+    _, indx, _ = oracle.topk_oracle(logits, k)
+    _, col, row = oracle.bitmatrix_metadata_oracle(indx, E)
+    assign = triton_b200.make_expt_assignment(W, E, triton_b200.make_expt_dict_random(W, E), "cpu")
+    return indx, col, row, assign
+
+
+def test_exchange_plan_is_a_consistent_permutation():
+    W, k = 4, 4
+    indx, col, row, assign = _plan_case(W=W, k=k)
+    T_local = indx.shape[0] // W
+    owner = expert_owner(assign)
+    order, counts, flat = make_exchange_plan(indx, col, owner, W, T_local)
+    assert sorted(order.tolist()) == list(range(indx.numel()))
+    assert counts.sum() == indx.numel()
+    starts = (torch.cumsum(counts.reshape(-1), 0) - counts.reshape(-1)).view(W, W)
+    for s in range(W):
+        for d in range(W):
+            seg = order[starts[s, d]:starts[s, d] + counts[s, d]]
+            assert (seg[1:] > seg[:-1]).all()
+            f = col[seg].long()
+            assert (f // (k * T_local) == s).all()
+            assert (owner[indx.reshape(-1)[f].long()] == d).all()
+
+
+def _gloo_worker(rank, W, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=W)
+    try:
+        k, d_model = 2, 8
+        indx, col, row, assign = _plan_case(T_global=32, E=8, k=k, W=W, seed=1)
+        T_global = indx.shape[0]
+        T_local = T_global // W
+        x = torch.arange(T_global * d_model, dtype=torch.float32).view(T_global, d_model)
+        owner = expert_owner(assign)
+        order, counts, flat = make_exchange_plan(indx, col, owner, W, T_local)
+        starts = (torch.cumsum(counts.reshape(-1), 0) - counts.reshape(-1)).view(W, W)
+        # dispatch, the way convert_dp_to_ep does it, with torch indexing standing in for the CUDA row kernels
+        lo, n_send = int(starts[rank, 0]), int(counts[rank].sum())
+        tok = flat[lo:lo + n_send] // k
+        send = x[tok]
+        recv_counts = counts[:, rank].tolist()
+        recv = torch.empty(sum(recv_counts), d_model)
+        dist.all_to_all_single(recv, send, recv_counts, counts[rank].tolist())
+        pos = torch.cat([order[int(starts[s, rank]):int(starts[s, rank]) + recv_counts[s]] for s in range(W)])
+        y_ep = torch.full((T_global * k, d_model), float("nan"))
+        y_ep[pos] = recv
+        # what a single process would have: row p of the expert-sorted buffer is token col[p] // k
+        full = x[col.long() // k]
+        mine = owner[indx.reshape(-1)[col.long()].long()] == rank
+        assert torch.equal(y_ep[mine], full[mine]) and torch.isnan(y_ep[~mine]).all()
+        # combine back: every rank returns y_ep * 2 for the rows it owns
+        send2 = (y_ep * 2)[pos]
+        recv2 = torch.empty(n_send, d_model)
+        dist.all_to_all_single(recv2, send2, counts[rank].tolist(), recv_counts)
+        out = torch.zeros(T_local * k, d_model)
+        out[flat[lo:lo + n_send] - rank * T_local * k] = recv2
+        expect = (x[rank * T_local:(rank + 1) * T_local] * 2).repeat_interleave(k, 0)
+        assert torch.equal(out, expect)
+        ret[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_plan_across_two_gloo_ranks():
+    W = 2
+    port = 29500 + os.getpid() % 2000
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, W, port, ret)) for r in range(W)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert sorted(ret.keys()) == list(range(W))
+
+
+def test_opt_flags_constraints_are_scoped():
+    from triton_b200.matmul_details import opt_flags
+    assert opt_flags.resolve_kernel_choice() == "auto"
+    with triton_b200.scoped_opt_flags_constraints({"kernel": "simt", "block_m": 64}):
+        assert opt_flags.resolve_kernel_choice() == "simt"
+    assert opt_flags.resolve_kernel_choice() == "auto"
+    with triton_b200.scoped_opt_flags_constraints({"split_k": 4}):
+        with pytest.raises(triton_b200.InapplicableConstraint):
+            opt_flags.resolve_kernel_choice()

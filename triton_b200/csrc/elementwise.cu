@@ -1,0 +1,244 @@
+// HBM-bound elementwise kernels: standalone SwiGLU, the masked / scaled k-way combine (reduce) and the
+// row gather / scatter used around the expert-parallel exchange.
+//
+// SwiGLU semantics: triton_kernels swiglu_details/_swiglu.py:55-64 (gate = even columns, linear = odd
+// columns; gate clamped above, linear clamped both ways; s = g / (1 + exp(-alpha g)); out = s*l + s).
+// Combine semantics: triton_kernels reduce.py:1181-1214 (fp32 sum over the reduced axis of
+// mask * scale * x, cast to the output type).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float swiglu_one(float g, float l, float alpha, float limit, bool has_limit) {
+  if (has_limit) {
+    g = fminf(g, limit);
+    l = fminf(fmaxf(l, -limit), limit);
+  }
+  const float s = g / (1.0f + ex2_approx(-alpha * g * 1.4426950408889634f));
+  return fmaf(s, l, s);
+}
+
+// thread = 8 outputs (16 interleaved inputs) on the vector path
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ a, int64_t ld_a, T* __restrict__ out,
+                                                     int64_t ld_out, int64_t M, int64_t N, float alpha, float limit,
+                                                     int has_limit, const int32_t* __restrict__ n_rows_dev) {
+  if (n_rows_dev) M = min(M, (int64_t)*n_rows_dev);
+  constexpr int V = VEC ? 8 : 1;
+  const int64_t per_row = (N + V - 1) / V;
+  const int64_t total = M * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row, c = (i - r * per_row) * V;
+    const T* src = a + r * ld_a + 2 * c;
+    T* dst = out + r * ld_out + c;
+    if constexpr (VEC && sizeof(T) == 2) {
+      uint4 v0 = *reinterpret_cast<const uint4*>(src);
+      uint4 v1 = *reinterpret_cast<const uint4*>(src + 8);
+      const T* e0 = reinterpret_cast<const T*>(&v0);
+      const T* e1 = reinterpret_cast<const T*>(&v1);
+      T o[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[j] = from_f32<T>(swiglu_one(to_f32<T>(e0[2 * j]), to_f32<T>(e0[2 * j + 1]), alpha, limit, has_limit));
+        o[4 + j] = from_f32<T>(swiglu_one(to_f32<T>(e1[2 * j]), to_f32<T>(e1[2 * j + 1]), alpha, limit, has_limit));
+      }
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (c + j < N)
+          dst[j] = from_f32<T>(swiglu_one(to_f32<T>(src[2 * j]), to_f32<T>(src[2 * j + 1]), alpha, limit, has_limit));
+    }
+  }
+}
+
+__device__ __forceinline__ bool mask_nonzero(const void* m, int bytes, int64_t off) {
+  switch (bytes) {
+    case 1: return ((const uint8_t*)m)[off] != 0;
+    case 2: return ((const uint16_t*)m)[off] != 0;
+    case 4: return ((const uint32_t*)m)[off] != 0;
+    default: return ((const unsigned long long*)m)[off] != 0;
+  }
+}
+
+// y[s0, s1] = sum_r mask * scale * x[r, s0, s1]; thread = V consecutive s1 (V = 8 on the vector path)
+template <typename TX, typename TY, bool VEC>
+__global__ void __launch_bounds__(256) reduce_kernel(const TX* __restrict__ x, int64_t R, int64_t S0, int64_t S1,
+                                                     int64_t sx_r, int64_t sx_0, int64_t sx_1, const void* __restrict__ mask,
+                                                     int mask_bytes, int64_t sm_r, int64_t sm_0, int64_t sm_1,
+                                                     const float* __restrict__ scale, int64_t ss_r, int64_t ss_0,
+                                                     int64_t ss_1, TY* __restrict__ y, int64_t sy_0, int64_t sy_1) {
+  constexpr int V = VEC ? 8 : 1;
+  const int64_t per_row = (S1 + V - 1) / V;
+  const int64_t total = S0 * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s0 = i / per_row, c = (i - s0 * per_row) * V;
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+    for (int64_t r = 0; r < R; ++r) {
+      if constexpr (VEC) {
+        // vector path: mask and scale do not vary along s1 (stride 0), x is contiguous along s1
+        if (mask && !mask_nonzero(mask, mask_bytes, r * sm_r + s0 * sm_0)) continue;
+        const float sc = scale ? scale[r * ss_r + s0 * ss_0] : 1.0f;
+        uint4 raw = *reinterpret_cast<const uint4*>(x + r * sx_r + s0 * sx_0 + c);
+        const TX* e = reinterpret_cast<const TX*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f32<TX>(e[j]) * sc;
+      } else {
+        if (mask && !mask_nonzero(mask, mask_bytes, r * sm_r + s0 * sm_0 + c * sm_1)) continue;
+        const float sc = scale ? scale[r * ss_r + s0 * ss_0 + c * ss_1] : 1.0f;
+        acc[0] += to_f32<TX>(x[r * sx_r + s0 * sx_0 + c * sx_1]) * sc;
+      }
+    }
+    if constexpr (VEC) {
+      TY o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = from_f32<TY>(acc[j]);
+      *reinterpret_cast<uint4*>(y + s0 * sy_0 + c) = *reinterpret_cast<const uint4*>(o);
+    } else {
+      y[s0 * sy_0 + c * sy_1] = from_f32<TY>(acc[0]);
+    }
+  }
+}
+
+// dst[i, :] = src[indx[i], :]   (indx < 0: zero row) -- 16 bytes per thread
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src, int64_t ld_src,
+                                                          const int32_t* __restrict__ indx, int64_t n_out,
+                                                          int64_t row_bytes, uint8_t* __restrict__ dst, int64_t ld_dst) {
+  const int64_t vec_per_row = row_bytes >> 4;
+  const int64_t total = n_out * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+    const int32_t s = indx ? indx[r] : (int32_t)r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (s >= 0) v = *reinterpret_cast<const uint4*>(src + (int64_t)s * ld_src + c * 16);
+    *reinterpret_cast<uint4*>(dst + r * ld_dst + c * 16) = v;
+  }
+}
+
+// dst[indx[i], :] = src[i, :]   (indx < 0: dropped)
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint8_t* __restrict__ src, int64_t ld_src,
+                                                           const int32_t* __restrict__ indx, int64_t n_in,
+                                                           int64_t row_bytes, uint8_t* __restrict__ dst, int64_t ld_dst) {
+  const int64_t vec_per_row = row_bytes >> 4;
+  const int64_t total = n_in * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+    const int32_t d = indx[r];
+    if (d < 0) continue;
+    *reinterpret_cast<uint4*>(dst + (int64_t)d * ld_dst + c * 16) =
+        *reinterpret_cast<const uint4*>(src + r * ld_src + c * 16);
+  }
+}
+
+int grid_for(int64_t total, int threads) {
+  int64_t blocks = cdiv64(total, threads);
+  int64_t cap = (int64_t)moe_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  return (int)(blocks < 1 ? 1 : blocks);
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_swiglu(const void* a, int64_t ld_a, void* out, int64_t ld_out, int dtype, int64_t M, int64_t N,
+                          float alpha, float limit, int has_limit, const int32_t* n_rows_dev, void* stream) {
+  MOE_CHECK_ARG(M >= 0 && N >= 0, "moe_swiglu: negative extent");
+  if (M == 0 || N == 0) return MOE_OK;
+  MOE_CHECK_ARG(a && out, "moe_swiglu: NULL pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  MOE_DISPATCH_FLOAT(dtype, T, {
+    const bool vec = sizeof(T) == 2 && N % 8 == 0 && ld_a % 8 == 0 && ld_out % 8 == 0 && (uintptr_t)a % 16 == 0 &&
+                     (uintptr_t)out % 16 == 0;
+    if (vec)
+      swiglu_kernel<T, true><<<grid_for(M * (N / 8), 256), 256, 0, st>>>((const T*)a, ld_a, (T*)out, ld_out, M, N, alpha,
+                                                                         limit, has_limit, n_rows_dev);
+    else
+      swiglu_kernel<T, false><<<grid_for(M * N, 256), 256, 0, st>>>((const T*)a, ld_a, (T*)out, ld_out, M, N, alpha,
+                                                                    limit, has_limit, n_rows_dev);
+  });
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+template <typename TX, typename TY>
+static int launch_reduce(const void* x, int64_t R, int64_t S0, int64_t S1, int64_t sx_r, int64_t sx_0, int64_t sx_1,
+                         const void* mask, int mb, int64_t sm_r, int64_t sm_0, int64_t sm_1, const float* scale,
+                         int64_t ss_r, int64_t ss_0, int64_t ss_1, void* y, int64_t sy_0, int64_t sy_1,
+                         cudaStream_t st) {
+  if constexpr (sizeof(TX) == 2 && sizeof(TY) == 2) {
+    const bool vec = sx_1 == 1 && sy_1 == 1 && S1 % 8 == 0 && sx_r % 8 == 0 && sx_0 % 8 == 0 && sy_0 % 8 == 0 &&
+                     (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (!mask || sm_1 == 0) && (!scale || ss_1 == 0);
+    if (vec) {
+      reduce_kernel<TX, TY, true><<<grid_for(S0 * (S1 / 8), 256), 256, 0, st>>>(
+          (const TX*)x, R, S0, S1, sx_r, sx_0, sx_1, mask, mb, sm_r, sm_0, sm_1, scale, ss_r, ss_0, ss_1, (TY*)y, sy_0,
+          sy_1);
+      MOE_CHECK_LAUNCH();
+      return MOE_OK;
+    }
+  }
+  reduce_kernel<TX, TY, false><<<grid_for(S0 * S1, 256), 256, 0, st>>>(
+      (const TX*)x, R, S0, S1, sx_r, sx_0, sx_1, mask, mb, sm_r, sm_0, sm_1, scale, ss_r, ss_0, ss_1, (TY*)y, sy_0, sy_1);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_reduce(const void* x, int dtype, int64_t R, int64_t S0, int64_t S1, int64_t sx_r, int64_t sx_0,
+                          int64_t sx_1, const void* mask, int mask_elem_bytes, int64_t sm_r, int64_t sm_0, int64_t sm_1,
+                          const float* scale, int64_t ss_r, int64_t ss_0, int64_t ss_1, void* y, int y_dtype,
+                          int64_t sy_0, int64_t sy_1, void* stream) {
+  MOE_CHECK_ARG(R >= 0 && S0 >= 0 && S1 >= 0, "moe_reduce: negative extent");
+  if (S0 == 0 || S1 == 0) return MOE_OK;
+  MOE_CHECK_ARG(x && y, "moe_reduce: NULL pointer");
+  MOE_CHECK_ARG(!mask || mask_elem_bytes == 1 || mask_elem_bytes == 2 || mask_elem_bytes == 4 || mask_elem_bytes == 8,
+                "moe_reduce: mask element size %d unsupported", mask_elem_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+#define MOE_REDUCE_CASE(DX, TX, DY, TY)                                                                             \
+  if (dtype == DX && y_dtype == DY)                                                                                 \
+    return launch_reduce<TX, TY>(x, R, S0, S1, sx_r, sx_0, sx_1, mask, mask_elem_bytes, sm_r, sm_0, sm_1, scale, ss_r, \
+                                 ss_0, ss_1, y, sy_0, sy_1, st);
+  MOE_REDUCE_CASE(MOE_BF16, __nv_bfloat16, MOE_BF16, __nv_bfloat16)
+  MOE_REDUCE_CASE(MOE_F16, __half, MOE_F16, __half)
+  MOE_REDUCE_CASE(MOE_F32, float, MOE_F32, float)
+  MOE_REDUCE_CASE(MOE_BF16, __nv_bfloat16, MOE_F32, float)
+  MOE_REDUCE_CASE(MOE_F16, __half, MOE_F32, float)
+  MOE_REDUCE_CASE(MOE_F32, float, MOE_BF16, __nv_bfloat16)
+  MOE_REDUCE_CASE(MOE_F32, float, MOE_F16, __half)
+#undef MOE_REDUCE_CASE
+  moe_set_error("moe_reduce: dtype combination (%d -> %d) unsupported", dtype, y_dtype);
+  return MOE_ERR_UNSUPPORTED;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out,
+                               int64_t row_bytes, void* dst, int64_t ld_dst, void* stream) {
+  MOE_CHECK_ARG(n_rows_out >= 0 && row_bytes >= 0, "moe_gather_rows: negative extent");
+  if (n_rows_out == 0 || row_bytes == 0) return MOE_OK;
+  MOE_CHECK_ARG(src && dst, "moe_gather_rows: NULL pointer");
+  MOE_CHECK_ARG(row_bytes % 16 == 0 && ld_src % 16 == 0 && ld_dst % 16 == 0 && (uintptr_t)src % 16 == 0 &&
+                    (uintptr_t)dst % 16 == 0,
+                "moe_gather_rows: rows must be 16-byte aligned multiples of 16 bytes");
+  gather_rows_kernel<<<grid_for(n_rows_out * (row_bytes / 16), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)src, ld_src, row_indx, n_rows_out, row_bytes, (uint8_t*)dst, ld_dst);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_scatter_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_in,
+                                int64_t row_bytes, void* dst, int64_t ld_dst, void* stream) {
+  MOE_CHECK_ARG(n_rows_in >= 0 && row_bytes >= 0, "moe_scatter_rows: negative extent");
+  if (n_rows_in == 0 || row_bytes == 0) return MOE_OK;
+  MOE_CHECK_ARG(src && dst && row_indx, "moe_scatter_rows: NULL pointer");
+  MOE_CHECK_ARG(row_bytes % 16 == 0 && ld_src % 16 == 0 && ld_dst % 16 == 0 && (uintptr_t)src % 16 == 0 &&
+                    (uintptr_t)dst % 16 == 0,
+                "moe_scatter_rows: rows must be 16-byte aligned multiples of 16 bytes");
+  scatter_rows_kernel<<<grid_for(n_rows_in * (row_bytes / 16), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)src, ld_src, row_indx, n_rows_in, row_bytes, (uint8_t*)dst, ld_dst);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}

@@ -1,0 +1,546 @@
+// Ragged grouped GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a:
+//   bf16 activations (gathered rows) x MXFP4 weights in the tile-contiguous layout of layout.cu,
+//   fp32 accumulators in tensor memory, fused bias / SwiGLU / routing-weight / scatter epilogue.
+//
+// No tcgen05 MMA kind multiplies bf16 by e2m1, so the weights are dequantised inside the SM to bf16
+// (e2m1 x 2^e is exact in bf16) and the contraction runs as kind::f16 with bf16 operands -- the same
+// arithmetic as the reference, which upcasts the weight tile in registers before its bf16 MMA
+// (triton_kernels matmul_details/opt_flags_details/opt_flags_nvidia.py:154-161).
+//
+// One persistent CTA per SM, 12 warps, specialised:
+//   warp 0      tensor-memory allocation, MMA issue (one elected lane)
+//   warp 1      weight producer: one bulk copy per value tile (8 KB) and scale tile (512 B) and k step
+//   warps 2-3   activation loader: 16-byte cp.async of (gathered) token rows into the 128B-swizzled
+//               K-major operand tile, zero fill for missing rows and the K tail
+//   warps 4-7   dequantiser: packed e2m1 + e8m0 -> bf16, written into the swizzled K-major B tile
+//   warps 8-11  epilogue: tcgen05.ld of the accumulator, bias*beta, out_alpha, SwiGLU, gamma, cast, store
+// Rings: raw weights (producer -> dequantiser), A and B operand stages (-> MMA), two accumulator
+// buffers (MMA -> epilogue).  Every mbarrier wait is bounded: when a wait expires the CTA raises a
+// shared abort flag, writes the caller's status word, drains its copies, frees tensor memory and
+// returns, so a protocol error can not hang the device.
+#include "gemm_common.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128;          // token rows per tile  (MMA M)
+constexpr int BLOCK_N = 128;          // weight rows per tile (MMA N)
+constexpr int BLOCK_K = 128;          // k per pipeline stage: two 64-wide swizzle sub-tiles
+constexpr int STAGES = 3;
+constexpr int NUM_THREADS = 384;
+constexpr int SUBTILE_BYTES = 128 * 128;                 // 128 rows x 128 bytes (64 bf16)
+constexpr int A_STAGE_BYTES = 2 * SUBTILE_BYTES;         // 32 KB
+constexpr int B_STAGE_BYTES = 2 * SUBTILE_BYTES;         // 32 KB
+constexpr int RAWV_BYTES = BLOCK_N * BLOCK_K / 2;        // 8 KB
+constexpr int RAWS_BYTES = BLOCK_N * 4;                  // 512 B
+constexpr int TMEM_COLS = 2 * BLOCK_N;                   // two fp32 accumulators of 128 columns
+
+constexpr int OFF_A = 0;
+constexpr int OFF_B = OFF_A + STAGES * A_STAGE_BYTES;
+constexpr int OFF_RAWV = OFF_B + STAGES * B_STAGE_BYTES;
+constexpr int OFF_RAWS = OFF_RAWV + STAGES * RAWV_BYTES;
+constexpr int OFF_SRC = OFF_RAWS + STAGES * RAWS_BYTES;          // int64 source rows, [2 loader warps][64]
+constexpr int OFF_BIAS = OFF_SRC + BLOCK_M * 8;                  // float bias, [4 epilogue warps][128]
+constexpr int OFF_BAR = OFF_BIAS + 4 * BLOCK_N * 4;              // mbarriers
+constexpr int NUM_BARS = 5 * STAGES + 4 + 1;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                 // tmem base, abort flag
+constexpr int SMEM_BYTES = OFF_MISC + 16;
+constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;                    // slack for 1024-byte alignment
+
+constexpr uint32_t WAIT_TIGHT_POLLS = 128;
+constexpr uint32_t WAIT_MAX_POLLS = 1u << 24;                    // ~1 s with the back-off below
+
+// ---- PTX wrappers -------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+struct Ctl {
+  volatile int* abort_flag;   // shared memory
+  int32_t* status;            // global, may be null
+};
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait expired, or another one did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int code) {
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i >= WAIT_TIGHT_POLLS) {
+      __nanosleep(32);
+      if (*ctl.abort_flag) return false;
+      if (i >= WAIT_MAX_POLLS) {
+        *ctl.abort_flag = 1;
+        if (ctl.status) atomicExch(ctl.status, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                            // 128-byte swizzle
+  return d;
+}
+
+// instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                           ((uint32_t)(BLOCK_M >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- weight dequantisation ---------------------------------------------------------------------------
+// `w` holds 8 e2m1 codes of one row: nibble p of the low half-word is k = 2p, of the high half-word k = 2p+1.
+// The 3 magnitude bits dropped at bf16 bit 6 give value * 2^-126; one bf16x2 multiply by 2^(s-1)
+// (s = e8m0 byte) gives value * 2^(s-127) exactly.  Byte 0 multiplies by 0.0 as in the reference's upcast
+// (scale bits s << 7); bytes above 128 would overflow the single factor and take two multiplies.
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t sb) {
+  uint32_t v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = (w >> (4 * i)) & 0x000F000Fu;
+    v[i] = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
+  }
+  if (sb <= 128u) {
+    const uint32_t c = sb ? ((sb + 126u) << 7) : 0u;
+    const uint32_t c2 = c | (c << 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = bf16x2_mul(v[i], c2);
+  } else {
+    const uint32_t s2 = (sb << 7) | (sb << 23);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = bf16x2_mul(bf16x2_mul(v[i], 0x7E807E80u /* 2^126 */), s2);
+  }
+  return make_uint4(v[0], v[1], v[2], v[3]);
+}
+
+template <typename TY> __device__ __forceinline__ void store_out(TY* dst, const float* v, int n, bool vec_ok);
+template <>
+__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* dst, const float* v, int n, bool vec_ok) {
+  if (vec_ok) {
+    for (int j = 0; j < n; j += 8) {
+      __nv_bfloat162 h[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+      *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(h);
+    }
+  } else {
+    for (int j = 0; j < n; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_out<float>(float* dst, const float* v, int n, bool vec_ok) {
+  if (vec_ok) {
+    for (int j = 0; j < n; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+    for (int j = 0; j < n; ++j) dst[j] = v[j];
+  }
+}
+
+// =========================================================================================================
+template <typename TY>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  const uint32_t bar0 = sbase + OFF_BAR;
+  auto BAR_RAW_FULL = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+  auto BAR_RAW_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
+  auto BAR_A_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(2 * STAGES + s); };
+  auto BAR_B_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(3 * STAGES + s); };
+  auto BAR_AB_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(4 * STAGES + s); };
+  auto BAR_ACC_FULL = [&](int a) { return bar0 + 8u * (uint32_t)(5 * STAGES + a); };
+  auto BAR_ACC_EMPTY = [&](int a) { return bar0 + 8u * (uint32_t)(5 * STAGES + 2 + a); };
+  const uint32_t BAR_DRAIN = bar0 + 8u * (uint32_t)(5 * STAGES + 4);
+  (void)bars;
+
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+  Ctl ctl{s_abort, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(BAR_RAW_FULL(s), 1);
+      mbar_init(BAR_RAW_EMPTY(s), 4);
+      mbar_init(BAR_A_FULL(s), 2);
+      mbar_init(BAR_B_FULL(s), 4);
+      mbar_init(BAR_AB_EMPTY(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(BAR_ACC_FULL(a), 1);
+      mbar_init(BAR_ACC_EMPTY(a), 4);
+    }
+    mbar_init(BAR_DRAIN, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + OFF_MISC),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  // ---- tile schedule shared by every role -----------------------------------------------------------
+  const int NT = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int KT = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int64_t useful_m = p.slice_sizes ? (int64_t)p.block_offs[p.E] : grid_m_static;
+  const int64_t n_tiles = useful_m * NT;
+
+  if (warp == 0) {
+    // ================================= MMA issuer ===================================================
+    if (lane == 0) {
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
+        int e; int64_t row0; int rows;
+        if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+        const uint32_t ab = tc & 1u;
+        ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc >> 1) & 1u) ^ 1u, ctl, 101);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + ab * BLOCK_N;
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 102) && mbar_wait(BAR_B_FULL(s), ph, ctl, 103);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint64_t adesc = make_desc(sbase + OFF_A + s * A_STAGE_BYTES + h * SUBTILE_BYTES);
+            const uint64_t bdesc = make_desc(sbase + OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), (kt | h | kk) ? 1u : 0u);
+          }
+          mma_commit(BAR_AB_EMPTY(s));
+        }
+        if (ok) mma_commit(BAR_ACC_FULL(ab));
+      }
+      // make sure every MMA issued by this thread has retired before tensor memory is freed
+      mma_commit(BAR_DRAIN);
+      mbar_wait(BAR_DRAIN, 0, ctl, 104);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================================= weight producer =================================================
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      const uint8_t* wv = (const uint8_t*)p.w;
+      const uint8_t* ws = p.w_scale;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        int e; int64_t row0; int rows;
+        if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+        const int nt = (int)(tile % NT);
+        const int64_t tile0 = ((int64_t)e * NT + nt) * KT;
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 201);
+          if (!ok) break;
+          mbar_expect_tx(BAR_RAW_FULL(s), RAWV_BYTES + RAWS_BYTES);
+          bulk_g2s(sbase + OFF_RAWV + s * RAWV_BYTES, wv + (tile0 + kt) * RAWV_BYTES, RAWV_BYTES, BAR_RAW_FULL(s));
+          bulk_g2s(sbase + OFF_RAWS + s * RAWS_BYTES, ws + (tile0 + kt) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
+        }
+      }
+      if (!ok) {
+        // aborting: let the copies that were already issued land before the CTA leaves
+        const uint32_t lo = it > STAGES ? it - STAGES : 0;
+        for (uint32_t j = lo; j < it; ++j)
+          for (uint32_t i = 0; i < (1u << 16) && !mbar_test(BAR_RAW_FULL(j % STAGES), (j / STAGES) & 1u); ++i) __nanosleep(64);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // ================================= activation loader ==============================================
+    // Each of the two loader warps owns 64 rows of the tile and keeps their source rows in a private
+    // shared array, so the only synchronisation inside the role is __syncwarp (a CTA-level named barrier
+    // could be left waiting by a warp that aborted).
+    const int lw = warp - 2;                        // 0..1
+    const int cc = lane & 15;                       // 16-byte chunk of the 256-byte stage row
+    const int hh = lane >> 4;                       // rows 2 lw + hh + 4 i, i = 0..31
+    int64_t* s_src = reinterpret_cast<int64_t*>(smem + OFF_SRC) + lw * 64;
+    const __nv_bfloat16* X = (const __nv_bfloat16*)p.x;
+    const uint32_t a_off = (uint32_t)((cc >> 3) * SUBTILE_BYTES);
+    const int c8 = cc & 7;
+    uint32_t it = 0, it_sig = 0;
+    bool ok = true;
+    auto signal_oldest = [&]() {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_A_FULL(it_sig % STAGES));
+      ++it_sig;
+    };
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      int e; int64_t row0; int rows;
+      if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+      __syncwarp();                                 // the previous tile's source rows are no longer read
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int r = 2 * lw + h2 + 4 * lane;       // slot h2 * 32 + lane
+        int64_t src = -1;
+        if (r < rows) {
+          const int64_t m = row0 + r;
+          src = p.gather_indx ? (int64_t)p.gather_indx[m] : m;
+          if (src >= p.rows_x) src = -1;
+        }
+        s_src[h2 * 32 + lane] = src;
+      }
+      __syncwarp();
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int s = it % STAGES;
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_AB_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 301));
+        if (!ok) break;
+        const int k = kt * BLOCK_K + cc * 8;
+        const int kleft = p.K - k;
+        const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
+        const uint32_t stage = sbase + OFF_A + s * A_STAGE_BYTES + a_off;
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+          const int r = 2 * lw + hh + 4 * i;
+          const int64_t src = s_src[hh * 32 + i];
+          const bool live = src >= 0 && kbytes;
+          const void* g = live ? (const void*)(X + src * p.ld_x + k) : (const void*)X;
+          cp_async16(stage + (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4)), g, live ? kbytes : 0u);
+        }
+        cp_async_commit();
+        if (it - it_sig >= 2) {
+          cp_async_wait<2>();
+          signal_oldest();
+        }
+      }
+    }
+    cp_async_wait<0>();
+    while (it_sig < it) signal_oldest();
+  } else if (warp < 8) {
+    // ================================= dequantiser ======================================================
+    const int t = threadIdx.x - 128;                // 0..127
+    const int j = t & 15;                           // 32-bit word of the 64-byte packed row (8 k values)
+    const int rb = t >> 4;                          // rows rb + 8 i
+    const uint32_t b_off = (uint32_t)((j >> 3) * SUBTILE_BYTES);
+    const int c8 = j & 7;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      int e; int64_t row0; int rows;
+      if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        ok = __all_sync(0xFFFFFFFFu,
+                        mbar_wait(BAR_RAW_FULL(s), ph, ctl, 401) && mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
+        if (!ok) break;
+        const uint32_t* rv = reinterpret_cast<const uint32_t*>(smem + OFF_RAWV + s * RAWV_BYTES);
+        const uint8_t* rs = smem + OFF_RAWS + s * RAWS_BYTES;
+        uint8_t* bst = smem + OFF_B + s * B_STAGE_BYTES + b_off;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int r = rb + 8 * i;
+          const uint4 o = dequant8(rv[r * 16 + j], rs[r * 4 + (j >> 2)]);
+          *reinterpret_cast<uint4*>(bst + r * 128 + ((c8 ^ (r & 7)) << 4)) = o;
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(BAR_B_FULL(s));
+          mbar_arrive(BAR_RAW_EMPTY(s));
+        }
+      }
+    }
+  } else {
+    // ================================= epilogue =========================================================
+    const int q = warp & 3;                         // tensor-memory lane quarter of this warp
+    const int r = q * 32 + lane;                    // accumulator row = token row inside the tile
+    float* s_bias = reinterpret_cast<float*>(smem + OFF_BIAS) + q * BLOCK_N;   // private to this warp
+    TY* Y = (TY*)p.y;
+    const bool swiglu = p.activation == MOE_ACT_SWIGLU;
+    const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
+    uint32_t tc = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
+      int e; int64_t row0; int rows;
+      if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+      const int n0 = (int)(tile % NT) * BLOCK_N;
+      const uint32_t ab = tc & 1u;
+      // stage this tile's bias columns (each warp keeps its own copy: no CTA-level barrier in this role)
+      __syncwarp();
+#pragma unroll
+      for (int jb = 0; jb < BLOCK_N / 32; ++jb) {
+        const int gn = n0 + jb * 32 + lane;
+        s_bias[jb * 32 + lane] = (p.bias && gn < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + gn) : 0.0f;
+      }
+      __syncwarp();
+      const int64_t m = row0 + r;
+      const bool row_live = r < rows;
+      int64_t dst = m;
+      float beta = 1.0f, gamma = 1.0f;
+      if (row_live) {
+        if (p.scatter_indx) dst = p.scatter_indx[m];
+        if (p.betas) beta = p.betas[m];
+        if (p.gammas) gamma = p.gammas[m];
+      }
+      const bool store_row = row_live && dst >= 0;
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc >> 1) & 1u, ctl, 501));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * BLOCK_N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+        uint32_t raw[32];
+        tmem_ld32(taddr + (uint32_t)c0, raw);
+        tmem_ld_wait();
+        if (!store_row || n0 + c0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int jx = 0; jx < 32; ++jx) {
+          float a = __uint_as_float(raw[jx]) + s_bias[c0 + jx] * beta;
+          if (p.has_out_alpha) a *= p.out_alpha;
+          v[jx] = a;
+        }
+        const int ncols = min(32, p.N - (n0 + c0));
+        if (swiglu) {
+          float o[16];
+#pragma unroll
+          for (int jx = 0; jx < 16; ++jx)
+            o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
+          store_out<TY>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, ncols >> 1, y_vec && ncols == 32);
+        } else {
+#pragma unroll
+          for (int jx = 0; jx < 32; ++jx) v[jx] *= gamma;
+          store_out<TY>(Y + dst * p.ld_y + (n0 + c0), v, ncols, y_vec && ncols == 32);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_ACC_EMPTY(ab));
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+}  // namespace
+
+bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why) {
+  if (a.w_kind != MOE_W_MX4_B200) { *why = "weights are not in the B200 tiled layout"; return false; }
+  if (a.x_dtype != MOE_BF16) { *why = "activations are not bf16"; return false; }
+  if (a.y_dtype != MOE_BF16 && a.y_dtype != MOE_F32) { *why = "output is neither bf16 nor fp32"; return false; }
+  if ((uintptr_t)a.x % 16 != 0 || a.ld_x % 8 != 0) { *why = "activation rows are not 16-byte aligned"; return false; }
+  if ((uintptr_t)a.w % 16 != 0 || (uintptr_t)a.w_scale % 16 != 0) { *why = "weights are not 16-byte aligned"; return false; }
+  *why = "";
+  return true;
+}
+
+static int64_t n_blocks_bound128(int64_t n_slices, int64_t n_rows) {
+  if (n_rows <= n_slices) return n_rows;
+  const int64_t a = n_rows + 1 - n_slices;   // -(n_slices - n_rows - 1)
+  return n_slices - 1 + (a + 127) / 128;
+}
+
+int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_t st) {
+  GemmParams p = p_in;
+  int64_t grid_m;
+  if (a.slice_sizes) {
+    p.block_offs = a.block_offs_16 + 3 * a.ld_block_offs;      // block size 128
+    p.block_sched = a.block_sched_16 + 3 * a.ld_block_sched;
+    grid_m = n_blocks_bound128(a.E, a.M);
+  } else {
+    grid_m = cdiv64(a.M, BLOCK_M);
+  }
+  if (grid_m == 0) return MOE_OK;
+  const int64_t tiles = grid_m * cdiv64(a.N, BLOCK_N);
+  const int sms = moe_sm_count();
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  if (a.y_dtype == MOE_BF16) {
+    MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+    gemm_tc_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_ALLOC, st>>>(p, grid_m);
+  } else {
+    MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+    gemm_tc_kernel<float><<<grid, NUM_THREADS, SMEM_ALLOC, st>>>(p, grid_m);
+  }
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}

@@ -1,0 +1,267 @@
+// MXFP4 quantiser / dequantiser for sm_100a: e2m1 values packed two per byte (element 2i in the low
+// nibble) with one e8m0 scale byte per 32 elements along the quantised axis.
+//
+// Arithmetic (bit-exact with triton_kernels numerics_details/mxfp_details/_downcast_to_mxfp.py:33-147
+// and _upcast_from_mxfp.py:8-53, 109-220):
+//   m      = max |x| over the 32-group, in fp32
+//   ds     = m / 6 (ROUND_UP) or m / 4 (ROUND_DOWN), IEEE round-to-nearest division
+//   u      = (bits(ds) + 0x007FFFFF) & 0x7F800000  (ROUND_UP: next power of two)
+//            bits(ds) & 0x7F800000                  (ROUND_DOWN)
+//   scale  = u >> 23 ;  inv = (u == 0) ? 0 : 1 / float(u)
+//   code   = RTNE_e2m1(x * inv), saturating at +-6
+// Both kernels are HBM-bound: 16-byte loads/stores, four threads per 32-group on the contiguous path.
+#include "common.cuh"
+#include <cuda_fp4.h>
+
+namespace {
+
+__device__ __forceinline__ uint32_t scale_bits(float m, int mode) {
+  if (mode == MOE_ROUND_UP) {
+    float ds = __fdiv_rn(m, 6.0f);
+    return (__float_as_uint(ds) + 0x007FFFFFu) & 0x7F800000u;
+  }
+  float ds = __fdiv_rn(m, 4.0f);
+  return __float_as_uint(ds) & 0x7F800000u;
+}
+
+__device__ __forceinline__ float inv_scale(uint32_t u) {
+  float f = __uint_as_float(u);
+  return (f == 0.0f) ? 0.0f : __fdiv_rn(1.0f, f);
+}
+
+// two fp32 -> one byte: `lo` in bits 0..3, `hi` in bits 4..7 (round-to-nearest-even, saturating)
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+  return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+}
+
+template <typename T> struct Vec16;  // 16-byte vector of T
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+template <> struct Vec16<__half> { static constexpr int N = 8; };
+template <> struct Vec16<float> { static constexpr int N = 4; };
+
+// ---- contiguous path: quant axis has unit stride, rows 16-byte aligned ------------------------------
+// One thread owns 8 consecutive elements; 4 consecutive lanes own one 32-group.
+template <typename T>
+__global__ void __launch_bounds__(256) downcast_rows_kernel(const T* __restrict__ x, int64_t n_rows, int64_t quant,
+                                                            int64_t outer, int64_t sx_batch, int64_t sx_outer,
+                                                            uint8_t* __restrict__ q, uint8_t* __restrict__ scale,
+                                                            int mode) {
+  const int64_t chunks_per_row = quant >> 3;
+  const int64_t total = n_rows * chunks_per_row;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // every lane of a warp runs the same trip count (the shuffles below need the whole warp); lanes past the
+  // end compute on zeros and store nothing
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31); i0 < total; i0 += stride) {
+    const int64_t i = i0 + (threadIdx.x & 31);
+    const bool live = i < total;
+    const int64_t ii = live ? i : 0;
+    const int64_t row = ii / chunks_per_row;
+    const int64_t c = ii - row * chunks_per_row;
+    const int64_t b = row / outer, o = row - b * outer;
+    const T* src = x + b * sx_batch + o * sx_outer + c * 8;
+    float v[8];
+    if constexpr (sizeof(T) == 2) {
+      uint4 raw = *reinterpret_cast<const uint4*>(src);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
+    } else {
+      float4 a = *reinterpret_cast<const float4*>(src);
+      float4 bb = *reinterpret_cast<const float4*>(src + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = bb.x; v[5] = bb.y; v[6] = bb.z; v[7] = bb.w;
+    }
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    const uint32_t u = scale_bits(m, mode);
+    const float inv = inv_scale(u);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
+    if (live) {
+      *reinterpret_cast<uint32_t*>(q + row * (quant >> 1) + c * 4) = packed;
+      if ((c & 3) == 0) scale[row * (quant >> 5) + (c >> 2)] = (uint8_t)(u >> 23);
+    }
+  }
+}
+
+// ---- strided path: any strides; consecutive threads walk the `outer` axis ---------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) downcast_strided_kernel(const T* __restrict__ x, int64_t batch, int64_t outer,
+                                                               int64_t quant, int64_t sx_batch, int64_t sx_outer,
+                                                               int64_t sx_quant, uint8_t* __restrict__ q,
+                                                               uint8_t* __restrict__ scale, int mode) {
+  const int64_t groups = quant >> 5;
+  const int64_t total = batch * outer * groups;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t o = i % outer;
+    const int64_t t = i / outer;
+    const int64_t g = t % groups;
+    const int64_t b = t / groups;
+    const T* src = x + b * sx_batch + o * sx_outer + g * 32 * sx_quant;
+    float v[32];
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      v[j] = to_f32<T>(src[j * sx_quant]);
+      m = fmaxf(m, fabsf(v[j]));
+    }
+    const uint32_t u = scale_bits(m, mode);
+    const float inv = inv_scale(u);
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t p = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p |= e2m1x2(v[8 * k + 2 * j] * inv, v[8 * k + 2 * j + 1] * inv) << (8 * j);
+      w[k] = p;
+    }
+    const int64_t row = b * outer + o;
+    *reinterpret_cast<uint4*>(q + row * (quant >> 1) + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    scale[row * groups + g] = (uint8_t)(u >> 23);
+  }
+}
+
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+  // magnitude bits e1 e0 m: 0, .5, 1, 1.5, 2, 3, 4, 6
+  const uint32_t mag = code & 7u;
+  uint32_t bits = (mag == 0) ? 0u : (mag == 1) ? 0x3F000000u : (((mag >> 1) + 126u) << 23) | ((mag & 1u) << 22);
+  return __uint_as_float(bits | ((code & 8u) << 28));
+}
+
+template <typename T> __device__ __forceinline__ float finite_max();
+template <> __device__ __forceinline__ float finite_max<float>() { return 3.4028234663852886e+38f; }
+template <> __device__ __forceinline__ float finite_max<__nv_bfloat16>() { return 3.3895313892515355e+38f; }
+template <> __device__ __forceinline__ float finite_max<__half>() { return 65504.0f; }
+
+template <typename T>
+__device__ __forceinline__ T dequant_one(uint32_t code, float s, bool nan_scale) {
+  float r = e2m1_to_f32(code) * s;
+  const float mx = finite_max<T>();
+  r = fminf(fmaxf(r, -mx), mx);
+  if (nan_scale) r = __uint_as_float(0x7FC00000u);
+  return from_f32<T>(r);
+}
+
+// contiguous output: thread owns 8 elements (4 input bytes)
+template <typename T>
+__global__ void __launch_bounds__(256) upcast_rows_kernel(const uint8_t* __restrict__ q,
+                                                          const uint8_t* __restrict__ scale, T* __restrict__ out,
+                                                          int64_t n_rows, int64_t quant, int64_t outer,
+                                                          int64_t so_batch, int64_t so_outer) {
+  const int64_t chunks_per_row = quant >> 3;
+  const int64_t total = n_rows * chunks_per_row;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t row = i / chunks_per_row;
+    const int64_t c = i - row * chunks_per_row;
+    const int64_t b = row / outer, o = row - b * outer;
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(q + row * (quant >> 1) + c * 4);
+    const uint32_t sb = scale[row * (quant >> 5) + (c >> 2)];
+    const float s = __uint_as_float(sb << 23);
+    const bool nan_scale = sb == 0xFFu;
+    T* dst = out + b * so_batch + o * so_outer + c * 8;
+    T e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = dequant_one<T>((w >> (4 * j)) & 0xFu, s, nan_scale);
+    if constexpr (sizeof(T) == 2) {
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(e);
+    } else {
+      *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(e);
+      *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(e + 4);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) upcast_strided_kernel(const uint8_t* __restrict__ q,
+                                                             const uint8_t* __restrict__ scale, T* __restrict__ out,
+                                                             int64_t batch, int64_t outer, int64_t quant,
+                                                             int64_t so_batch, int64_t so_outer, int64_t so_quant) {
+  const int64_t groups = quant >> 5;
+  const int64_t total = batch * outer * groups;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t o = i % outer;
+    const int64_t t = i / outer;
+    const int64_t g = t % groups;
+    const int64_t b = t / groups;
+    const int64_t row = b * outer + o;
+    const uint4 raw = *reinterpret_cast<const uint4*>(q + row * (quant >> 1) + g * 16);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const uint32_t sb = scale[row * groups + g];
+    const float s = __uint_as_float(sb << 23);
+    const bool nan_scale = sb == 0xFFu;
+    T* dst = out + b * so_batch + o * so_outer + g * 32 * so_quant;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dst[j * so_quant] = dequant_one<T>((w[j >> 3] >> (4 * (j & 7))) & 0xFu, s, nan_scale);
+  }
+}
+
+int grid_for(int64_t total, int threads) {
+  int64_t blocks = cdiv64(total, threads);
+  int64_t cap = (int64_t)moe_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_downcast_mxfp4(const void* x, int src_dtype, int64_t batch, int64_t outer, int64_t quant,
+                                  int64_t sx_batch, int64_t sx_outer, int64_t sx_quant, uint8_t* q, uint8_t* scale,
+                                  int rounding_mode, void* stream) {
+  MOE_CHECK_ARG(batch >= 0 && outer >= 0 && quant >= 0, "moe_downcast_mxfp4: negative extent");
+  MOE_CHECK_ARG(quant % 32 == 0, "moe_downcast_mxfp4: quantised axis (%lld) must be a multiple of 32", (long long)quant);
+  MOE_CHECK_ARG(rounding_mode == MOE_ROUND_UP || rounding_mode == MOE_ROUND_DOWN, "moe_downcast_mxfp4: bad rounding mode");
+  if (batch * outer * quant == 0) return MOE_OK;
+  MOE_CHECK_ARG(x && q && scale, "moe_downcast_mxfp4: NULL pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  MOE_DISPATCH_FLOAT(src_dtype, T, {
+    const int64_t align = 16 / (int64_t)sizeof(T);
+    const bool rows_ok = sx_quant == 1 && ((uintptr_t)x % 16 == 0) && (sx_outer % align == 0) &&
+                         (sx_batch % align == 0) && ((uintptr_t)q % 4 == 0);
+    if (rows_ok) {
+      const int64_t total = batch * outer * (quant >> 3);
+      downcast_rows_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, batch * outer, quant, outer, sx_batch,
+                                                                    sx_outer, q, scale, rounding_mode);
+    } else {
+      MOE_CHECK_ARG((uintptr_t)q % 16 == 0, "moe_downcast_mxfp4: q must be 16-byte aligned");
+      const int64_t total = batch * outer * (quant >> 5);
+      downcast_strided_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, batch, outer, quant, sx_batch,
+                                                                       sx_outer, sx_quant, q, scale, rounding_mode);
+    }
+  });
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_upcast_mxfp4(const uint8_t* q, const uint8_t* scale, void* out, int dst_dtype, int64_t batch,
+                                int64_t outer, int64_t quant, int64_t so_batch, int64_t so_outer, int64_t so_quant,
+                                void* stream) {
+  MOE_CHECK_ARG(batch >= 0 && outer >= 0 && quant >= 0, "moe_upcast_mxfp4: negative extent");
+  MOE_CHECK_ARG(quant % 32 == 0, "moe_upcast_mxfp4: quantised axis (%lld) must be a multiple of 32", (long long)quant);
+  if (batch * outer * quant == 0) return MOE_OK;
+  MOE_CHECK_ARG(q && scale && out, "moe_upcast_mxfp4: NULL pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  MOE_DISPATCH_FLOAT(dst_dtype, T, {
+    const int64_t align = 16 / (int64_t)sizeof(T);
+    const bool rows_ok = so_quant == 1 && ((uintptr_t)out % 16 == 0) && (so_outer % align == 0) &&
+                         (so_batch % align == 0) && ((uintptr_t)q % 4 == 0);
+    if (rows_ok) {
+      const int64_t total = batch * outer * (quant >> 3);
+      upcast_rows_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(q, scale, (T*)out, batch * outer, quant, outer,
+                                                                  so_batch, so_outer);
+    } else {
+      MOE_CHECK_ARG((uintptr_t)q % 16 == 0, "moe_upcast_mxfp4: q must be 16-byte aligned");
+      const int64_t total = batch * outer * (quant >> 5);
+      upcast_strided_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(q, scale, (T*)out, batch, outer, quant, so_batch,
+                                                                     so_outer, so_quant);
+    }
+  });
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}

@@ -1,0 +1,439 @@
+// Routing kernels for sm_100a: top-k (+softmax) + expert bitmatrix, the expert histogram with the
+// stable expert-major sort of the (token, slot) entries, and the ragged-segment metadata.
+//
+// Semantics follow triton_kernels topk_details/_topk_forward.py:15-150, tensor_details/bitmatrix.py:43-150
+// and tensor_details/ragged_tensor.py:128-210, 310-381; the kernels themselves are organised
+// differently (one warp per token row for the top-k; a three-pass counting sort instead of
+// per-block bitonic sorts; one launch each for the ragged metadata and its remap).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kMaxTopK = 64;
+
+// order-preserving map float -> uint32 (larger float <=> larger key)
+__device__ __forceinline__ uint32_t float_key(float f) {
+  uint32_t b = __float_as_uint(f);
+  return b ^ ((b & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  uint32_t b = k ^ ((k & 0x80000000u) ? 0x80000000u : 0xFFFFFFFFu);
+  return __uint_as_float(b);
+}
+
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+
+// One warp per token row.  Selection i picks the largest packed key (value key << 32 | ~index) that is
+// smaller than the key picked by selection i-1, so equal values resolve to the smaller expert index and
+// the k results come out sorted by (value desc, index asc).  The row is re-read from L1 for each pick.
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) topk_kernel(
+    const T* __restrict__ logits, int64_t ld_logits, int64_t T_rows, int E, int k, int apply_softmax,
+    T* __restrict__ vals, int64_t ld_vals, int16_t* __restrict__ indx, int64_t ld_indx,
+    uint32_t* __restrict__ bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,
+    const int32_t* __restrict__ n_rows_dev, int use_provided_indx) {
+  __shared__ float s_val[kWarpsPerBlock][kMaxTopK];
+  __shared__ int s_idx[kWarpsPerBlock][kMaxTopK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
+  const int64_t n_rows = n_rows_dev ? (int64_t)*n_rows_dev : T_rows;
+  if (row >= T_rows || row >= n_rows) return;
+  const T* x = logits + row * ld_logits;
+
+  if (use_provided_indx) {
+    for (int j = lane; j < k; j += 32) {
+      int e = indx[row * ld_indx + j];
+      s_idx[warp][j] = e;
+      s_val[warp][j] = to_f32<T>(x[e]);
+    }
+  } else {
+    unsigned long long prev = ~0ull;
+    for (int j = 0; j < k; ++j) {
+      unsigned long long best = 0ull;
+      for (int e = lane; e < E; e += 32) {
+        unsigned long long key = ((unsigned long long)float_key(to_f32<T>(x[e])) << 32) | (uint32_t)(~(uint32_t)e);
+        if (key < prev && key > best) best = key;
+      }
+      best = warp_max_u64(best);
+      prev = best;
+      if (lane == 0) {
+        s_idx[warp][j] = (int)(~(uint32_t)(best & 0xFFFFFFFFull));
+        s_val[warp][j] = key_float((uint32_t)(best >> 32));
+      }
+    }
+  }
+  __syncwarp();
+
+  if (apply_softmax) {
+    float mx = -INFINITY;
+    for (int j = 0; j < k; ++j) mx = fmaxf(mx, s_val[warp][j]);
+    float sum = 0.0f;
+    for (int j = 0; j < k; ++j) sum += expf(s_val[warp][j] - mx);
+    for (int j = lane; j < k; j += 32) vals[row * ld_vals + j] = from_f32<T>(__fdiv_rn(expf(s_val[warp][j] - mx), sum));
+  } else {
+    for (int j = lane; j < k; j += 32) vals[row * ld_vals + j] = from_f32<T>(s_val[warp][j]);
+  }
+  if (!use_provided_indx)
+    for (int j = lane; j < k; j += 32) indx[row * ld_indx + j] = (int16_t)s_idx[warp][j];
+
+  const int words = (E + 31) >> 5;
+  for (int w = lane; w < words; w += 32) {
+    uint32_t bits = 0;
+    for (int j = 0; j < k; ++j) {
+      int e = s_idx[warp][j];
+      if ((e >> 5) == w) bits |= 1u << (e & 31);
+    }
+    bitmatrix[row * bm_stride_row + (int64_t)w * bm_stride_word] = bits;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Expert histogram + stable expert-major sort.  Flat entry i = token * k + slot, expert c = indx[i]
+// (negative, or token >= n_rows: dropped).  row_sorted[i] = col_offs[c] + #{j < i : indx[j] == c},
+// col_sorted = inverse permutation; both -1 padded.
+//   pass 1: per block of kTokPerBlock tokens, a shared-memory histogram -> partial[blk][e]; global
+//           histogram by atomics; both index arrays pre-filled with -1.
+//   pass 2: exclusive scan of partial[.][e] over blocks, exclusive scan of col_sum -> col_offs.
+//   pass 3: rank inside the block: each warp owns 32 consecutive tokens and ranks them in order with
+//           warp match, on top of the counts of the warps before it.
+constexpr int kTokPerBlock = 256;
+
+__device__ __forceinline__ int entry_expert(const int16_t* indx, int64_t ld_indx, int k, int64_t token, int slot,
+                                            int64_t n_rows, int E) {
+  if (token >= n_rows) return -1;
+  int c = indx[token * ld_indx + slot];
+  return (c < 0 || c >= E) ? -1 : c;
+}
+
+__global__ void __launch_bounds__(256) bm_hist_kernel(const int16_t* __restrict__ indx, int64_t ld_indx, int64_t T_rows,
+                                                      int E, int k, const int32_t* __restrict__ n_rows_dev,
+                                                      int32_t* __restrict__ col_sum, int32_t* __restrict__ partial,
+                                                      int32_t* __restrict__ col_sorted, int32_t* __restrict__ row_sorted) {
+  extern __shared__ int32_t s_cnt[];
+  const int64_t n_rows = n_rows_dev ? min((int64_t)*n_rows_dev, T_rows) : T_rows;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+  __syncthreads();
+  const int64_t tok0 = (int64_t)blockIdx.x * kTokPerBlock;
+  const int64_t n_ent = (int64_t)kTokPerBlock * k;
+  for (int64_t j = threadIdx.x; j < n_ent; j += blockDim.x) {
+    const int64_t token = tok0 + j / k;
+    if (token >= T_rows) break;
+    const int slot = (int)(j % k);
+    const int64_t flat = token * k + slot;
+    col_sorted[flat] = -1;
+    row_sorted[flat] = -1;
+    int c = entry_expert(indx, ld_indx, k, token, slot, n_rows, E);
+    if (c >= 0) atomicAdd(&s_cnt[c], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int v = s_cnt[e];
+    partial[(int64_t)blockIdx.x * E + e] = v;
+    if (v) atomicAdd(&col_sum[e], v);
+  }
+}
+
+// block-wide exclusive scan of `n` ints (in place allowed), returns nothing; one block only.
+__device__ void block_exclusive_scan(const int32_t* in, int32_t* out, int n, int32_t* s_warp /*[33]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int carry = 0;
+  for (int base = 0; base < n; base += blockDim.x) {
+    int i = base + threadIdx.x;
+    int v = (i < n) ? in[i] : 0;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      int w = (lane < nwarps) ? s_warp[lane] : 0;
+      int winc = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xFFFFFFFFu, winc, o);
+        if (lane >= o) winc += t;
+      }
+      s_warp[lane] = winc - w;          // exclusive warp offsets
+      if (lane == 31) s_warp[32] = winc;  // chunk total
+    }
+    __syncthreads();
+    if (i < n) out[i] = carry + s_warp[warp] + inc - v;
+    carry += s_warp[32];
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(1024) bm_scan_kernel(int32_t* __restrict__ partial, int64_t n_blocks, int E,
+                                                       const int32_t* __restrict__ col_sum,
+                                                       int32_t* __restrict__ col_offs) {
+  __shared__ int32_t s_warp[33];
+  if (blockIdx.x == 0) {
+    block_exclusive_scan(col_sum, col_offs, E, s_warp);
+    return;
+  }
+  // remaining blocks: one thread per expert walks the blocks of tokens
+  const int e = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int run = 0;
+  for (int64_t b = 0; b < n_blocks; ++b) {
+    int v = partial[b * E + e];
+    partial[b * E + e] = run;
+    run += v;
+  }
+}
+
+__global__ void __launch_bounds__(256) bm_rank_kernel(const int16_t* __restrict__ indx, int64_t ld_indx, int64_t T_rows,
+                                                      int E, int k, const int32_t* __restrict__ n_rows_dev,
+                                                      const int32_t* __restrict__ partial,
+                                                      const int32_t* __restrict__ col_offs,
+                                                      int32_t* __restrict__ col_sorted, int32_t* __restrict__ row_sorted) {
+  extern __shared__ int32_t s_cnt[];  // [8 warps][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n_rows = n_rows_dev ? min((int64_t)*n_rows_dev, T_rows) : T_rows;
+  int32_t* my = s_cnt + (int64_t)warp * E;
+  for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) s_cnt[i] = 0;
+  __syncthreads();
+  const int64_t tok0 = (int64_t)blockIdx.x * kTokPerBlock + warp * 32;
+  const int n_ent = 32 * k;
+  // count the entries of this warp's 32 tokens
+  for (int j = lane; j < n_ent; j += 32) {
+    int c = entry_expert(indx, ld_indx, k, tok0 + j / k, j % k, n_rows, E);
+    if (c >= 0) atomicAdd(&my[c], 1);
+  }
+  __syncthreads();
+  // turn the per-warp counts into starting offsets: base + counts of the warps before this one
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = partial[(int64_t)blockIdx.x * E + e] + col_offs[e];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      int v = s_cnt[w * E + e];
+      s_cnt[w * E + e] = run;
+      run += v;
+    }
+  }
+  __syncthreads();
+  // rank in order, 32 entries at a time
+  for (int j0 = 0; j0 < n_ent; j0 += 32) {
+    const int j = j0 + lane;
+    const int64_t token = tok0 + j / k;
+    const int slot = j % k;
+    int c = (j < n_ent && token < T_rows) ? entry_expert(indx, ld_indx, k, token, slot, n_rows, E) : -1;
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, c);
+    const int before = __popc(peers & ((1u << lane) - 1u));
+    int base = 0;
+    if (c >= 0) base = my[c];
+    __syncwarp();
+    if (c >= 0 && before == 0) my[c] = base + __popc(peers);
+    __syncwarp();
+    if (c >= 0) {
+      const int pos = base + before;
+      const int64_t flat = token * k + slot;
+      row_sorted[flat] = pos;
+      col_sorted[pos] = (int32_t)flat;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Ragged metadata.  blockIdx.x = 0: slice_offs (block size 1); 1..4: block sizes 16,32,64,128.
+// Every block scans its own offsets into shared memory; blockIdx.y == 0 writes them out; all blocks of
+// a row fill their chunk of the schedule by binary search: sched[p] = ((p - offs[e]) << 16) | e.
+constexpr int kSchedChunk = 4096;
+
+__global__ void __launch_bounds__(1024) ragged_kernel(const int32_t* __restrict__ slice_sizes, int E,
+                                                      int32_t* __restrict__ slice_offs, int32_t* __restrict__ block_offs,
+                                                      int64_t ld_block_offs, int32_t* __restrict__ block_sched,
+                                                      int64_t ld_sched, int64_t n_sched) {
+  extern __shared__ int32_t s_offs[];  // [E + 1] then scratch [E + 1]
+  __shared__ int32_t s_warp[33];
+  const int row = blockIdx.x;                     // 0 = slice_offs
+  const int log2bs = row == 0 ? 0 : row + 3;
+  int32_t* s_nb = s_offs + (E + 1);
+  for (int e = threadIdx.x; e <= E; e += blockDim.x)
+    s_nb[e] = (e < E) ? (int32_t)(((int64_t)max(slice_sizes[e], 0) + ((1 << log2bs) - 1)) >> log2bs) : 0;
+  __syncthreads();
+  block_exclusive_scan(s_nb, s_offs, E + 1, s_warp);
+  __syncthreads();
+  int32_t* dst = row == 0 ? slice_offs : block_offs + (int64_t)(row - 1) * ld_block_offs;
+  if (blockIdx.y == 0)
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) dst[e] = s_offs[e];
+  if (row == 0) return;
+  const int32_t total = s_offs[E];
+  int32_t* sched = block_sched + (int64_t)(row - 1) * ld_sched;
+  const int64_t p0 = (int64_t)blockIdx.y * kSchedChunk;
+  for (int64_t p = p0 + threadIdx.x; p < min(p0 + kSchedChunk, n_sched); p += blockDim.x) {
+    int32_t v = -1;
+    if (p < total) {
+      int lo = 0, hi = E;  // largest e with offs[e] <= p
+      while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (s_offs[mid] <= p) lo = mid; else hi = mid;
+      }
+      v = (int32_t)(((uint32_t)(p - s_offs[lo]) << 16) | (uint32_t)lo);
+    }
+    sched[p] = v;
+  }
+}
+
+// Stable compaction by one block: out[rank(i)] = val(i) for kept i, tail filled with -1. Returns the count.
+template <typename ValFn, typename KeepFn>
+__device__ int block_compact(int32_t* out, int64_t n, ValFn val, KeepFn keep, int32_t* s_warp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int carry = 0;
+  for (int64_t base = 0; base < n; base += blockDim.x) {
+    const int64_t i = base + threadIdx.x;
+    const bool kp = (i < n) && keep(i);
+    const unsigned m = __ballot_sync(0xFFFFFFFFu, kp);
+    if (lane == 0) s_warp[warp] = __popc(m);
+    __syncthreads();
+    int off = 0, tot = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      int c = s_warp[w];
+      if (w < warp) off += c;
+      tot += c;
+    }
+    if (kp) out[carry + off + __popc(m & ((1u << lane) - 1u))] = val(i);
+    carry += tot;
+    __syncthreads();
+  }
+  for (int64_t i = carry + threadIdx.x; i < n; i += blockDim.x) out[i] = -1;
+  return carry;
+}
+
+__global__ void __launch_bounds__(1024) ragged_remap_kernel(
+    const int32_t* __restrict__ slice_sizes, const int32_t* __restrict__ slice_offs,
+    const int32_t* __restrict__ block_offs, int64_t ld_block_offs, const int32_t* __restrict__ block_sched,
+    int64_t ld_sched, int64_t n_sched, const int32_t* __restrict__ slice_map, int E, int32_t* __restrict__ o_sizes,
+    int32_t* __restrict__ o_offs, int32_t* __restrict__ o_block_offs, int32_t* __restrict__ o_sched) {
+  __shared__ int32_t s_warp[32];
+  const int b = blockIdx.x;
+  auto keep_slice = [&](int64_t i) { return i < E && slice_map[i] != -1; };
+  if (b == 0) {
+    block_compact(o_sizes, E, [&](int64_t i) { return slice_sizes[i]; }, keep_slice, s_warp);
+    __syncthreads();
+    block_compact(o_offs, E + 1, [&](int64_t i) { return slice_offs[i]; }, keep_slice, s_warp);
+    __syncthreads();
+  }
+  const int32_t* bo = block_offs + (int64_t)b * ld_block_offs;
+  const int32_t* bs = block_sched + (int64_t)b * ld_sched;
+  int32_t* obo = o_block_offs + (int64_t)b * ld_block_offs;
+  int32_t* obs = o_sched + (int64_t)b * ld_sched;
+  const int n_kept = block_compact(obo, E + 1, [&](int64_t i) { return bo[i]; }, keep_slice, s_warp);
+  __syncthreads();
+  const int n_blk = block_compact(
+      obs, n_sched,
+      [&](int64_t i) {
+        uint32_t v = (uint32_t)bs[i];
+        return (int32_t)((v & 0xFFFF0000u) | (uint32_t)slice_map[v & 0xFFFFu]);
+      },
+      [&](int64_t i) {
+        uint32_t v = (uint32_t)bs[i];
+        uint32_t s = v & 0xFFFFu;
+        return s != 0xFFFFu && (int)s < E && slice_map[s] != -1;
+      },
+      s_warp);
+  __syncthreads();
+  if (threadIdx.x == 0) obo[n_kept] = n_blk;
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_topk_fwd(const void* logits, int dtype, int64_t T, int E, int k, int apply_softmax,
+                            int64_t ld_logits, void* vals, int64_t ld_vals, int16_t* indx, int64_t ld_indx,
+                            uint32_t* bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,
+                            const int32_t* n_rows_dev, int use_provided_indx, void* stream) {
+  MOE_CHECK_ARG(T >= 0 && E > 0 && E < 32768, "moe_topk_fwd: need 0 < n_expts < 32768, got %d", E);
+  MOE_CHECK_ARG(k > 0 && k <= kMaxTopK && k <= E, "moe_topk_fwd: need 0 < k <= min(%d, n_expts), got %d", kMaxTopK, k);
+  if (T == 0) return MOE_OK;
+  MOE_CHECK_ARG(logits && vals && indx && bitmatrix, "moe_topk_fwd: NULL pointer");
+  const int grid = (int)cdiv64(T, kWarpsPerBlock);
+  cudaStream_t st = (cudaStream_t)stream;
+  MOE_DISPATCH_FLOAT(dtype, Tv, {
+    topk_kernel<Tv><<<grid, kWarpsPerBlock * 32, 0, st>>>((const Tv*)logits, ld_logits, T, E, k, apply_softmax,
+                                                          (Tv*)vals, ld_vals, indx, ld_indx, bitmatrix, bm_stride_row,
+                                                          bm_stride_word, n_rows_dev, use_provided_indx);
+  });
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) size_t moe_bitmatrix_metadata_workspace(int64_t T, int E, int k) {
+  (void)k;
+  const int64_t nb = cdiv64(T > 0 ? T : 1, kTokPerBlock);
+  return (size_t)((nb * E + E) * (int64_t)sizeof(int32_t));
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_bitmatrix_metadata(const int16_t* indx, int64_t ld_indx, int64_t T, int E, int k,
+                                      const int32_t* n_rows_dev, int32_t* col_sum, int32_t* col_sorted,
+                                      int32_t* row_sorted, void* workspace, size_t workspace_bytes, void* stream) {
+  MOE_CHECK_ARG(T >= 0 && E > 0 && k > 0, "moe_bitmatrix_metadata: bad extents T=%lld E=%d k=%d", (long long)T, E, k);
+  MOE_CHECK_ARG(col_sum, "moe_bitmatrix_metadata: col_sum is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  MOE_CHECK_CUDA(cudaMemsetAsync(col_sum, 0, sizeof(int32_t) * (size_t)E, st));
+  if (T == 0) return MOE_OK;
+  MOE_CHECK_ARG(indx && col_sorted && row_sorted && workspace, "moe_bitmatrix_metadata: NULL pointer");
+  MOE_CHECK_ARG(workspace_bytes >= moe_bitmatrix_metadata_workspace(T, E, k),
+                "moe_bitmatrix_metadata: workspace too small (%zu < %zu)", workspace_bytes,
+                moe_bitmatrix_metadata_workspace(T, E, k));
+  const size_t smem_rank = (size_t)8 * E * sizeof(int32_t);
+  MOE_CHECK_ARG(smem_rank <= 200 * 1024, "moe_bitmatrix_metadata: n_expts=%d too large for the shared-memory counters", E);
+  const int64_t nb = cdiv64(T, kTokPerBlock);
+  int32_t* partial = (int32_t*)workspace;
+  int32_t* col_offs = partial + nb * E;
+  bm_hist_kernel<<<(int)nb, 256, (size_t)E * sizeof(int32_t), st>>>(indx, ld_indx, T, E, k, n_rows_dev, col_sum, partial,
+                                                                  col_sorted, row_sorted);
+  MOE_CHECK_LAUNCH();
+  bm_scan_kernel<<<1 + (int)cdiv64(E, 1024), 1024, 0, st>>>(partial, nb, E, col_sum, col_offs);
+  MOE_CHECK_LAUNCH();
+  if (smem_rank > 48 * 1024)
+    MOE_CHECK_CUDA(cudaFuncSetAttribute(bm_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rank));
+  bm_rank_kernel<<<(int)nb, 256, smem_rank, st>>>(indx, ld_indx, T, E, k, n_rows_dev, partial, col_offs, col_sorted,
+                                                  row_sorted);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_ragged_metadata(const int32_t* slice_sizes, int E, int32_t* slice_offs, int32_t* block_offs,
+                                   int64_t ld_block_offs, int32_t* block_sched, int64_t ld_sched, int64_t n_sched,
+                                   void* stream) {
+  MOE_CHECK_ARG(E > 0 && E < 65535, "moe_ragged_metadata: need 0 < n_slices < 65535, got %d", E);
+  MOE_CHECK_ARG(slice_sizes && slice_offs && block_offs && (block_sched || n_sched == 0), "moe_ragged_metadata: NULL pointer");
+  MOE_CHECK_ARG(ld_block_offs >= E + 1 && ld_sched >= n_sched, "moe_ragged_metadata: leading dimensions too small");
+  const size_t smem = (size_t)2 * (E + 1) * sizeof(int32_t);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (smem > 48 * 1024)
+    MOE_CHECK_CUDA(cudaFuncSetAttribute(ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(5, (unsigned)(n_sched > 0 ? cdiv64(n_sched, kSchedChunk) : 1));
+  ragged_kernel<<<grid, 1024, smem, st>>>(slice_sizes, E, slice_offs, block_offs, ld_block_offs, block_sched, ld_sched,
+                                          n_sched);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_ragged_metadata_remap(const int32_t* slice_sizes, const int32_t* slice_offs,
+                                         const int32_t* block_offs, int64_t ld_block_offs, const int32_t* block_sched,
+                                         int64_t ld_sched, int64_t n_sched, const int32_t* slice_map, int E,
+                                         int32_t* out_slice_sizes, int32_t* out_slice_offs, int32_t* out_block_offs,
+                                         int32_t* out_block_sched, void* stream) {
+  MOE_CHECK_ARG(E > 0 && E < 65535, "moe_ragged_metadata_remap: need 0 < n_slices < 65535, got %d", E);
+  MOE_CHECK_ARG(slice_sizes && slice_offs && block_offs && slice_map && out_slice_sizes && out_slice_offs &&
+                    out_block_offs && (n_sched == 0 || (block_sched && out_block_sched)),
+                "moe_ragged_metadata_remap: NULL pointer");
+  ragged_remap_kernel<<<4, 1024, 0, (cudaStream_t)stream>>>(slice_sizes, slice_offs, block_offs, ld_block_offs,
+                                                            block_sched, ld_sched, n_sched, slice_map, E,
+                                                            out_slice_sizes, out_slice_offs, out_block_offs,
+                                                            out_block_sched);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}

@@ -1,0 +1,241 @@
+"""Expert parallelism: expert -> rank assignment and the two token exchanges of an EP MoE layer
+(triton_kernels/distributed.py:9-95, 176-211, 256-283; distributed_details/mesh.py).
+
+Design.  One process per GPU over `torch.distributed` (NCCL on GPUs).  Routing metadata is replicated:
+every rank holds the global top-k indices and the global expert-major sort, as in the reference.  The
+reference moves rows with peer stores into symmetric memory; here each exchange is ONE variable-size
+NCCL all-to-all over NVLink: rows are packed per destination (CUDA gather kernel), exchanged, and
+unpacked into the position the reference would have stored them at (CUDA scatter kernel).  The split
+sizes are a W x W count matrix computed on the device from the replicated metadata and read by the host
+once per exchange pair.  No TMA multicast and no loads from peer memory are involved.
+"""
+import random
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+@dataclass
+class ExptAssignment:
+    # [n_shards, ceil(n_expts / 32)] int32: bit j of word j // 32 set iff expert j lives on the shard
+    expt_bitmask: torch.Tensor
+    # [n_shards, n_expts] bool
+    expt_boolmask: torch.Tensor
+    # [n_shards, n_expts] int32: local id of expert j on the shard, or -1
+    expt_map: torch.Tensor
+    n_expts_per_shard: list
+
+
+def make_expt_dict_uniform(n_expt_shard, n_expt_tot):
+    """shard i owns experts [i * (n/shards), (i+1) * (n/shards))"""
+    per = n_expt_tot // n_expt_shard
+    return {i: list(range(per * i, per * (i + 1))) for i in range(n_expt_shard)}
+
+
+def make_expt_dict_random(n_expt_shard, n_expt_tot):
+    """disjoint random subsets, no empty shard (seeded)"""
+    rng = random.Random(0)
+    perm = list(range(n_expt_tot))
+    rng.shuffle(perm)
+    cuts = [0] + sorted(rng.sample(range(1, n_expt_tot), n_expt_shard - 1)) + [n_expt_tot]
+    return {i: perm[cuts[i]:cuts[i + 1]] for i in range(n_expt_shard)}
+
+
+def make_expt_assignment(n_expt_shard, n_expt_tot, expt_dict, device) -> ExptAssignment:
+    words = (n_expt_tot + 31) // 32
+    bitmask = torch.zeros((n_expt_shard, words), dtype=torch.int64)
+    boolmask = torch.zeros((n_expt_shard, n_expt_tot), dtype=torch.bool)
+    counts = [0] * n_expt_tot
+    for shard, experts in expt_dict.items():
+        if not isinstance(experts, (list, tuple)):
+            raise TypeError(f"expt_dict[{shard}] must be a list/tuple of ints")
+        if len(experts) == 0:
+            raise ValueError(f"shard {shard} has no experts")
+        if shard < 0 or shard >= n_expt_shard:
+            raise ValueError(f"shard {shard} out of range [0, {n_expt_shard})")
+        for e in experts:
+            if not (0 <= e < n_expt_tot):
+                raise ValueError(f"expert id {e} out of range [0, {n_expt_tot})")
+            counts[e] += 1
+            bitmask[shard, e >> 5] |= (1 << (e & 31))
+            boolmask[shard, e] = True
+    if not all(c == 1 for c in counts):
+        raise ValueError("each expert must be owned by exactly one shard")
+    bitmask = torch.where(bitmask >= 2**31, bitmask - 2**32, bitmask).to(torch.int32)
+    expt_map = torch.full((n_expt_shard, n_expt_tot), -1, dtype=torch.int32)
+    for shard, experts in expt_dict.items():
+        for local_id, global_id in enumerate(sorted(experts)):
+            expt_map[shard, global_id] = local_id
+    return ExptAssignment(bitmask.to(device), boolmask.to(device), expt_map.to(device),
+                          [len(v) for v in expt_dict.values()])
+
+
+class Mesh:
+
+    def __init__(self, process_group=None):
+        self.process_group = process_group
+        if dist.is_available() and dist.is_initialized():
+            self.world_size = dist.get_world_size(process_group)
+            self.local_rank = dist.get_rank(process_group)
+        else:
+            self.world_size, self.local_rank = 1, 0
+
+
+class SymmetricMemoryPool:
+    """Holds the process group of the EP exchange.  The name is the reference's (its pool carves one
+    symmetric-memory arena); with NCCL all-to-all there is no peer-mapped memory to manage, so this object
+    only carries the mesh and the sizes given to `initialize_matmul`."""
+
+    def __init__(self, mesh: Mesh):
+        self.mesh = mesh
+        self._is_initialized = False
+        self.sizes = {}
+
+    def initialize_matmul(self, n_tokens_global, d_input, d_model, n_expts_act, n_expts_tot, dtype, device):
+        self.sizes = dict(n_tokens_global=n_tokens_global, d_input=d_input, d_model=d_model, n_expts_act=n_expts_act,
+                          n_expts_tot=n_expts_tot, dtype=dtype, device=device)
+        self._is_initialized = True
+
+    def all_gather_routing(self, y_vals, y_indx, bm_store, T_local, rank):
+        """In-place all-gather of the routing outputs: rank r's rows are [r * T_local, (r+1) * T_local)."""
+        g = self.mesh.process_group
+        W = self.mesh.world_size
+        dist.all_gather_into_tensor(y_vals, y_vals[rank * T_local:(rank + 1) * T_local].clone(), group=g)
+        if y_indx is not None:
+            dist.all_gather_into_tensor(y_indx[:W * T_local], y_indx[rank * T_local:(rank + 1) * T_local].clone(), group=g)
+        words = bm_store.shape[0]
+        loc = bm_store[:, rank * T_local:(rank + 1) * T_local].t().contiguous()      # [T_local, words]
+        allr = torch.empty((W * T_local, words), dtype=bm_store.dtype, device=bm_store.device)
+        dist.all_gather_into_tensor(allr, loc, group=g)
+        bm_store[:, :W * T_local].copy_(allr.t())
+
+
+# ---------------------------------------------------------------------------------------------------------
+# exchange plan (pure index arithmetic on replicated metadata; device-agnostic so that it can be tested
+# with CPU ranks)
+# ---------------------------------------------------------------------------------------------------------
+
+def expert_owner(expt_assignment: ExptAssignment) -> torch.Tensor:
+    """[n_expts] int64: rank that owns each expert."""
+    return expt_assignment.expt_boolmask.to(torch.int64).argmax(dim=0)
+
+
+def make_exchange_plan(expt_indx, col_sorted_indx, owner, world_size, n_tokens_local):
+    """For every valid expert-sorted position p: source rank s(p) (home of its token) and destination rank
+    d(p) (owner of its expert).  Returns
+
+      order   [n_valid] positions p sorted by (s, d, p)   -- the order rows travel in, on both sides
+      counts  [W, W]    counts[s, d] = rows rank s sends to rank d
+      flat    [n_valid] flat (token * k + slot) index of order[i]
+
+    Rank s sends order[start(s, d) : +counts[s, d]] to d; rank d receives from s exactly that list.
+    """
+    k = expt_indx.shape[1]
+    valid = col_sorted_indx >= 0
+    p = torch.nonzero(valid).flatten()
+    flat = col_sorted_indx[p].long()
+    src = torch.div(flat, k * n_tokens_local, rounding_mode="floor")
+    dst = owner[expt_indx.reshape(-1)[flat].long()]
+    key = src * world_size + dst
+    perm = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=world_size * world_size).view(world_size, world_size)
+    return p[perm], counts, flat[perm]
+
+
+def _starts(counts):
+    c = counts.reshape(-1)
+    return (torch.cumsum(c, 0) - c).view_as(counts)
+
+
+def _rows_call(fn, src, indx, n, dst):
+    row_bytes = src.shape[1] * src.element_size()
+    _lib.check(fn(_lib.ptr(src), src.stride(0) * src.element_size(), _lib.ptr(indx), n, row_bytes, _lib.ptr(dst),
+                  dst.stride(0) * dst.element_size(), _lib.stream()), "moe_gather_rows/moe_scatter_rows")
+
+
+def convert_dp_to_ep(src, expt_assignment, expt_indx, gate_indx, symm_mem_pool: SymmetricMemoryPool,
+                     col_sorted_indx=None):
+    """src [T_local, d] (this rank's tokens) -> [T_global * k, d] in global expert-sorted order, filled at
+    the rows whose expert lives on this rank (other rows are left unwritten).  `gate_indx` is the global
+    row_sorted_indx (flat index -> sorted position); `col_sorted_indx` (its inverse) is derived when absent."""
+    lib = _lib.load()
+    mesh = symm_mem_pool.mesh
+    W, rank = mesh.world_size, mesh.local_rank
+    T_local, d = src.shape
+    T_global, k = expt_indx.shape
+    assert T_local * W <= T_global
+    dev = src.device
+    n = T_global * k
+    if col_sorted_indx is None:
+        col_sorted_indx = torch.full((n,), -1, dtype=torch.int64, device=dev)
+        g = gate_indx.reshape(-1).long()
+        ok = g >= 0
+        col_sorted_indx[g[ok]] = torch.nonzero(ok).flatten()
+    owner = expert_owner(expt_assignment)
+    order, counts, flat = make_exchange_plan(expt_indx, col_sorted_indx.reshape(-1), owner, W, T_local)
+    counts_h = counts.cpu()
+    starts_h = _starts(counts_h)
+    dst = torch.empty((n, d), dtype=src.dtype, device=dev)
+    send_lo = int(starts_h[rank, 0])
+    n_send = int(counts_h[rank].sum())
+    # pack: local token of each outgoing row, in (destination, position) order
+    tok_local = (torch.div(flat[send_lo:send_lo + n_send], k, rounding_mode="floor") - rank * T_local).to(torch.int32)
+    sendbuf = torch.empty((n_send, d), dtype=src.dtype, device=dev)
+    if n_send:
+        _rows_call(lib.moe_gather_rows, src, tok_local, n_send, sendbuf)
+    recv_counts = counts_h[:, rank].tolist()
+    n_recv = sum(recv_counts)
+    recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
+    if W > 1:
+        dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=recv_counts,
+                               input_split_sizes=counts_h[rank].tolist(), group=mesh.process_group)
+    else:
+        recvbuf = sendbuf
+    # unpack: received row i belongs at sorted position pos[i]
+    pos = torch.cat([order[int(starts_h[s, rank]):int(starts_h[s, rank]) + recv_counts[s]] for s in range(W)]) \
+        if n_recv else torch.empty(0, dtype=torch.int64, device=dev)
+    if n_recv:
+        _rows_call(lib.moe_scatter_rows, recvbuf, pos.to(torch.int32), n_recv, dst)
+    return dst
+
+
+def convert_ep_to_dp(src, expt_assignment, expt_indx, topk_indx, symm_mem_pool: SymmetricMemoryPool):
+    """src [T_global * k, d] in expert-sorted order (valid at this rank's experts) -> [T_local * k, d]: row
+    (t_local * k + slot) is the output of the expert in that slot.  `topk_indx` is the global
+    col_sorted_indx (sorted position -> flat index)."""
+    lib = _lib.load()
+    mesh = symm_mem_pool.mesh
+    W, rank = mesh.world_size, mesh.local_rank
+    n, d = src.shape
+    T_global, k = expt_indx.shape
+    T_local = T_global // W
+    dev = src.device
+    owner = expert_owner(expt_assignment)
+    order, counts, flat = make_exchange_plan(expt_indx, topk_indx.reshape(-1), owner, W, T_local)
+    counts_h = counts.cpu()
+    starts_h = _starts(counts_h)
+    # this rank (as expert owner d) returns to each home rank s the rows order[start(s, d) : +counts[s, d]]
+    send_counts = counts_h[:, rank].tolist()
+    n_send = sum(send_counts)
+    pos = torch.cat([order[int(starts_h[s, rank]):int(starts_h[s, rank]) + send_counts[s]] for s in range(W)]) \
+        if n_send else torch.empty(0, dtype=torch.int64, device=dev)
+    sendbuf = torch.empty((n_send, d), dtype=src.dtype, device=dev)
+    if n_send:
+        _rows_call(lib.moe_gather_rows, src, pos.to(torch.int32), n_send, sendbuf)
+    recv_counts = counts_h[rank].tolist()
+    n_recv = sum(recv_counts)
+    recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
+    if W > 1:
+        dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                               group=mesh.process_group)
+    else:
+        recvbuf = sendbuf
+    dst = torch.zeros((T_local * k, d), dtype=src.dtype, device=dev)
+    lo = int(starts_h[rank, 0])
+    where = (flat[lo:lo + n_recv] - rank * T_local * k).to(torch.int32)
+    if n_recv:
+        _rows_call(lib.moe_scatter_rows, recvbuf, where, n_recv, dst)
+    return dst

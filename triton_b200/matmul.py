@@ -1,0 +1,293 @@
+"""Ragged grouped GEMM with gather / scatter and fused epilogue (triton_kernels/matmul.py:245-766):
+
+    y[rows(e)] = act((x[gather(rows(e))] @ w[e] + bias[e] * betas) * out_alpha) * gammas
+
+`matmul` keeps the reference's signature and argument meaning.  The body validates, allocates the
+output through torch and makes one call into libmoe_b200 (`moe_grouped_gemm`), which picks the tcgen05
+kernel for bf16 activations x MXFP4 weights in the B200 tiled layouts and the SIMT kernel otherwise."""
+from dataclasses import dataclass
+from enum import Enum, auto
+from typing import Callable
+
+import torch
+
+from . import _lib
+from .matmul_details.opt_flags import (InapplicableConstraint, reset_opt_flags_constraints,  # noqa: F401
+                                       resolve_kernel_choice, scoped_opt_flags_constraints, set_idle_sms,
+                                       update_opt_flags_constraints)
+from .numerics import InFlexData, OutFlexData
+from .specialize import FnSpecs
+from .tensor import FP4, RaggedTensorMetadata, Tensor, convert_layout, wrap_torch_tensor
+from .tensor_details.layout import (B200MXScaleLayout, B200MXValueLayout, BlackwellMXScaleLayout,
+                                    BlackwellMXValueLayout, StridedLayout)
+
+
+@dataclass(frozen=True)
+class FusedActivation:
+    specs: FnSpecs = FnSpecs.default()
+    fn_args: tuple = tuple()
+
+
+@dataclass(frozen=True)
+class Epilogue:
+    specs: FnSpecs = FnSpecs.default()
+    fn_arg_values_matmul: tuple = tuple()
+    fn_arg_values_finalize: tuple = tuple()
+    effective_itemsize: float | None = None
+
+
+class FnName(Enum):
+    QUANTIZE_MXFP8 = auto()
+    QUANTIZE_MXFP4 = auto()
+    QUANTIZE_NVFP4 = auto()
+
+
+@dataclass(frozen=True)
+class FlexCtx:
+    lhs_data: InFlexData = InFlexData()
+    rhs_data: InFlexData = InFlexData()
+    out_data: OutFlexData = OutFlexData()
+    acc_data: InFlexData = InFlexData()
+
+
+@dataclass
+class PrecisionConfig:
+    max_num_imprecise_acc: int | None = None
+    allow_tf32: bool = True
+    flex_ctx: FlexCtx = FlexCtx()
+    acc_scale: float = 1.0
+    flexpoint_saturate_inf: bool = False
+    report_quantization_err_fn: Callable | None = None
+    a_mx_scale: torch.Tensor | Tensor | None = None
+    a_mx_tensor_scale: torch.Tensor | None = None
+    a_microblock_size: int | None = None
+    b_mx_scale: torch.Tensor | Tensor | None = None
+    b_mx_tensor_scale: torch.Tensor | None = None
+    b_microblock_size: int | None = None
+    c_mx_scale: torch.Tensor | Tensor | None = None
+    c_microblock_size: int | None = None
+    c_value_pack_factor: int = 1
+    out_dtype: torch.dtype | None = None
+    intermediate_out_dtype: torch.dtype | None = None
+    enforce_bitwise_invariance: bool = False
+
+
+def matmul_set_idle_sms(num_idle_sms):
+    set_idle_sms(num_idle_sms)
+
+
+_status_words = {}
+_scale_cache = {}
+
+
+def _status_word(device):
+    key = torch.device(device).index
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def matmul_check_status(device=None):
+    """Synchronise and raise if a bounded wait inside the tensor-core kernel expired since the last check."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _status_word(dev)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"moe_grouped_gemm: a pipeline wait timed out inside the tcgen05 kernel (code {code})")
+
+
+def _canonical_scale(b_scale: Tensor):
+    """[E, K/32, N] view of an MX scale tensor stored in the reference's Blackwell scale layout (unswizzled
+    once and remembered while the storage tensor is alive)."""
+    data = b_scale.storage.data
+    key = (data.data_ptr(), tuple(b_scale.shape))
+    hit = _scale_cache.get(key)
+    if hit is not None and hit[0]() is data:
+        return hit[1]
+    import weakref
+    canon = b_scale.storage.layout.make_transformation(list(b_scale.shape), False).unswizzle_data(data).contiguous()
+    _scale_cache[key] = (weakref.ref(data), canon)
+    return canon
+
+
+def matmul(a, b, bias,
+           a_ragged_metadata: RaggedTensorMetadata | None = None,
+           b_ragged_metadata: RaggedTensorMetadata | None = None,
+           gather_indx: torch.Tensor | None = None,
+           scatter_indx: torch.Tensor | None = None,
+           precision_config: PrecisionConfig | None = None,
+           betas: torch.Tensor | None = None,
+           gammas: torch.Tensor | None = None,
+           out_alpha: float | None = None,
+           c: torch.Tensor | None = None,
+           fused_comm=None,
+           fused_activation: FusedActivation | None = None,
+           epilogue: Epilogue | None = None,
+           c_acc_in: torch.Tensor | None = None):
+    """Y[idxs_y_m(e), :] = matmul(X[idxs_x_m(e), :], W[e, :, :]) for every expert e, with the epilogue above.
+
+    a: [M, K] activations (bf16 / fp16 / fp32), K contiguous.  b: [E, K, N] (or [K, N]) dense tensor of the
+    same dtype, or an FP4 `Tensor` / uint8 tensor packed along K together with
+    `precision_config.b_mx_scale` ([E, K/32, N] e8m0).  a_ragged_metadata splits the (gathered) rows into
+    one slice per expert.  gather_indx[m] is the row of `a` read for problem row m, scatter_indx[m] the row of
+    the output written (-1 drops it); betas / gammas are per problem row, in expert-sorted order.
+    """
+    if a.ndim == 3:
+        raise NotImplementedError("batched (3-D) activations are outside the MoE path")
+    if b_ragged_metadata is not None:
+        raise NotImplementedError("ragged-K (weight-gradient) matmul is outside the MoE path")
+    if fused_comm is not None:
+        raise NotImplementedError("fused_comm is not implemented")
+    if c_acc_in is not None:
+        raise NotImplementedError("c_acc_in is not implemented")
+    if precision_config is None:
+        precision_config = PrecisionConfig()
+    if fused_activation is None:
+        fused_activation = FusedActivation(FnSpecs.default(), tuple())
+    if epilogue is not None and epilogue.specs.name != "dflt":
+        raise NotImplementedError("quantising epilogues are not implemented")
+    pc = precision_config
+    if pc.a_mx_scale is not None or pc.c_mx_scale is not None:
+        raise NotImplementedError("microscaled activations / outputs are not implemented")
+    fc = pc.flex_ctx
+    if any(s is not None for s in (fc.lhs_data.scale, fc.rhs_data.scale, fc.out_data.expected_scale, fc.acc_data.scale)):
+        raise NotImplementedError("flexpoint scales are not implemented")
+    kernel_choice = resolve_kernel_choice()
+    if isinstance(a, Tensor):
+        a = a.storage.data
+    assert a.ndim == 2
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    lib = _lib.load()
+    dev = a.device
+    args = _lib.MoeGemmArgs()
+    keep = []                                           # temporaries that must outlive the launch call
+
+    # ---- weights --------------------------------------------------------------------------------------
+    b_scale = pc.b_mx_scale
+    if b_scale is not None:
+        assert pc.b_microblock_size in (None, 32), "only 32-element e8m0 micro-blocks are supported"
+        if not isinstance(b, Tensor):
+            assert b.dtype == torch.uint8, "MX weights must be packed e2m1 (uint8)"
+            b = wrap_torch_tensor(b, dtype=FP4)
+        if not isinstance(b_scale, Tensor):
+            b_scale = wrap_torch_tensor(b_scale)
+        assert b.dtype == FP4, "only MXFP4 weights are supported with b_mx_scale"
+        shape = list(b.shape)
+        if len(shape) == 2:
+            shape = [1] + shape
+        E, K, N = shape
+        vl, sl = b.storage.layout, b_scale.storage.layout
+        if isinstance(vl, B200MXValueLayout) != isinstance(sl, B200MXScaleLayout):
+            raise ValueError("B200 tiled weights need both B200MXValueLayout values and B200MXScaleLayout scales")
+        if isinstance(vl, B200MXValueLayout):
+            args.w_kind = _lib.MOE_W_MX4_B200
+            args.w, args.w_scale = b.storage.data.data_ptr(), b_scale.storage.data.data_ptr()
+        else:
+            wd = b.storage.data
+            if wd.ndim == 2:
+                wd = wd.unsqueeze(0)
+            if isinstance(vl, (StridedLayout, BlackwellMXValueLayout)):
+                assert wd.stride(-2) == 1, "MXFP4 weights must be packed and contiguous along K"
+            else:
+                raise NotImplementedError(f"weight value layout {vl} is not supported")
+            if isinstance(sl, StridedLayout):
+                sd = b_scale.storage.data
+                if sd.ndim == 2:
+                    sd = sd.unsqueeze(0)
+            elif isinstance(sl, BlackwellMXScaleLayout):
+                sd = _canonical_scale(b_scale)
+                if sd.ndim == 2:
+                    sd = sd.unsqueeze(0)
+            else:
+                raise NotImplementedError(f"weight scale layout {sl} is not supported")
+            assert tuple(sd.shape) == (E, K // 32, N), f"scale shape {tuple(sd.shape)} != {(E, K // 32, N)}"
+            keep += [wd, sd]
+            args.w_kind = _lib.MOE_W_MX4_CANONICAL
+            args.w, args.w_scale = wd.data_ptr(), sd.data_ptr()
+            args.w_stride_e, args.w_stride_k, args.w_stride_n = wd.stride(0), 1, wd.stride(2)
+            args.ws_stride_e, args.ws_stride_k, args.ws_stride_n = sd.stride(0), sd.stride(1), sd.stride(2)
+    else:
+        if isinstance(b, Tensor):
+            b = b.storage.data
+        assert b.dtype == a.dtype, "dense weights must have the activation dtype"
+        wd = b if b.ndim == 3 else b.unsqueeze(0)
+        E, K, N = wd.shape
+        keep.append(wd)
+        args.w_kind = _lib.MOE_W_DENSE
+        args.w = wd.data_ptr()
+        args.w_stride_e, args.w_stride_k, args.w_stride_n = wd.stride(0), wd.stride(1), wd.stride(2)
+    assert a.shape[-1] == K, f"inner dimensions differ: {a.shape[-1]} vs {K}"
+
+    # ---- shapes / output ------------------------------------------------------------------------------
+    M = a.shape[0] if gather_indx is None else gather_indx.shape[0]
+    if scatter_indx is not None:
+        assert scatter_indx.shape[0] == M, "scatter_indx must have one entry per problem row"
+    red_n = fused_activation.specs.reduction_n
+    act_name = fused_activation.specs.name
+    if act_name not in ("dflt", "swiglu"):
+        raise NotImplementedError(f"fused activation {act_name!r} is not implemented")
+    assert (act_name == "swiglu") == (red_n == 2), "swiglu halves N (reduction_n == 2)"
+    out_rows = M if scatter_indx is None else scatter_indx.shape[0]
+    out_dtype = pc.out_dtype or a.dtype
+    out_shape = (out_rows, N // red_n)
+    if c is None:
+        c = torch.empty(out_shape, dtype=out_dtype, device=dev)
+    else:
+        if c.ndim == 3 and c.shape[0] == 1:
+            c = c[0]
+        assert tuple(c.shape) == out_shape and c.stride(-1) == 1 and c.dtype == out_dtype
+    if M == 0 or N == 0:
+        return c
+    if a_ragged_metadata is None:
+        assert E == 1, "several weight matrices need a_ragged_metadata"
+
+    def i32(t):
+        if t is None:
+            return None
+        t = t if t.dtype == torch.int32 else t.to(torch.int32)
+        t = t if t.is_contiguous() else t.contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    def f32v(t):
+        if t is None:
+            return None
+        t = t if t.dtype == torch.float32 else t.float()
+        t = t if t.is_contiguous() else t.contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    args.x, args.x_dtype, args.ld_x, args.rows_x = a.data_ptr(), _lib.dtype_code(a.dtype), a.stride(0), a.shape[0]
+    args.E, args.K, args.N, args.M = E, K, N, M
+    if a_ragged_metadata is not None:
+        md = a_ragged_metadata
+        assert md.block_offs_data.stride(1) == 1 and md.block_schedule_data.stride(1) == 1
+        args.slice_sizes, args.slice_offs = md.slice_sizes.data_ptr(), md.slice_offs.data_ptr()
+        args.block_offs_16, args.block_sched_16 = md.block_offs_data.data_ptr(), md.block_schedule_data.data_ptr()
+        args.ld_block_offs, args.ld_block_sched = md.block_offs_data.stride(0), md.block_schedule_data.stride(0)
+    if bias is not None:
+        if bias.ndim == 1:
+            bias = bias.view(1, -1)
+        assert bias.shape[-1] == N and bias.stride(-1) == 1
+        args.bias, args.bias_dtype, args.ld_bias = bias.data_ptr(), _lib.dtype_code(bias.dtype), bias.stride(0)
+    args.gather_indx, args.scatter_indx = i32(gather_indx), i32(scatter_indx)
+    args.betas, args.gammas = f32v(betas), f32v(gammas)
+    if out_alpha is not None:
+        args.out_alpha, args.has_out_alpha = float(out_alpha), 1
+    if act_name == "swiglu":
+        alpha, limit = fused_activation.fn_args
+        args.activation, args.act_alpha = _lib.MOE_ACT_SWIGLU, float(alpha)
+        args.act_limit, args.act_has_limit = (float(limit), 1) if limit is not None else (0.0, 0)
+    args.y, args.y_dtype, args.ld_y = c.data_ptr(), _lib.dtype_code(c.dtype), c.stride(0)
+    args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05}[kernel_choice]
+    args.status = _status_word(dev).data_ptr()
+    st = lib.moe_grouped_gemm(args, _lib.stream())
+    if st == 3:
+        raise InapplicableConstraint(lib.moe_last_error().decode(errors="replace"))
+    _lib.check(st, "moe_grouped_gemm")
+    return c
+
+
+matmul_ogs = matmul          # the name this operator had in earlier releases of the reference
