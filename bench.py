@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T]
+
+A step is one MoE layer forward (routing -> fc1 + SwiGLU -> fc2 x routing weight -> k-way combine; with
+N > 1 ranks also the two expert-parallel all-to-all exchanges) over one batch of seeded synthetic input of
+the gpt-oss-120b layer shape: d_model 2880, d_ff 2880 (fused gate+up 5760), 128 experts, top-4, bf16
+activations N(0,1), MXFP4 weights from bf16 N(0,0.02), router logits fp32 N(0,1) plus a per-expert bias
+N(0,1) (skewed load), 16384 tokens per rank (weak scaling).  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the reference's torch implementation (oracle/) on the host
+cores of this box on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+D_MODEL, D_FF, N_EXPTS, TOP_K = 2880, 2880, 128, 4
+FLOP_PER_ROW_FC1 = 2 * D_MODEL * 2 * D_FF          # 33,177,600
+FLOP_PER_ROW_FC2 = 2 * D_FF * D_MODEL              # 16,588,800
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def workload_name(tokens_per_rank, n_gpus):
+    return (f"gpt-oss-120b MoE layer: d_model {D_MODEL}, fused gate+up {2 * D_FF}, E={N_EXPTS} top-{TOP_K}, "
+            f"{tokens_per_rank} tokens/rank, skewed router, bf16 x MXFP4, EP over {n_gpus} GPU(s)")
+
+
+# ---------------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle (a port of the reference's torch implementation) on a bounded sample
+# ---------------------------------------------------------------------------------------------------------
+CPU_SAMPLE_TOKENS, CPU_SAMPLE_EXPTS = 256, 8
+
+
+def cpu_sample_inputs(seed=0):
+    import oracle
+    g = torch.Generator().manual_seed(seed)
+    E, T = CPU_SAMPLE_EXPTS, CPU_SAMPLE_TOKENS
+    x = torch.randn(T, D_MODEL, generator=g).bfloat16()
+    logits = torch.randn(T, E, generator=g) + torch.randn(E, generator=g)
+    w1 = (torch.randn(E, D_MODEL, 2 * D_FF, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn(E, D_FF, D_MODEL, generator=g) * 0.02).bfloat16()
+    q1, s1 = oracle.downcast_to_mxfp_oracle(w1, 1)
+    q2, s2 = oracle.downcast_to_mxfp_oracle(w2, 1)
+    b1 = (torch.randn(E, 2 * D_FF, generator=g) * 0.01).bfloat16()
+    b2 = (torch.randn(E, D_MODEL, generator=g) * 0.01).bfloat16()
+    return x, logits, (q1, s1, b1, q2, s2, b2)
+
+
+def cpu_layer_step(x, logits, w):
+    """One layer the way the reference's torch path runs it: weights are dequantised inside every call
+    (matmul.py:772-817 is invoked by matmul_torch)."""
+    import oracle
+    q1, s1, b1, q2, s2, b2 = w
+    w1 = oracle.dequant_weight_oracle(q1, s1)
+    w2 = oracle.dequant_weight_oracle(q2, s2)
+    return oracle.moe_layer_oracle(x, logits, w1, b1, w2, b2, TOP_K, 1.702, 7.0)
+
+
+def cpu_sample_desc():
+    return (f"{CPU_SAMPLE_TOKENS} tokens, top-{TOP_K} over {CPU_SAMPLE_EXPTS} experts of the same shape "
+            f"(d_model {D_MODEL}, fused gate+up {2 * D_FF}), weights dequantised per call as the reference does")
+
+
+def run_cpu_baseline(steps, warmup):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, logits, w = cpu_sample_inputs()
+    for _ in range(warmup):
+        cpu_layer_step(x, logits, w)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_layer_step(x, logits, w)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return CPU_SAMPLE_TOKENS / dt, dt, cores
+
+
+def reference_arm(args, rank):
+    if rank != 0:
+        return
+    steps, warmup = min(args.steps, 10), min(args.warmup, 2)
+    v, dt, cores = run_cpu_baseline(steps, warmup)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(args.tokens, args.gpus), "timed": "CPU oracle on a bounded sample"},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_desc()},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def gemm_traffic_note():
+    """DRAM bytes per launch of the grouped-GEMM kernel from the committed ncu summary, if one exists."""
+    p = ROOT / "profiles" / "gemm_tc_traffic.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text())
+        except Exception:
+            return None
+    return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=16384, help="tokens per rank")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus != 1 or world != 1:
+            raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+
+    import torch.distributed as dist
+    import triton_b200 as tb
+    from triton_b200.moe import moe_layer_forward, moe_layer_forward_ep
+    from triton_b200.testing import make_synthetic_layer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    T = args.tokens
+    E_local = N_EXPTS // world
+    # every rank builds its own experts with a rank-dependent seed; router bias and tokens are seeded per rank
+    lw = make_synthetic_layer(E_local, D_MODEL, D_FF, dev, seed=1000 + rank)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn(T, D_MODEL, device=dev, generator=g).bfloat16()
+    gb = torch.Generator(device=dev).manual_seed(12345)
+    expert_bias = torch.randn(N_EXPTS, device=dev, generator=gb)
+    logits = torch.randn(T, N_EXPTS, device=dev, generator=g) + expert_bias
+    pool = assignment = None
+    if world > 1:
+        assignment = tb.make_expt_assignment(world, N_EXPTS, tb.make_expt_dict_uniform(world, N_EXPTS), dev)
+        pool = tb.SymmetricMemoryPool(tb.Mesh(dist.group.WORLD))
+        pool.initialize_matmul(T * world, D_MODEL, D_MODEL, TOP_K, N_EXPTS, torch.bfloat16, dev)
+
+    def step(xi, li, timer=None):
+        if world > 1:
+            return moe_layer_forward_ep(xi, li, lw, TOP_K, assignment, pool, gemm_timer=timer)
+        return moe_layer_forward(xi, li, lw, TOP_K, gemm_timer=timer)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        z = step(x, logits)
+    barrier()
+    tb.matmul_check_status()
+
+    # ---- timed region: K steps, inputs resident in HBM; the expert weights (1.69 GB / world) are far larger
+    # than the 126 MB L2 and are streamed once per step, so no separate L2 flush is needed -----------------
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        ev[0].record()
+        for _ in range(args.steps):
+            z = step(x, logits)
+        ev[1].record()
+        barrier()
+    elapsed_ms = ev[0].elapsed_time(ev[1])
+    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    tb.matmul_check_status()
+    ms_per_step = elapsed_ms / args.steps
+    value = T * world / (ms_per_step * 1e-3)
+
+    # ---- the dominant kernel, timed on its own stream position inside the same step --------------------
+    # (events around the two grouped-GEMM launches of each step; every other kernel of the step still runs)
+    class GemmTimer:
+        def __init__(self):
+            self.spans = []
+
+        def __call__(self):
+            return self
+
+        def __enter__(self):
+            self._e0 = torch.cuda.Event(enable_timing=True)
+            self._e0.record()
+
+        def __exit__(self, *a):
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.spans.append((self._e0, e1))
+            return False
+
+    gt = GemmTimer()
+    barrier()
+    for _ in range(args.steps):
+        z = step(x, logits, gt)
+    barrier()
+    gemm_ms = [sum(e0.elapsed_time(e1) for e0, e1 in gt.spans)]
+    n_gemm = [len(gt.spans)]
+    rows_local = T * world * TOP_K / world        # routed rows this rank multiplies (uniform expert ownership: average)
+    if world == 1:
+        rows_local = T * TOP_K
+    flop_per_step = rows_local * (FLOP_PER_ROW_FC1 + FLOP_PER_ROW_FC2)
+    gemm_ms_per_step = gemm_ms[0] / args.steps
+    achieved_tflops = flop_per_step / (gemm_ms_per_step * 1e-3) / 1e12
+    peaks = measured_peaks()
+    traffic = gemm_traffic_note()
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_tc_kernel (fc1 + fc2 launches of a step, bf16 kind::f16 after in-SM dequant)",
+        "achieved": achieved_tflops, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+        "frac": achieved_tflops / peaks["bf16_tflops_sustained"], "peak_source": f"{peaks['source']} bf16 cuBLAS, sustained",
+        "traffic": None if traffic is None else traffic.get("dram_bytes_per_step"),
+        "ms_per_step_in_kernel": gemm_ms_per_step, "launches_per_step": n_gemm[0] / args.steps,
+        "frac_of_inferred_mxfp4_peak": achieved_tflops / (4 * peaks["bf16_tflops_sustained"]),
+    }
+
+    # ---- end to end: host buffers in, host result out, through the public API ---------------------------
+    e2e = None
+    if not args.no_e2e:
+        xh = x.cpu().pin_memory()
+        lh = logits.cpu().pin_memory()
+        zh = torch.empty((T, D_MODEL), dtype=torch.bfloat16).pin_memory()
+        xd, ld = torch.empty_like(x), torch.empty_like(logits)
+
+        def e2e_step():
+            xd.copy_(xh, non_blocking=True)
+            ld.copy_(lh, non_blocking=True)
+            zz = step(xd, ld)
+            zh.copy_(zz, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        n_e2e = max(3, args.steps // 2)
+        ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev2[0].record()
+        for _ in range(n_e2e):
+            e2e_step()
+        ev2[1].record()
+        barrier()
+        t2 = torch.tensor([ev2[0].elapsed_time(ev2[1])], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        e2e = {"value": T * world / (float(t2.item()) / n_e2e * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": xh.numel() * 2 + lh.numel() * 4, "d2h_bytes_per_step": zh.numel() * 2,
+               "steps": n_e2e}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, dt, cores = run_cpu_baseline(3, 1)
+        cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_desc(),
+                        "s_per_step": dt}
+
+    launches_per_step = 8 if world == 1 else 13     # topk, 3 sort passes, ragged, 2 GEMMs, reduce (+ remap, 4 row moves)
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(T, world), "l2": "inputs larger than L2 (weights streamed once per step)",
+                       "tflops_per_step_algorithmic": flop_per_step * world / 1e12 if world > 1 else flop_per_step / 1e12},
+            "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

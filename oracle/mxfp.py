@@ -55,6 +55,10 @@ def downcast_to_mxfp_oracle(x: torch.Tensor, axis: int, rounding_mode: int = ROU
     src, axis = _as_f32_last(x, axis)
     L = src.shape[-1]
     assert L % 2 == 0
+    if src.numel() == 0:
+        lead = tuple(src.shape[:-1])
+        return (torch.empty(lead + (L // 2,), dtype=torch.uint8).transpose(axis, -1),
+                torch.empty(lead + ((L + MX_BLOCK - 1) // MX_BLOCK,), dtype=torch.uint8).transpose(axis, -1))
     pad = (-L) % MX_BLOCK
     a = src.numpy()
     lead = a.shape[:-1]
@@ -97,7 +101,7 @@ def upcast_from_mxfp_oracle(q: torch.Tensor, scale: torch.Tensor, dtype: torch.d
     vals[..., 0::2] = lut[qn & 0xF]
     vals[..., 1::2] = lut[qn >> 4]
     L = vals.shape[-1]
-    if L == 0:
+    if vals.size == 0:
         return torch.from_numpy(vals).to(dtype).transpose(axis, -1).contiguous()
     s = (sn.astype(np.uint32) << 23).view(np.float32)
     pad = (-L) % MX_BLOCK

@@ -1,0 +1,50 @@
+"""Standalone SwiGLU and the k-way combine (reduce) on the GPU against the oracle and the reference fixture."""
+import pytest
+import torch
+
+import oracle
+import triton_b200 as tb
+from triton_b200.swiglu import PrecisionConfig as SwigluPC
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M, N", [(1311, 4352), (7, 34), (256, 2880)])
+@pytest.mark.parametrize("limit", [1e-2, 10, None])
+def test_swiglu(M, N, limit, device):
+    # reference tests/test_swiglu.py:23-32
+    torch.manual_seed(0)
+    x = torch.randn(M, N, device=device).bfloat16()
+    y = tb.swiglu(x, 0.5, SwigluPC(limit))
+    ref = oracle.swiglu_oracle(x.cpu().float(), 0.5, limit).bfloat16()
+    oracle.assert_close_oracle(ref, y.cpu())
+
+
+def test_swiglu_and_reduce_against_reference_fixture(golden, device):
+    g = golden("gemm_small")
+    act = tb.swiglu(g["y_plain"].to(device), g["alpha"], SwigluPC(g["limit"]))
+    oracle.assert_close_oracle(g["act"], act.cpu())
+    red, _ = tb.reduce(g["yk"].to(device), 1, mask=g["mask"].to(device))
+    torch.testing.assert_close(red.cpu().float(), g["red"].float(), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("shape", [(25, 2, 48), (4096, 4, 2880), (3, 5, 7)])
+@pytest.mark.parametrize("dim", [0, 1, 2])
+@pytest.mark.parametrize("mask_mode", ["none", "row", "full"])
+def test_reduce(shape, dim, mask_mode, device):
+    # reference tests/test_reduce.py:41-121 (tolerance 1e-3)
+    if shape[0] > 1000 and dim != 1:
+        pytest.skip("large case is the combine only")
+    torch.manual_seed(0)
+    x = torch.randn(shape, device=device).bfloat16()
+    mask = None
+    if mask_mode == "row":
+        mshape = list(shape)
+        mshape[2] = 1
+        mask = (torch.rand(mshape, device=device) > 0.3).expand(shape)
+    elif mask_mode == "full":
+        mask = (torch.rand(shape, device=device) > 0.3).to(torch.int32)
+    scale = torch.rand(shape[0], shape[1], 1, device=device) if mask_mode != "full" else None
+    y, _ = tb.reduce(x, dim, mask=mask, scale=scale)
+    ref = oracle.reduce_oracle(x.cpu(), dim, None if mask is None else mask.cpu(), None if scale is None else scale.cpu())
+    torch.testing.assert_close(y.cpu().float(), ref.float(), atol=1e-2, rtol=1e-2)

@@ -1,0 +1,116 @@
+"""The MoE layer as the reference composes it from its operators
+(python/triton_kernels/tests/test_distributed.py:213-247, bench/bench_mlp.py:60-96):
+
+    routing -> [dispatch] -> fc1 (+bias, SwiGLU fused) -> fc2 (+bias, x routing weight) -> [combine exchange]
+            -> k-way reduce
+
+`MoeLayerWeights` holds MXFP4 expert weights already in the B200 tiled layouts."""
+from dataclasses import dataclass
+
+import torch
+
+from .matmul import FusedActivation, PrecisionConfig, matmul
+from .numerics_details.mxfp import downcast_to_mxfp
+from .reduce import reduce
+from .routing import routing
+from .specialize import FnSpecs
+from .swiglu import swiglu_fn
+from .tensor import (FP4, Tensor, convert_layout, make_ragged_tensor_metadata, remap_ragged_tensor_metadata,
+                     wrap_torch_tensor)
+from .tensor_details.layout import make_default_matmul_mxfp4_w_layout, make_default_matmul_mxfp4_w_scale_layout
+from .topk import topk
+
+
+@dataclass
+class MoeLayerWeights:
+    w1: Tensor                 # FP4 [E, d_model, 2 * d_ff] (gate / linear columns interleaved)
+    w1_scale: Tensor
+    b1: torch.Tensor           # [E, 2 * d_ff]
+    w2: Tensor                 # FP4 [E, d_ff, d_model]
+    w2_scale: Tensor
+    b2: torch.Tensor           # [E, d_model]
+    alpha: float = 1.702
+    limit: float | None = 7.0
+    # canonical copies (packed along K), kept only when asked for (tests)
+    w1_q: torch.Tensor | None = None
+    w1_s: torch.Tensor | None = None
+    w2_q: torch.Tensor | None = None
+    w2_s: torch.Tensor | None = None
+
+    @property
+    def n_expts(self):
+        return self.b1.shape[0]
+
+    def weight_bytes(self):
+        return sum(t.storage.data.numel() for t in (self.w1, self.w1_scale, self.w2, self.w2_scale)) + \
+            self.b1.numel() * self.b1.element_size() + self.b2.numel() * self.b2.element_size()
+
+
+def quantize_expert_weights(w: torch.Tensor):
+    """bf16 [E, K, N] -> (FP4 values, e8m0 scales) quantised along K, in the default B200 layouts, plus the
+    canonical tensors they were made from."""
+    q, s = downcast_to_mxfp(w, torch.uint8, axis=1)
+    tq = convert_layout(wrap_torch_tensor(q, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=-2))
+    ts = convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=-2))
+    return tq, ts, q, s
+
+
+class _NoTimer:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def _span(timer):
+    """`timer` (optional) is a context-manager factory: timer() brackets each grouped-GEMM launch."""
+    return timer() if timer is not None else _NoTimer()
+
+
+def _activation(lw):
+    return FusedActivation(FnSpecs("swiglu", swiglu_fn, ("alpha", "limit"), reduction_n=2), (lw.alpha, lw.limit))
+
+
+def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
+    """x [T, d_model] bf16, logits [T, E] -> [T, d_model]: sum over the k selected experts of
+    softmax-weight * (SwiGLU(x W1 + b1) W2 + b2)."""
+    T = x.shape[0]
+    ragged, gather_idx, scatter_idx, sparse = routing(logits, k)
+    gammas = sparse.vals.reshape(-1)[scatter_idx.long()]               # routing weights in expert-sorted order
+    pc1 = PrecisionConfig(b_mx_scale=lw.w1_scale, b_microblock_size=32)
+    pc2 = PrecisionConfig(b_mx_scale=lw.w2_scale, b_microblock_size=32)
+    with _span(gemm_timer):
+        h = matmul(x, lw.w1, lw.b1, ragged, gather_indx=gather_idx, precision_config=pc1,
+                   fused_activation=_activation(lw))
+    with _span(gemm_timer):
+        y = matmul(h, lw.w2, lw.b2, ragged, scatter_indx=scatter_idx, precision_config=pc2, gammas=gammas)
+    z, _ = reduce(y.view(T, k, -1), dim=1)
+    return z
+
+
+def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: int, expt_assignment, pool,
+                         gemm_timer=None):
+    """Expert-parallel layer: tokens are sharded over ranks (x_local [T_local, d_model]), experts over ranks
+    (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered, token
+    rows travel to the expert owners and back by one NCCL all-to-all each way."""
+    from .distributed import convert_dp_to_ep, convert_ep_to_dp
+    rank = pool.mesh.local_rank
+    sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
+    md = sparse.mask_metadata
+    n_entries = md.row_sorted_indx.shape[0]
+    meta_global = make_ragged_tensor_metadata(md.col_sum, n_entries)
+    x_ep = convert_dp_to_ep(x_local, expt_assignment, sparse.indx, md.row_sorted_indx, pool,
+                            col_sorted_indx=md.col_sorted_indx)
+    meta_local = remap_ragged_tensor_metadata(meta_global, expt_assignment.expt_map[rank, :])
+    gammas = sparse.vals.reshape(-1)[md.col_sorted_indx.long().clamp_min(0)]
+    pc1 = PrecisionConfig(b_mx_scale=lw_local.w1_scale, b_microblock_size=32)
+    pc2 = PrecisionConfig(b_mx_scale=lw_local.w2_scale, b_microblock_size=32)
+    with _span(gemm_timer):
+        h = matmul(x_ep, lw_local.w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
+                   fused_activation=_activation(lw_local))
+    with _span(gemm_timer):
+        y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas)
+    y_dp = convert_ep_to_dp(y, expt_assignment, sparse.indx, md.col_sorted_indx, pool)
+    z, _ = reduce(y_dp.view(x_local.shape[0], k, -1), dim=1)
+    return z

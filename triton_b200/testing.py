@@ -41,3 +41,33 @@ def assert_close(ref, tri, maxtol=None, rmstol=None, description="--", verbose=T
         print(f"{description} RMS relative error = {rms_err} (threshold = {rmstol})")
     assert max_err <= maxtol
     assert rms_err <= rmstol
+
+
+def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=False, chunk=8):
+    """Random-init MoE expert weights of a gpt-oss-shaped layer: bf16 N(0, 0.02) quantised to MXFP4 along K,
+    bias bf16 N(0, 0.01).  Experts are generated and quantised `chunk` at a time to bound peak memory."""
+    from .moe import MoeLayerWeights
+    from .numerics_details.mxfp import downcast_to_mxfp
+    from .tensor import FP4, convert_layout, wrap_torch_tensor
+    from .tensor_details.layout import make_default_matmul_mxfp4_w_layout, make_default_matmul_mxfp4_w_scale_layout
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def quant(K, N):
+        qs, ss = [], []
+        for e0 in range(0, n_expts, chunk):
+            n = min(chunk, n_expts - e0)
+            w = (torch.randn(n, K, N, device=device, generator=g) * 0.02).bfloat16()
+            q, s = downcast_to_mxfp(w, torch.uint8, axis=1)
+            qs.append(q)
+            ss.append(s)
+        q = torch.cat([t.transpose(1, 2) for t in qs]).transpose(1, 2)          # keeps K contiguous
+        s = torch.cat([t.transpose(1, 2) for t in ss]).transpose(1, 2)
+        tq = convert_layout(wrap_torch_tensor(q, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=-2))
+        ts = convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=-2))
+        return tq, ts, (q if keep_canonical else None), (s if keep_canonical else None)
+
+    w1, s1, q1, c1 = quant(d_model, 2 * d_ff)
+    w2, s2, q2, c2 = quant(d_ff, d_model)
+    b1 = (torch.randn(n_expts, 2 * d_ff, device=device, generator=g) * 0.01).bfloat16()
+    b2 = (torch.randn(n_expts, d_model, device=device, generator=g) * 0.01).bfloat16()
+    return MoeLayerWeights(w1, s1, b1, w2, s2, b2, w1_q=q1, w1_s=c1, w2_q=q2, w2_s=c2)
