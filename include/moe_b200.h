@@ -78,6 +78,24 @@ int moe_bitmatrix_metadata(const int16_t* indx, int64_t ld_indx, int64_t T, int 
                            const int32_t* n_rows_dev, int32_t* col_sum, int32_t* col_sorted,
                            int32_t* row_sorted, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  The same computation as moe_bitmatrix_metadata for callers that cannot
+ * supply a workspace because they cannot allocate device memory when they call: a serving process that gave
+ * all device memory to its own pools at start-up, or a latency-critical section where cudaMalloc, which
+ * synchronises the device, is not acceptable.  The scratch is a fixed 1 MiB array inside the library
+ * (moe_bitmatrix_metadata_noalloc_capacity() bytes, held by every GPU that loads the library until the
+ * process exits); inputs and outputs are still the caller's.  It serves problems with
+ * (ceil(T / 256) * E + E) * 4 <= capacity, e.g. T = 65536 tokens with E = 128 experts, or 8192 tokens with
+ * E = 4096, and returns MOE_ERR_ARG with a message for anything larger.  It calls no cudaMalloc / cudaFree or
+ * other allocating routine.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before any stream capture begins.
+ * All calls share the one array, and it keeps whatever the previous call left (nothing in it needs to start
+ * at zero): two calls whose kernels may overlap on the GPU -- different streams, no ordering between them --
+ * race on it and give wrong results; order them on one stream or with events.                           */
+size_t moe_bitmatrix_metadata_noalloc_capacity(void);
+int moe_bitmatrix_metadata_noalloc(const int16_t* indx, int64_t ld_indx, int64_t T, int E, int k,
+                                   const int32_t* n_rows_dev, int32_t* col_sum, int32_t* col_sorted,
+                                   int32_t* row_sorted, void* stream);
+
 /* Replaces tensor_details/ragged_tensor.py:183-210 (make_ragged_tensor_metadata: memset + compute
  * kernels).  block_offs is [4][ld_block_offs] (block sizes 16,32,64,128), block_sched is
  * [4][ld_sched] with n_sched valid columns each (= max_n_blocks), padded with -1.                  */

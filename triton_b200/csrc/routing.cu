@@ -437,3 +437,48 @@ extern "C" __attribute__((visibility("default"))) int moe_ragged_metadata_remap(
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// moe_bitmatrix_metadata_noalloc: the same histogram + expert-major sort for hosts that cannot give this
+// library a scratch buffer because they cannot allocate one at that point -- a serving process that handed
+// all device memory to its own pools at start-up, or a latency-critical section in which cudaMalloc (which
+// synchronises the device) is not acceptable.  The three sort passes need nb * E + E ints of scratch
+// (nb = ceil(T / 256)); here that scratch is a fixed array inside the library image.
+//
+// Cost: every GPU that loads libmoe_b200.so carries kNoAllocScratchBytes (1 MiB) of device memory until the
+// process exits, whether or not this entry point is ever called.
+static __device__ __align__(256) int32_t g_bm_scratch[(1 << 20) / sizeof(int32_t)];
+constexpr size_t kNoAllocScratchBytes = sizeof(int32_t) * ((1 << 20) / sizeof(int32_t));
+
+// Device address of g_bm_scratch, looked up once per device.  In host code the name g_bm_scratch is only a
+// handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress with that device current.
+static void* g_bm_scratch_addr[64] = {nullptr};
+
+extern "C" __attribute__((visibility("default"))) size_t moe_bitmatrix_metadata_noalloc_capacity(void) {
+  return kNoAllocScratchBytes;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_bitmatrix_metadata_noalloc(
+    const int16_t* indx, int64_t ld_indx, int64_t T, int E, int k, const int32_t* n_rows_dev, int32_t* col_sum,
+    int32_t* col_sorted, int32_t* row_sorted, void* stream) {
+  MOE_CHECK_ARG(T >= 0 && E > 0 && k > 0, "moe_bitmatrix_metadata_noalloc: bad extents T=%lld E=%d k=%d", (long long)T, E, k);
+  const size_t need = moe_bitmatrix_metadata_workspace(T, E, k);
+  MOE_CHECK_ARG(need <= kNoAllocScratchBytes,
+                "moe_bitmatrix_metadata_noalloc: T=%lld tokens x E=%d experts needs %zu bytes of scratch, the built-in "
+                "scratch holds %zu (ceil(T/256) * E + E ints must fit); use moe_bitmatrix_metadata with a caller buffer",
+                (long long)T, E, need, kNoAllocScratchBytes);
+  int dev = -1;
+  MOE_CHECK_CUDA(cudaGetDevice(&dev));
+  MOE_CHECK_ARG(dev >= 0 && dev < 64, "moe_bitmatrix_metadata_noalloc: device index %d out of range", dev);
+  if (g_bm_scratch_addr[dev] == nullptr) {
+    // first call on this device: resolve the symbol (not an allocation; the array is part of the module image)
+    void* p = nullptr;
+    MOE_CHECK_CUDA(cudaGetSymbolAddress(&p, g_bm_scratch));
+    MOE_CHECK_ARG(p != nullptr, "moe_bitmatrix_metadata_noalloc: cudaGetSymbolAddress returned NULL");
+    g_bm_scratch_addr[dev] = p;
+  }
+  // Nothing in the scratch has to start at zero: pass 1 writes every partial[block][expert] and pass 2 every
+  // col_offs[expert] before they are read.  col_sum, which must, is cleared by the call below.
+  return moe_bitmatrix_metadata(indx, ld_indx, T, E, k, n_rows_dev, col_sum, col_sorted, row_sorted,
+                                g_bm_scratch_addr[dev], kNoAllocScratchBytes, stream);
+}
