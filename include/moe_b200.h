@@ -127,8 +127,8 @@ int moe_reduce(const void* x, int dtype, int64_t R, int64_t S0, int64_t S1,
  * One-time re-layout of canonical MXFP4 weights (the output of moe_downcast_mxfp4 on w[E,K,N] along
  * K: values [E][N][K/2], scales [E][N][K/32]) into the tile-contiguous layout the tensor-core kernel
  * streams with bulk copies: tiles of 128 n x 128 k, ordered [E][n_tile][k_tile]; a value tile is
- * 128 rows x 64 bytes with the nibbles of every 32-bit word reordered (k0,k2,k4,k6,k1,k3,k5,k7), a
- * scale tile is 128 rows x 4 bytes; K and N are zero-padded to multiples of 128.  Plays the role of
+ * [4 scale groups][128 rows][16 bytes] with the nibbles of every 32-bit word reordered
+ * (k0,k2,k4,k6,k1,k3,k5,k7), a scale tile is 128 rows x 4 bytes; K and N are zero-padded to multiples of 128.  Plays the role of
  * convert_layout(..., BlackwellMX4ValueShuffledLayout / BlackwellMXScaleLayout)
  * (tensor_details/layout_details/blackwell_value_shuffled.py:203-261, blackwell_scale.py:505-533).
  * Either half (values or scales) may be skipped by passing NULL for both its input and output.    */

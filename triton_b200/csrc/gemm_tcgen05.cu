@@ -7,13 +7,15 @@
 // arithmetic as the reference, which upcasts the weight tile in registers before its bf16 MMA
 // (triton_kernels matmul_details/opt_flags_details/opt_flags_nvidia.py:154-161).
 //
-// One persistent CTA per SM, 12 warps, specialised:
-//   warp 0      tensor-memory allocation, MMA issue (one elected lane)
-//   warp 1      weight producer: one bulk copy per value tile (8 KB) and scale tile (512 B) and k step
-//   warps 2-3   activation loader: 16-byte cp.async of (gathered) token rows into the 128B-swizzled
-//               K-major operand tile, zero fill for missing rows and the K tail
-//   warps 4-7   dequantiser: packed e2m1 + e8m0 -> bf16, written into the swizzled K-major B tile
-//   warps 8-11  epilogue: tcgen05.ld of the accumulator, bias*beta, out_alpha, SwiGLU, gamma, cast, store
+// One persistent CTA per SM, 18 warps, specialised:
+//   warp 0       tensor-memory allocation, MMA issue (one elected lane)
+//   warp 1       weight producer: one bulk copy per value tile (8 KB) and scale tile (512 B) and k step
+//   warps 2-5    activation loader: 16-byte cp.async of (gathered) token rows into the 128B-swizzled
+//                K-major operand tile, zero fill for missing rows and the K tail; the source offsets of a
+//                thread's 16 rows stay in registers for the whole tile
+//   warps 6-13   dequantiser: packed e2m1 + e8m0 -> bf16, written into the swizzled K-major B tile; a thread
+//                takes the 32 k values of one (row, scale group) at a time: one 16-byte load, one scale byte
+//   warps 14-17  epilogue: tcgen05.ld of the accumulator, bias*beta, out_alpha, SwiGLU, gamma, cast, store
 // Rings: raw weights (producer -> dequantiser), A and B operand stages (-> MMA), two accumulator
 // buffers (MMA -> epilogue).  Every mbarrier wait is bounded: when a wait expires the CTA raises a
 // shared abort flag, writes the caller's status word, drains its copies, frees tensor memory and
@@ -26,7 +28,9 @@ constexpr int BLOCK_M = 128;          // token rows per tile  (MMA M)
 constexpr int BLOCK_N = 128;          // weight rows per tile (MMA N)
 constexpr int BLOCK_K = 128;          // k per pipeline stage: two 64-wide swizzle sub-tiles
 constexpr int STAGES = 3;
-constexpr int NUM_THREADS = 384;
+constexpr int NUM_THREADS = 576;
+constexpr int LOADER_WARPS = 4, DEQUANT_WARPS = 8;
+constexpr int WARP_LOADER0 = 2, WARP_DEQ0 = 6, WARP_EPI0 = 14;
 constexpr int SUBTILE_BYTES = 128 * 128;                 // 128 rows x 128 bytes (64 bf16)
 constexpr int A_STAGE_BYTES = 2 * SUBTILE_BYTES;         // 32 KB
 constexpr int B_STAGE_BYTES = 2 * SUBTILE_BYTES;         // 32 KB
@@ -38,16 +42,14 @@ constexpr int OFF_A = 0;
 constexpr int OFF_B = OFF_A + STAGES * A_STAGE_BYTES;
 constexpr int OFF_RAWV = OFF_B + STAGES * B_STAGE_BYTES;
 constexpr int OFF_RAWS = OFF_RAWV + STAGES * RAWV_BYTES;
-constexpr int OFF_SRC = OFF_RAWS + STAGES * RAWS_BYTES;          // int64 source rows, [2 loader warps][64]
-constexpr int OFF_BIAS = OFF_SRC + BLOCK_M * 8;                  // float bias, [4 epilogue warps][128]
+constexpr int OFF_BIAS = OFF_RAWS + STAGES * RAWS_BYTES;         // float bias, [4 epilogue warps][128]
 constexpr int OFF_BAR = OFF_BIAS + 4 * BLOCK_N * 4;              // mbarriers
 constexpr int NUM_BARS = 5 * STAGES + 4 + 1;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                 // tmem base, abort flag
 constexpr int SMEM_BYTES = OFF_MISC + 16;
 constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;                    // slack for 1024-byte alignment
 
-constexpr uint32_t WAIT_TIGHT_POLLS = 128;
-constexpr uint32_t WAIT_MAX_POLLS = 1u << 24;                    // ~1 s with the back-off below
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;      // a wait that lasts 2 s aborts the CTA
 
 // ---- PTX wrappers -------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -72,6 +74,23 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait parks the thread in hardware until the phase completes or an implementation-defined time passes
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 struct Ctl {
   volatile int* abort_flag;   // shared memory
@@ -80,16 +99,15 @@ struct Ctl {
 
 // Bounded wait.  Returns false when the CTA is aborting (this wait expired, or another one did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctl& ctl, int code) {
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i >= WAIT_TIGHT_POLLS) {
-      __nanosleep(32);
-      if (*ctl.abort_flag) return false;
-      if (i >= WAIT_MAX_POLLS) {
-        *ctl.abort_flag = 1;
-        if (ctl.status) atomicExch(ctl.status, code);
-        return false;
-      }
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (*ctl.abort_flag) return false;
+    if (global_ns() - t0 > WAIT_LIMIT_NS) {
+      *ctl.abort_flag = 1;
+      if (ctl.status) atomicExch(ctl.status, code);
+      return false;
     }
   }
 }
@@ -162,46 +180,43 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-__device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t sb) {
-  uint32_t v[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t t = (w >> (4 * i)) & 0x000F000Fu;
-    v[i] = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
-  }
-  if (sb <= 128u) {
-    const uint32_t c = sb ? ((sb + 126u) << 7) : 0u;
-    const uint32_t c2 = c | (c << 16);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = bf16x2_mul(v[i], c2);
-  } else {
-    const uint32_t s2 = (sb << 7) | (sb << 23);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = bf16x2_mul(bf16x2_mul(v[i], 0x7E807E80u /* 2^126 */), s2);
-  }
-  return make_uint4(v[0], v[1], v[2], v[3]);
+// pair i of word w -> bf16x2 bit pattern of (value * 2^-126): magnitude to bits 8:6 / 24:22, sign to 15 / 31
+template <int I> __device__ __forceinline__ uint32_t e2m1_pair(uint32_t w) {
+  const uint32_t mag = (I < 2 ? (w << (6 - 4 * I)) : (w >> (4 * I - 6))) & 0x01C001C0u;
+  const uint32_t sgn = (w << (12 - 4 * I)) & 0x80008000u;
+  return mag | sgn;
+}
+__device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t c2) {
+  return make_uint4(bf16x2_mul(e2m1_pair<0>(w), c2), bf16x2_mul(e2m1_pair<1>(w), c2),
+                    bf16x2_mul(e2m1_pair<2>(w), c2), bf16x2_mul(e2m1_pair<3>(w), c2));
+}
+__device__ __forceinline__ uint4 dequant8_wide(uint32_t w, uint32_t sb) {      // scale bytes above 128
+  const uint32_t s2 = (sb << 7) | (sb << 23);
+  const uint32_t k = 0x7E807E80u;                                               // 2^126
+  return make_uint4(bf16x2_mul(bf16x2_mul(e2m1_pair<0>(w), k), s2), bf16x2_mul(bf16x2_mul(e2m1_pair<1>(w), k), s2),
+                    bf16x2_mul(bf16x2_mul(e2m1_pair<2>(w), k), s2), bf16x2_mul(bf16x2_mul(e2m1_pair<3>(w), k), s2));
 }
 
-template <typename TY> __device__ __forceinline__ void store_out(TY* dst, const float* v, int n, bool vec_ok);
-template <>
-__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* dst, const float* v, int n, bool vec_ok) {
-  if (vec_ok) {
-    for (int j = 0; j < n; j += 8) {
-      __nv_bfloat162 h[4];
+// store N consecutive outputs of one row; `vec` selects 16-byte stores, `n_valid` bounds the scalar path
+template <typename TY, int N> __device__ __forceinline__ void store_out(TY* dst, const float (&v)[N], bool vec, int n_valid) {
+  if (vec) {
+    if constexpr (sizeof(TY) == 2) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
-      *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(h);
+      for (int j = 0; j < N; j += 8) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[j + 2 * q], v[j + 2 * q + 1]);
+        *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(h);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     }
   } else {
-    for (int j = 0; j < n; ++j) dst[j] = __float2bfloat16_rn(v[j]);
-  }
-}
-template <>
-__device__ __forceinline__ void store_out<float>(float* dst, const float* v, int n, bool vec_ok) {
-  if (vec_ok) {
-    for (int j = 0; j < n; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
-    for (int j = 0; j < n; ++j) dst[j] = v[j];
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (j < n_valid) dst[j] = from_f32<TY>(v[j]);
   }
 }
 
@@ -232,9 +247,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(BAR_RAW_FULL(s), 1);
-      mbar_init(BAR_RAW_EMPTY(s), 4);
-      mbar_init(BAR_A_FULL(s), 2);
-      mbar_init(BAR_B_FULL(s), 4);
+      mbar_init(BAR_RAW_EMPTY(s), DEQUANT_WARPS);
+      mbar_init(BAR_A_FULL(s), LOADER_WARPS);
+      mbar_init(BAR_B_FULL(s), DEQUANT_WARPS);
       mbar_init(BAR_AB_EMPTY(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -327,18 +342,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       }
     }
     __syncwarp();
-  } else if (warp < 4) {
+  } else if (warp < WARP_DEQ0) {
     // ================================= activation loader ==============================================
-    // Each of the two loader warps owns 64 rows of the tile and keeps their source rows in a private
-    // shared array, so the only synchronisation inside the role is __syncwarp (a CTA-level named barrier
-    // could be left waiting by a warp that aborted).
-    const int lw = warp - 2;                        // 0..1
-    const int cc = lane & 15;                       // 16-byte chunk of the 256-byte stage row
-    const int hh = lane >> 4;                       // rows 2 lw + hh + 4 i, i = 0..31
-    int64_t* s_src = reinterpret_cast<int64_t*>(smem + OFF_SRC) + lw * 64;
-    const __nv_bfloat16* X = (const __nv_bfloat16*)p.x;
+    // 128 threads move the 128 x 256-byte stage: thread t owns 16-byte chunk (t & 15) of rows (t >> 4) + 8 i.
+    // The source of each row (byte offset / 16 into x, or none) is kept in registers for the whole tile.
+    const int t = threadIdx.x - WARP_LOADER0 * 32;  // 0..127
+    const int cc = t & 15;
+    const int rbase = t >> 4;
+    const uint8_t* Xb = (const uint8_t*)p.x;
     const uint32_t a_off = (uint32_t)((cc >> 3) * SUBTILE_BYTES);
     const int c8 = cc & 7;
+    const uint32_t ld16 = (uint32_t)(p.ld_x >> 3);  // row pitch in 16-byte units
+    uint32_t dst_off[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int r = rbase + 8 * i;
+      dst_off[i] = a_off + (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4));
+    }
     uint32_t it = 0, it_sig = 0;
     bool ok = true;
     auto signal_oldest = [&]() {
@@ -350,19 +370,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int e; int64_t row0; int rows;
       if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
-      __syncwarp();                                 // the previous tile's source rows are no longer read
+      uint32_t src16[16];                           // 0xFFFFFFFF: no source row
 #pragma unroll
-      for (int h2 = 0; h2 < 2; ++h2) {
-        const int r = 2 * lw + h2 + 4 * lane;       // slot h2 * 32 + lane
+      for (int i = 0; i < 16; ++i) {
+        const int r = rbase + 8 * i;
         int64_t src = -1;
         if (r < rows) {
           const int64_t m = row0 + r;
           src = p.gather_indx ? (int64_t)p.gather_indx[m] : m;
           if (src >= p.rows_x) src = -1;
         }
-        s_src[h2 * 32 + lane] = src;
+        src16[i] = src < 0 ? 0xFFFFFFFFu : (uint32_t)src * ld16;
       }
-      __syncwarp();
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % STAGES;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_AB_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 301));
@@ -370,14 +389,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         const int k = kt * BLOCK_K + cc * 8;
         const int kleft = p.K - k;
         const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
-        const uint32_t stage = sbase + OFF_A + s * A_STAGE_BYTES + a_off;
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-          const int r = 2 * lw + hh + 4 * i;
-          const int64_t src = s_src[hh * 32 + i];
-          const bool live = src >= 0 && kbytes;
-          const void* g = live ? (const void*)(X + src * p.ld_x + k) : (const void*)X;
-          cp_async16(stage + (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4)), g, live ? kbytes : 0u);
+        const uint32_t stage = sbase + OFF_A + s * A_STAGE_BYTES;
+        const uint32_t kc16 = (uint32_t)(k >> 3);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool live = src16[i] != 0xFFFFFFFFu && kbytes;
+          const uint8_t* g = live ? Xb + ((uint64_t)(src16[i] + kc16) << 4) : Xb;
+          cp_async16(stage + dst_off[i], g, live ? kbytes : 0u);
         }
         cp_async_commit();
         if (it - it_sig >= 2) {
@@ -388,13 +406,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     }
     cp_async_wait<0>();
     while (it_sig < it) signal_oldest();
-  } else if (warp < 8) {
+  } else if (warp < WARP_EPI0) {
     // ================================= dequantiser ======================================================
-    const int t = threadIdx.x - 128;                // 0..127
-    const int j = t & 15;                           // 32-bit word of the 64-byte packed row (8 k values)
-    const int rb = t >> 4;                          // rows rb + 8 i
-    const uint32_t b_off = (uint32_t)((j >> 3) * SUBTILE_BYTES);
-    const int c8 = j & 7;
+    // 256 threads; lane = (scale group g) * 8 + (row within 8): a thread converts the 32 k values of one
+    // (row, group) -- one 16-byte load, one scale byte, four 16-byte swizzled stores -- for rows
+    // 8 * dequant_warp + (lane & 7) and that + 64.
+    const int dw = warp - WARP_DEQ0;                // 0..7
+    const int g = lane >> 3;                        // 32-k group of the 128-k stage
+    const int rl = dw * 8 + (lane & 7);
+    const uint32_t b_sub = (uint32_t)((g >> 1) * SUBTILE_BYTES);
+    const int cbase = (g & 1) * 4;                  // first 16-byte chunk of the group inside the 128-byte row
     uint32_t it = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -406,14 +427,33 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         ok = __all_sync(0xFFFFFFFFu,
                         mbar_wait(BAR_RAW_FULL(s), ph, ctl, 401) && mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
         if (!ok) break;
-        const uint32_t* rv = reinterpret_cast<const uint32_t*>(smem + OFF_RAWV + s * RAWV_BYTES);
-        const uint8_t* rs = smem + OFF_RAWS + s * RAWS_BYTES;
-        uint8_t* bst = smem + OFF_B + s * B_STAGE_BYTES + b_off;
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int r = rb + 8 * i;
-          const uint4 o = dequant8(rv[r * 16 + j], rs[r * 4 + (j >> 2)]);
-          *reinterpret_cast<uint4*>(bst + r * 128 + ((c8 ^ (r & 7)) << 4)) = o;
+        const uint4* rv = reinterpret_cast<const uint4*>(smem + OFF_RAWV + s * RAWV_BYTES) + g * BLOCK_N;
+        const uint8_t* rs = smem + OFF_RAWS + s * RAWS_BYTES + g;
+        uint8_t* bst = smem + OFF_B + s * B_STAGE_BYTES + b_sub;
+        uint4 raw[2];
+        uint32_t sb[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          raw[i] = rv[rl + 64 * i];
+          sb[i] = rs[(rl + 64 * i) * 4];
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int r = rl + 64 * i;
+          uint8_t* row = bst + r * 128;
+          const int x7 = r & 7;
+          const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+          if (sb[i] <= 128u) {
+            const uint32_t c = sb[i] ? ((sb[i] + 126u) << 7) : 0u;
+            const uint32_t c2 = c * 0x10001u;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(row + (((cbase + q) ^ x7) << 4)) = dequant8(w[q], c2);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(row + (((cbase + q) ^ x7) << 4)) = dequant8_wide(w[q], sb[i]);
+          }
         }
         fence_proxy_async();
         __syncwarp();
@@ -479,11 +519,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
 #pragma unroll
           for (int jx = 0; jx < 16; ++jx)
             o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
-          store_out<TY>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, ncols >> 1, y_vec && ncols == 32);
+          store_out<TY, 16>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 32, ncols >> 1);
         } else {
 #pragma unroll
           for (int jx = 0; jx < 32; ++jx) v[jx] *= gamma;
-          store_out<TY>(Y + dst * p.ld_y + (n0 + c0), v, ncols, y_vec && ncols == 32);
+          store_out<TY, 32>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 32, ncols);
         }
       }
       tc_fence_before();
@@ -510,6 +550,7 @@ bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why) {
   if (a.y_dtype != MOE_BF16 && a.y_dtype != MOE_F32) { *why = "output is neither bf16 nor fp32"; return false; }
   if ((uintptr_t)a.x % 16 != 0 || a.ld_x % 8 != 0) { *why = "activation rows are not 16-byte aligned"; return false; }
   if ((uintptr_t)a.w % 16 != 0 || (uintptr_t)a.w_scale % 16 != 0) { *why = "weights are not 16-byte aligned"; return false; }
+  if ((double)a.rows_x * (double)a.ld_x * 2.0 >= 68719476736.0 * 0.99) { *why = "activations exceed 64 GB"; return false; }
   *why = "";
   return true;
 }

@@ -3,9 +3,11 @@
 // Canonical (what moe_downcast_mxfp4 writes for w[E,K,N] quantised along K): values [E][N][K/2] bytes,
 // byte b of a row holding k = 2b (low nibble) and 2b+1 (high nibble); scales [E][N][K/32] (any strides).
 // Tiled: tiles of 128 n x 128 k ordered [E][n_tile][k_tile].
-//   value tile: 128 rows x 64 bytes; 32-bit word j of a row covers k = 8j .. 8j+7 with nibble p holding
-//               k = 8j + {0,2,4,6,1,3,5,7}[p], so that (word >> 4i) & 0x000F000F yields the pair (2i, 2i+1)
-//               in the low and high half-word.
+//   value tile: 8 KB = [4 scale groups][128 rows][16 bytes]: the 16 bytes of (group g, row r) are the 32 k values
+//               k = 32g .. 32g+31 of that row, so that 8 consecutive lanes reading 8 consecutive rows of one
+//               group touch 128 contiguous bytes.  Inside, 32-bit word q covers k = 32g + 8q .. +7 with nibble p
+//               holding k + {0,2,4,6,1,3,5,7}[p], so that (word >> 4i) & 0x000F000F yields the pair (2i, 2i+1) in
+//               the low and high half-word.
 //   scale tile: 128 rows x 4 bytes (the four 32-groups of the k tile).
 // Out-of-range n or k is zero (value 0, scale byte 0).
 #include "common.cuh"
@@ -38,8 +40,10 @@ __global__ void __launch_bounds__(256) to_b200_values(const uint8_t* __restrict_
                                                       uint32_t* __restrict__ out) {
   const int64_t total = (int64_t)E * NT * KT * TN * 16;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int j = (int)(i & 15);
-    const int r = (int)((i >> 4) & (TN - 1));
+    const int qw = (int)(i & 3);                       // word inside the 16-byte group chunk
+    const int r = (int)((i >> 2) & (TN - 1));
+    const int g = (int)((i >> 9) & 3);
+    const int j = g * 4 + qw;                          // word of the row: k = 8 j .. 8 j + 7
     int64_t t = i >> 11;
     const int kt = (int)(t % KT); t /= KT;
     const int nt = (int)(t % NT);
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(256) from_b200_kernel(const uint32_t* __restri
     const int nt = n / TN, r = n % TN, kt = k / TK, j = (k % TK) / 8;
     const int64_t tile = ((int64_t)e * NT + nt) * KT + kt;
     if (q) {
-      const uint32_t w = nibble_deinterleave(values[tile * (TN * 16) + r * 16 + j]);
+      const uint32_t w = nibble_deinterleave(values[tile * (TN * 16) + (j >> 2) * (TN * 4) + r * 4 + (j & 3)]);
       uint8_t* dst = q + ((int64_t)e * N + n) * (K >> 1) + (k >> 1);
       dst[0] = (uint8_t)w; dst[1] = (uint8_t)(w >> 8); dst[2] = (uint8_t)(w >> 16); dst[3] = (uint8_t)(w >> 24);
     }
