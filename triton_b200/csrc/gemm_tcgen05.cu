@@ -16,6 +16,7 @@
 //   warps 6-13   dequantiser: packed e2m1 + e8m0 -> bf16, written into the swizzled K-major B tile; a thread
 //                takes the 32 k values of one (row, scale group) at a time: one 16-byte load, one scale byte
 //   warps 14-17  epilogue: tcgen05.ld of the accumulator, bias*beta, out_alpha, SwiGLU, gamma, cast, store
+// Tile 128 x 128, 64 k per stage, 6 stages.
 // Rings: raw weights (producer -> dequantiser), A and B operand stages (-> MMA), two accumulator
 // buffers (MMA -> epilogue).  Every mbarrier wait is bounded: when a wait expires the CTA raises a
 // shared abort flag, writes the caller's status word, drains its copies, frees tensor memory and
@@ -26,16 +27,17 @@ namespace {
 
 constexpr int BLOCK_M = 128;          // token rows per tile  (MMA M)
 constexpr int BLOCK_N = 128;          // weight rows per tile (MMA N)
-constexpr int BLOCK_K = 128;          // k per pipeline stage: two 64-wide swizzle sub-tiles
-constexpr int STAGES = 3;
+constexpr int BLOCK_K = 64;           // k per pipeline stage: one 128-byte swizzle row of bf16
+constexpr int STAGES = 6;
+constexpr int TILE_K = 128;           // k extent of a weight tile in global memory (two stages)
 constexpr int NUM_THREADS = 576;
 constexpr int LOADER_WARPS = 4, DEQUANT_WARPS = 8;
 constexpr int WARP_LOADER0 = 2, WARP_DEQ0 = 6, WARP_EPI0 = 14;
 constexpr int SUBTILE_BYTES = 128 * 128;                 // 128 rows x 128 bytes (64 bf16)
-constexpr int A_STAGE_BYTES = 2 * SUBTILE_BYTES;         // 32 KB
-constexpr int B_STAGE_BYTES = 2 * SUBTILE_BYTES;         // 32 KB
-constexpr int RAWV_BYTES = BLOCK_N * BLOCK_K / 2;        // 8 KB
-constexpr int RAWS_BYTES = BLOCK_N * 4;                  // 512 B
+constexpr int A_STAGE_BYTES = SUBTILE_BYTES;             // 16 KB
+constexpr int B_STAGE_BYTES = SUBTILE_BYTES;             // 16 KB
+constexpr int RAWV_BYTES = BLOCK_N * BLOCK_K / 2;        // 4 KB: half of an 8 KB weight tile ([2 groups][128 rows][16 B])
+constexpr int RAWS_BYTES = BLOCK_N * 4;                  // 512 B: the scale tile of the whole 128-k weight tile
 constexpr int TMEM_COLS = 2 * BLOCK_N;                   // two fp32 accumulators of 128 columns
 
 constexpr int OFF_A = 0;
@@ -124,10 +126,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// arrive on `bar` once every cp.async this thread has issued so far has landed (the barrier's expected count
+// already includes this arrival)
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(BAR_RAW_FULL(s), 1);
       mbar_init(BAR_RAW_EMPTY(s), DEQUANT_WARPS);
-      mbar_init(BAR_A_FULL(s), LOADER_WARPS);
+      mbar_init(BAR_A_FULL(s), LOADER_WARPS * 32);
       mbar_init(BAR_B_FULL(s), DEQUANT_WARPS);
       mbar_init(BAR_AB_EMPTY(s), 1);
     }
@@ -273,7 +278,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
 
   // ---- tile schedule shared by every role -----------------------------------------------------------
   const int NT = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const int KT = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int KT = (p.K + BLOCK_K - 1) / BLOCK_K;           // 64-k steps
+  const int KT_TILES = (p.K + TILE_K - 1) / TILE_K;      // 128-k weight tiles per (expert, n tile)
   const int64_t useful_m = p.slice_sizes ? (int64_t)p.block_offs[p.E] : grid_m_static;
   const int64_t n_tiles = useful_m * NT;
 
@@ -295,15 +301,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 102) && mbar_wait(BAR_B_FULL(s), ph, ctl, 103);
           if (!ok) break;
+          fence_proxy_async();          // the A tile was written by cp.async (generic proxy) of other threads
           tc_fence_after();
+          const uint64_t adesc = make_desc(sbase + OFF_A + s * A_STAGE_BYTES);
+          const uint64_t bdesc = make_desc(sbase + OFF_B + s * B_STAGE_BYTES);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint64_t adesc = make_desc(sbase + OFF_A + s * A_STAGE_BYTES + h * SUBTILE_BYTES);
-            const uint64_t bdesc = make_desc(sbase + OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), (kt | h | kk) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), (kt | kk) ? 1u : 0u);
           mma_commit(BAR_AB_EMPTY(s));
         }
         if (ok) mma_commit(BAR_ACC_FULL(ab));
@@ -324,14 +328,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         int e; int64_t row0; int rows;
         if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
         const int nt = (int)(tile % NT);
-        const int64_t tile0 = ((int64_t)e * NT + nt) * KT;
+        const int64_t tile0 = ((int64_t)e * NT + nt) * KT_TILES;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 201);
           if (!ok) break;
           mbar_expect_tx(BAR_RAW_FULL(s), RAWV_BYTES + RAWS_BYTES);
-          bulk_g2s(sbase + OFF_RAWV + s * RAWV_BYTES, wv + (tile0 + kt) * RAWV_BYTES, RAWV_BYTES, BAR_RAW_FULL(s));
-          bulk_g2s(sbase + OFF_RAWS + s * RAWS_BYTES, ws + (tile0 + kt) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
+          // stage kt is half (kt & 1) of weight tile kt >> 1: 4 KB of values, plus the tile's 512 scale bytes
+          bulk_g2s(sbase + OFF_RAWV + s * RAWV_BYTES, wv + (tile0 * 2 + kt) * RAWV_BYTES, RAWV_BYTES, BAR_RAW_FULL(s));
+          bulk_g2s(sbase + OFF_RAWS + s * RAWS_BYTES, ws + (tile0 + (kt >> 1)) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
         }
       }
       if (!ok) {
@@ -344,36 +349,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     __syncwarp();
   } else if (warp < WARP_DEQ0) {
     // ================================= activation loader ==============================================
-    // 128 threads move the 128 x 256-byte stage: thread t owns 16-byte chunk (t & 15) of rows (t >> 4) + 8 i.
-    // The source of each row (byte offset / 16 into x, or none) is kept in registers for the whole tile.
+    // 128 threads move the 128 x 128-byte stage: thread t owns 16-byte chunk (t & 7) of rows (t >> 3) + 16 i.
+    // The source of each row (byte offset / 16 into x, or none) is kept in registers for the whole tile.  A
+    // stage is published by cp.async.mbarrier.arrive.noinc: the barrier completes when the copies of all 128
+    // threads have landed, and no thread ever waits for its own copies.
     const int t = threadIdx.x - WARP_LOADER0 * 32;  // 0..127
-    const int cc = t & 15;
-    const int rbase = t >> 4;
+    const int c8 = t & 7;
+    const int rbase = t >> 3;
     const uint8_t* Xb = (const uint8_t*)p.x;
-    const uint32_t a_off = (uint32_t)((cc >> 3) * SUBTILE_BYTES);
-    const int c8 = cc & 7;
     const uint32_t ld16 = (uint32_t)(p.ld_x >> 3);  // row pitch in 16-byte units
-    uint32_t dst_off[16];
+    uint32_t dst_off[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int r = rbase + 8 * i;
-      dst_off[i] = a_off + (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4));
+    for (int i = 0; i < 8; ++i) {
+      const int r = rbase + 16 * i;
+      dst_off[i] = (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4));
     }
-    uint32_t it = 0, it_sig = 0;
+    uint32_t it = 0;
     bool ok = true;
-    auto signal_oldest = [&]() {
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR_A_FULL(it_sig % STAGES));
-      ++it_sig;
-    };
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int e; int64_t row0; int rows;
       if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
-      uint32_t src16[16];                           // 0xFFFFFFFF: no source row
+      uint32_t src16[8];                            // 0xFFFFFFFF: no source row
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int r = rbase + 8 * i;
+      for (int i = 0; i < 8; ++i) {
+        const int r = rbase + 16 * i;
         int64_t src = -1;
         if (r < rows) {
           const int64_t m = row0 + r;
@@ -386,36 +385,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         const int s = it % STAGES;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_AB_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 301));
         if (!ok) break;
-        const int k = kt * BLOCK_K + cc * 8;
+        const int k = kt * BLOCK_K + c8 * 8;
         const int kleft = p.K - k;
         const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
         const uint32_t stage = sbase + OFF_A + s * A_STAGE_BYTES;
         const uint32_t kc16 = (uint32_t)(k >> 3);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 8; ++i) {
           const bool live = src16[i] != 0xFFFFFFFFu && kbytes;
           const uint8_t* g = live ? Xb + ((uint64_t)(src16[i] + kc16) << 4) : Xb;
           cp_async16(stage + dst_off[i], g, live ? kbytes : 0u);
         }
-        cp_async_commit();
-        if (it - it_sig >= 2) {
-          cp_async_wait<2>();
-          signal_oldest();
-        }
+        cp_async_arrive_noinc(BAR_A_FULL(s));
       }
     }
-    cp_async_wait<0>();
-    while (it_sig < it) signal_oldest();
+    cp_async_wait_all();
   } else if (warp < WARP_EPI0) {
     // ================================= dequantiser ======================================================
-    // 256 threads; lane = (scale group g) * 8 + (row within 8): a thread converts the 32 k values of one
-    // (row, group) -- one 16-byte load, one scale byte, four 16-byte swizzled stores -- for rows
-    // 8 * dequant_warp + (lane & 7) and that + 64.
+    // 256 threads, one (row, 32-k scale group) unit each per stage: one 16-byte load, one scale byte, four
+    // 16-byte swizzled stores.  A quarter-warp holds one group of 8 consecutive rows, which keeps the load
+    // (128 contiguous bytes) and the stores (8 distinct 16-byte columns) free of bank conflicts.
     const int dw = warp - WARP_DEQ0;                // 0..7
-    const int g = lane >> 3;                        // 32-k group of the 128-k stage
-    const int rl = dw * 8 + (lane & 7);
-    const uint32_t b_sub = (uint32_t)((g >> 1) * SUBTILE_BYTES);
-    const int cbase = (g & 1) * 4;                  // first 16-byte chunk of the group inside the 128-byte row
+    const int g = (lane >> 3) & 1;                  // scale group inside the 64-k stage
+    const int r = dw * 16 + (lane >> 4) * 8 + (lane & 7);
+    const int x7 = r & 7;
+    const uint32_t row_off = (uint32_t)(r * 128);
     uint32_t it = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -427,33 +421,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         ok = __all_sync(0xFFFFFFFFu,
                         mbar_wait(BAR_RAW_FULL(s), ph, ctl, 401) && mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
         if (!ok) break;
-        const uint4* rv = reinterpret_cast<const uint4*>(smem + OFF_RAWV + s * RAWV_BYTES) + g * BLOCK_N;
-        const uint8_t* rs = smem + OFF_RAWS + s * RAWS_BYTES + g;
-        uint8_t* bst = smem + OFF_B + s * B_STAGE_BYTES + b_sub;
-        uint4 raw[2];
-        uint32_t sb[2];
+        const uint4 raw = reinterpret_cast<const uint4*>(smem + OFF_RAWV + s * RAWV_BYTES)[g * BLOCK_N + r];
+        const uint32_t sb = (smem + OFF_RAWS + s * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
+        uint8_t* row = smem + OFF_B + s * B_STAGE_BYTES + row_off;
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (sb <= 128u) {
+          const uint32_t c = sb ? ((sb + 126u) << 7) : 0u;
+          const uint32_t c2 = c * 0x10001u;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          raw[i] = rv[rl + 64 * i];
-          sb[i] = rs[(rl + 64 * i) * 4];
-        }
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int r = rl + 64 * i;
-          uint8_t* row = bst + r * 128;
-          const int x7 = r & 7;
-          const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-          if (sb[i] <= 128u) {
-            const uint32_t c = sb[i] ? ((sb[i] + 126u) << 7) : 0u;
-            const uint32_t c2 = c * 0x10001u;
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              *reinterpret_cast<uint4*>(row + (((cbase + q) ^ x7) << 4)) = dequant8(w[q], c2);
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              *reinterpret_cast<uint4*>(row + (((cbase + q) ^ x7) << 4)) = dequant8_wide(w[q], sb[i]);
-          }
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sb);
         }
         fence_proxy_async();
         __syncwarp();
