@@ -172,6 +172,7 @@ typedef struct {
   void* y; int y_dtype; int64_t ld_y;              /* [M or len(scatter), N / (2 if swiglu)] */
   /* tuning */
   int kernel;                                      /* MOE_GEMM_* */
+  int tile_m;                                      /* token rows per tile of the tcgen05 kernel: 0 auto, 128, 256 */
   int32_t* status;                                 /* device word, set non-zero when a bounded wait expires */
 } MoeGemmArgs;
 int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);

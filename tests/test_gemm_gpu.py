@@ -51,7 +51,7 @@ def reference(p, fp32_act=True):
     return y
 
 
-def run(p, device, layout, kernel="auto"):
+def run(p, device, layout, kernel="auto", block_m=None):
     dev = lambda t: None if t is None else t.to(device)
     wq = wrap_torch_tensor(dev(p["wq"]), dtype=FP4)
     ws = wrap_torch_tensor(dev(p["ws"]))
@@ -65,7 +65,10 @@ def run(p, device, layout, kernel="auto"):
     fa = None
     if p["act"]:
         fa = tb.FusedActivation(tb.FnSpecs("swiglu", tb.swiglu_fn, ("alpha", "limit"), reduction_n=2), p["act"])
-    with tb.scoped_opt_flags_constraints({"kernel": kernel}):
+    cons = {"kernel": kernel}
+    if block_m:
+        cons["block_m"] = block_m
+    with tb.scoped_opt_flags_constraints(cons):
         y = tb.matmul(dev(p["x"]), wq, dev(p["bias"]), md, None, dev(p["gather"]), dev(p["scatter"]), pc,
                       betas=dev(p["betas"]), gammas=dev(p["gammas"]), fused_activation=fa)
     tb.matmul_check_status()
@@ -88,21 +91,22 @@ SMALL = [
     (1, 64, 32, [5], 9),
     (3, 512, 256, [130, 1, 64], 200),
     (8, 2880, 384, [0, 17, 128, 129, 3, 0, 64, 255], 300),
+    (5, 320, 128, [600, 256, 257, 0, 511], 700),
 ]
 
 
 @pytest.mark.parametrize("case", SMALL)
 @pytest.mark.parametrize("mode", ["plain", "gather", "scatter_w", "swiglu", "all"])
-@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05"])
+@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256"])
 def test_grouped_gemm(case, mode, path, device):
     E, K, N, sizes, T = case
     opts = dict(plain=dict(gather=False), gather=dict(gather=True),
                 scatter_w=dict(gather=True, scatter=True, weights=True), swiglu=dict(gather=True, act=True),
                 all=dict(gather=True, scatter=True, weights=True, act=True))[mode]
     p = make_problem(E, K, N, sizes, T, seed=hash((E, K, N, mode)) % 1000, device=device, **opts)
-    layout, kernel = {"simt-canonical": ("canonical", "simt"), "simt-blackwell": ("blackwell", "simt"),
-                      "tcgen05": ("b200", "tcgen05")}[path]
-    y = run(p, device, layout, kernel)
+    layout, kernel, block_m = {"simt-canonical": ("canonical", "simt", None), "simt-blackwell": ("blackwell", "simt", None),
+                               "tcgen05": ("b200", "tcgen05", 128), "tcgen05-256": ("b200", "tcgen05", 256)}[path]
+    y = run(p, device, layout, kernel, block_m)
     check(p, y)
 
 

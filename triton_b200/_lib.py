@@ -40,7 +40,7 @@ class MoeGemmArgs(C.Structure):
         ("out_alpha", f32), ("has_out_alpha", i32),
         ("activation", i32), ("act_alpha", f32), ("act_limit", f32), ("act_has_limit", i32),
         ("y", vp), ("y_dtype", i32), ("ld_y", i64),
-        ("kernel", i32), ("status", vp),
+        ("kernel", i32), ("tile_m", i32), ("status", vp),
     ]
 
 

@@ -16,7 +16,7 @@
 //   warps 6-13   dequantiser: packed e2m1 + e8m0 -> bf16, written into the swizzled K-major B tile; a thread
 //                takes the 32 k values of one (row, scale group) at a time: one 16-byte load, one scale byte
 //   warps 14-17  epilogue: tcgen05.ld of the accumulator, bias*beta, out_alpha, SwiGLU, gamma, cast, store
-// Tile 128 x 128, 64 k per stage, 6 stages.
+// Tile (128 or 256 token rows) x 128 weight rows, 64 k per stage, 6 or 4 stages.
 // Rings: raw weights (producer -> dequantiser), A and B operand stages (-> MMA), two accumulator
 // buffers (MMA -> epilogue).  Every mbarrier wait is bounded: when a wait expires the CTA raises a
 // shared abort flag, writes the caller's status word, drains its copies, frees tensor memory and
@@ -25,31 +25,39 @@
 
 namespace {
 
-constexpr int BLOCK_M = 128;          // token rows per tile  (MMA M)
+constexpr int HALF_M = 128;           // token rows of one MMA (MMA M)
 constexpr int BLOCK_N = 128;          // weight rows per tile (MMA N)
 constexpr int BLOCK_K = 64;           // k per pipeline stage: one 128-byte swizzle row of bf16
-constexpr int STAGES = 6;
 constexpr int TILE_K = 128;           // k extent of a weight tile in global memory (two stages)
 constexpr int NUM_THREADS = 576;
 constexpr int LOADER_WARPS = 4, DEQUANT_WARPS = 8;
 constexpr int WARP_LOADER0 = 2, WARP_DEQ0 = 6, WARP_EPI0 = 14;
 constexpr int SUBTILE_BYTES = 128 * 128;                 // 128 rows x 128 bytes (64 bf16)
-constexpr int A_STAGE_BYTES = SUBTILE_BYTES;             // 16 KB
 constexpr int B_STAGE_BYTES = SUBTILE_BYTES;             // 16 KB
 constexpr int RAWV_BYTES = BLOCK_N * BLOCK_K / 2;        // 4 KB: half of an 8 KB weight tile ([2 groups][128 rows][16 B])
 constexpr int RAWS_BYTES = BLOCK_N * 4;                  // 512 B: the scale tile of the whole 128-k weight tile
-constexpr int TMEM_COLS = 2 * BLOCK_N;                   // two fp32 accumulators of 128 columns
+constexpr int TMEM_COLS = 512;                           // two accumulator buffers of MH x 128 columns (256 used when MH = 1)
+constexpr int MAX_PREFIX_EXPERTS = 2048;                 // experts the 256-row tile schedule can index
 
-constexpr int OFF_A = 0;
-constexpr int OFF_B = OFF_A + STAGES * A_STAGE_BYTES;
-constexpr int OFF_RAWV = OFF_B + STAGES * B_STAGE_BYTES;
-constexpr int OFF_RAWS = OFF_RAWV + STAGES * RAWV_BYTES;
-constexpr int OFF_BIAS = OFF_RAWS + STAGES * RAWS_BYTES;         // float bias, [4 epilogue warps][128]
-constexpr int OFF_BAR = OFF_BIAS + 4 * BLOCK_N * 4;              // mbarriers
-constexpr int NUM_BARS = 5 * STAGES + 4 + 1;
-constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;                 // tmem base, abort flag
-constexpr int SMEM_BYTES = OFF_MISC + 16;
-constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;                    // slack for 1024-byte alignment
+// Shared-memory map for a tile of MH x 128 token rows.  MH = 1: 6 stages; MH = 2: 4 stages (the two halves
+// of a token tile share every dequantised weight stage, which halves the dequantiser work per FLOP).
+template <int MH> struct Cfg {
+  static constexpr int BLOCK_M = HALF_M * MH;
+  static constexpr int STAGES = MH == 1 ? 6 : 4;
+  static constexpr int A_STAGE_BYTES = MH * SUBTILE_BYTES;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_STAGE_BYTES;
+  static constexpr int OFF_RAWV = OFF_B + STAGES * B_STAGE_BYTES;
+  static constexpr int OFF_RAWS = OFF_RAWV + STAGES * RAWV_BYTES;
+  static constexpr int OFF_BIAS = OFF_RAWS + STAGES * RAWS_BYTES;       // float bias, [4 epilogue warps][128]
+  static constexpr int OFF_BAR = OFF_BIAS + 4 * BLOCK_N * 4;            // mbarriers
+  static constexpr int NUM_BARS = 5 * STAGES + 4 + 1;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;               // tmem base, abort flag
+  static constexpr int OFF_PREFIX = OFF_MISC + 16;                      // MH = 2: int32 tile prefix over experts
+  static constexpr int SMEM_BYTES = OFF_PREFIX + (MH == 2 ? (MAX_PREFIX_EXPERTS + 1) * 4 : 0);
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;                  // slack for 1024-byte alignment
+  static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
+};
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;      // a wait that lasts 2 s aborts the CTA
 
@@ -147,7 +155,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 
 // instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
-                           ((uint32_t)(BLOCK_M >> 4) << 24);
+                           ((uint32_t)(HALF_M >> 4) << 24);
 
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
   asm volatile(
@@ -226,15 +234,39 @@ template <typename TY, int N> __device__ __forceinline__ void store_out(TY* dst,
 }
 
 // =========================================================================================================
-template <typename TY>
+// Token-tile -> (expert, first row, valid rows).  MH = 1 follows the block schedule for blocks of 128 rows.
+// MH = 2 pairs consecutive 128-row blocks of one expert: tile j of expert e covers rows [256 j, 256 j + 256);
+// `prefix` (shared memory) holds the exclusive prefix of ceil(blocks128(e) / 2) over experts.
+template <int MH>
+__device__ __forceinline__ bool map_tile(const GemmParams& p, const int32_t* prefix, int64_t pid_m, int& e,
+                                         int64_t& row0, int& rows) {
+  if constexpr (MH == 1) {
+    return gemm_map_block<HALF_M>(p, pid_m, e, row0, rows);
+  } else {
+    if (p.slice_sizes == nullptr) return gemm_map_block<2 * HALF_M>(p, pid_m, e, row0, rows);
+    int lo = 0, hi = p.E;                         // largest e with prefix[e] <= pid_m
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (prefix[mid] <= pid_m) lo = mid; else hi = mid;
+    }
+    e = lo;
+    const int j = (int)(pid_m - prefix[lo]);
+    row0 = (int64_t)p.slice_offs[e] + (int64_t)j * (2 * HALF_M);
+    rows = min(2 * HALF_M, p.slice_sizes[e] - j * (2 * HALF_M));
+    return rows > 0;
+  }
+}
+
+template <typename TY, int MH>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static) {
+  using C = Cfg<MH>;
+  constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-  const uint32_t bar0 = sbase + OFF_BAR;
+  const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR_RAW_FULL = [&](int s) { return bar0 + 8u * (uint32_t)s; };
   auto BAR_RAW_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
   auto BAR_A_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(2 * STAGES + s); };
@@ -243,10 +275,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   auto BAR_ACC_FULL = [&](int a) { return bar0 + 8u * (uint32_t)(5 * STAGES + a); };
   auto BAR_ACC_EMPTY = [&](int a) { return bar0 + 8u * (uint32_t)(5 * STAGES + 2 + a); };
   const uint32_t BAR_DRAIN = bar0 + 8u * (uint32_t)(5 * STAGES + 4);
-  (void)bars;
 
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
+  int32_t* s_prefix = reinterpret_cast<int32_t*>(smem + C::OFF_PREFIX);
   Ctl ctl{s_abort, p.status};
 
   if (threadIdx.x == 0) {
@@ -266,10 +298,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + OFF_MISC),
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + C::OFF_MISC),
                  "r"((uint32_t)TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if constexpr (MH == 2) {
+    // tile prefix over experts: number of 256-row tiles of expert e = ceil(blocks128(e) / 2)
+    if (p.slice_sizes != nullptr) {
+      for (int e = threadIdx.x; e < p.E; e += NUM_THREADS)
+        s_prefix[e + 1] = (p.block_offs[e + 1] - p.block_offs[e] + 1) >> 1;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int run = 0;
+        s_prefix[0] = 0;
+        for (int e = 1; e <= p.E; ++e) {
+          run += s_prefix[e];
+          s_prefix[e] = run;
+        }
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -280,7 +328,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   const int NT = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int KT = (p.K + BLOCK_K - 1) / BLOCK_K;           // 64-k steps
   const int KT_TILES = (p.K + TILE_K - 1) / TILE_K;      // 128-k weight tiles per (expert, n tile)
-  const int64_t useful_m = p.slice_sizes ? (int64_t)p.block_offs[p.E] : grid_m_static;
+  int64_t useful_m = grid_m_static;
+  if (p.slice_sizes) useful_m = (MH == 2) ? (int64_t)s_prefix[p.E] : (int64_t)p.block_offs[p.E];
   const int64_t n_tiles = useful_m * NT;
 
   if (warp == 0) {
@@ -290,12 +339,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
         int e; int64_t row0; int rows;
-        if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+        if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
+        const int halves = rows > HALF_M ? 2 : 1;
         const uint32_t ab = tc & 1u;
         ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc >> 1) & 1u) ^ 1u, ctl, 101);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + ab * BLOCK_N;
+        const uint32_t d_tmem = tmem_base + ab * (MH * BLOCK_N);
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -303,11 +353,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           if (!ok) break;
           fence_proxy_async();          // the A tile was written by cp.async (generic proxy) of other threads
           tc_fence_after();
-          const uint64_t adesc = make_desc(sbase + OFF_A + s * A_STAGE_BYTES);
-          const uint64_t bdesc = make_desc(sbase + OFF_B + s * B_STAGE_BYTES);
+          const uint64_t adesc = make_desc(sbase + C::OFF_A + s * C::A_STAGE_BYTES);
+          const uint64_t bdesc = make_desc(sbase + C::OFF_B + s * B_STAGE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
+          for (int kk = 0; kk < 4; ++kk) {
             mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), (kt | kk) ? 1u : 0u);
+            if (MH == 2 && halves == 2)
+              mma_bf16(d_tmem + BLOCK_N, adesc + (uint64_t)((SUBTILE_BYTES >> 4) + kk * 2), bdesc + (uint64_t)(kk * 2),
+                       (kt | kk) ? 1u : 0u);
+          }
           mma_commit(BAR_AB_EMPTY(s));
         }
         if (ok) mma_commit(BAR_ACC_FULL(ab));
@@ -326,7 +380,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       const uint8_t* ws = p.w_scale;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int e; int64_t row0; int rows;
-        if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+        if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
         const int nt = (int)(tile % NT);
         const int64_t tile0 = ((int64_t)e * NT + nt) * KT_TILES;
         for (int kt = 0; kt < KT; ++kt, ++it) {
@@ -335,13 +389,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           if (!ok) break;
           mbar_expect_tx(BAR_RAW_FULL(s), RAWV_BYTES + RAWS_BYTES);
           // stage kt is half (kt & 1) of weight tile kt >> 1: 4 KB of values, plus the tile's 512 scale bytes
-          bulk_g2s(sbase + OFF_RAWV + s * RAWV_BYTES, wv + (tile0 * 2 + kt) * RAWV_BYTES, RAWV_BYTES, BAR_RAW_FULL(s));
-          bulk_g2s(sbase + OFF_RAWS + s * RAWS_BYTES, ws + (tile0 + (kt >> 1)) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
+          bulk_g2s(sbase + C::OFF_RAWV + s * RAWV_BYTES, wv + (tile0 * 2 + kt) * RAWV_BYTES, RAWV_BYTES, BAR_RAW_FULL(s));
+          bulk_g2s(sbase + C::OFF_RAWS + s * RAWS_BYTES, ws + (tile0 + (kt >> 1)) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
         }
       }
       if (!ok) {
         // aborting: let the copies that were already issued land before the CTA leaves
-        const uint32_t lo = it > STAGES ? it - STAGES : 0;
+        const uint32_t lo = it > (uint32_t)STAGES ? it - STAGES : 0;
         for (uint32_t j = lo; j < it; ++j)
           for (uint32_t i = 0; i < (1u << 16) && !mbar_test(BAR_RAW_FULL(j % STAGES), (j / STAGES) & 1u); ++i) __nanosleep(64);
       }
@@ -349,29 +403,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     __syncwarp();
   } else if (warp < WARP_DEQ0) {
     // ================================= activation loader ==============================================
-    // 128 threads move the 128 x 128-byte stage: thread t owns 16-byte chunk (t & 7) of rows (t >> 3) + 16 i.
-    // The source of each row (byte offset / 16 into x, or none) is kept in registers for the whole tile.  A
-    // stage is published by cp.async.mbarrier.arrive.noinc: the barrier completes when the copies of all 128
-    // threads have landed, and no thread ever waits for its own copies.
+    // 128 threads move the (MH x 128) x 128-byte stage: thread t owns 16-byte chunk (t & 7) of rows
+    // (t >> 3) + 16 i.  The source of each row (byte offset / 16 into x, or none) is kept in registers for the
+    // whole tile.  A stage is published by cp.async.mbarrier.arrive.noinc: the barrier completes when the
+    // copies of all 128 threads have landed, and no thread ever waits for its own copies.
+    constexpr int NR = 8 * MH;                      // rows per thread
     const int t = threadIdx.x - WARP_LOADER0 * 32;  // 0..127
     const int c8 = t & 7;
     const int rbase = t >> 3;
     const uint8_t* Xb = (const uint8_t*)p.x;
     const uint32_t ld16 = (uint32_t)(p.ld_x >> 3);  // row pitch in 16-byte units
-    uint32_t dst_off[8];
+    uint32_t dst_off[NR];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = rbase + 16 * i;
+    for (int i = 0; i < NR; ++i) {
+      const int r = rbase + 16 * i;                 // rows 128.. land in the second 16 KB sub-tile
       dst_off[i] = (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4));
     }
     uint32_t it = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int e; int64_t row0; int rows;
-      if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
-      uint32_t src16[8];                            // 0xFFFFFFFF: no source row
+      if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
+      const int nr_live = (MH == 2 && rows > HALF_M) ? NR : 8;   // the MMA skips an empty second half
+      uint32_t src16[NR];                           // 0xFFFFFFFF: no source row
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < NR; ++i) {
         const int r = rbase + 16 * i;
         int64_t src = -1;
         if (r < rows) {
@@ -388,13 +444,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         const int k = kt * BLOCK_K + c8 * 8;
         const int kleft = p.K - k;
         const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
-        const uint32_t stage = sbase + OFF_A + s * A_STAGE_BYTES;
+        const uint32_t stage = sbase + C::OFF_A + s * C::A_STAGE_BYTES;
         const uint32_t kc16 = (uint32_t)(k >> 3);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const bool live = src16[i] != 0xFFFFFFFFu && kbytes;
-          const uint8_t* g = live ? Xb + ((uint64_t)(src16[i] + kc16) << 4) : Xb;
-          cp_async16(stage + dst_off[i], g, live ? kbytes : 0u);
+        for (int i = 0; i < NR; ++i) {
+          if (i < nr_live) {
+            const bool live = src16[i] != 0xFFFFFFFFu && kbytes;
+            const uint8_t* g = live ? Xb + ((uint64_t)(src16[i] + kc16) << 4) : Xb;
+            cp_async16(stage + dst_off[i], g, live ? kbytes : 0u);
+          }
         }
         cp_async_arrive_noinc(BAR_A_FULL(s));
       }
@@ -414,16 +472,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int e; int64_t row0; int rows;
-      if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+      if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         ok = __all_sync(0xFFFFFFFFu,
                         mbar_wait(BAR_RAW_FULL(s), ph, ctl, 401) && mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
         if (!ok) break;
-        const uint4 raw = reinterpret_cast<const uint4*>(smem + OFF_RAWV + s * RAWV_BYTES)[g * BLOCK_N + r];
-        const uint32_t sb = (smem + OFF_RAWS + s * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
-        uint8_t* row = smem + OFF_B + s * B_STAGE_BYTES + row_off;
+        const uint4 raw = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + s * RAWV_BYTES)[g * BLOCK_N + r];
+        const uint32_t sb = (smem + C::OFF_RAWS + s * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
+        uint8_t* row = smem + C::OFF_B + s * B_STAGE_BYTES + row_off;
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
         if (sb <= 128u) {
           const uint32_t c = sb ? ((sb + 126u) << 7) : 0u;
@@ -447,8 +505,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   } else {
     // ================================= epilogue =========================================================
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
-    const int r = q * 32 + lane;                    // accumulator row = token row inside the tile
-    float* s_bias = reinterpret_cast<float*>(smem + OFF_BIAS) + q * BLOCK_N;   // private to this warp
+    float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + q * BLOCK_N;   // private to this warp
     TY* Y = (TY*)p.y;
     const bool swiglu = p.activation == MOE_ACT_SWIGLU;
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
@@ -456,7 +513,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
       int e; int64_t row0; int rows;
-      if (!gemm_map_block<BLOCK_M>(p, tile / NT, e, row0, rows)) continue;
+      if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
+      const int halves = rows > HALF_M ? 2 : 1;
       const int n0 = (int)(tile % NT) * BLOCK_N;
       const uint32_t ab = tc & 1u;
       // stage this tile's bias columns (each warp keeps its own copy: no CTA-level barrier in this role)
@@ -467,44 +525,47 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         s_bias[jb * 32 + lane] = (p.bias && gn < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + gn) : 0.0f;
       }
       __syncwarp();
-      const int64_t m = row0 + r;
-      const bool row_live = r < rows;
-      int64_t dst = m;
-      float beta = 1.0f, gamma = 1.0f;
-      if (row_live) {
-        if (p.scatter_indx) dst = p.scatter_indx[m];
-        if (p.betas) beta = p.betas[m];
-        if (p.gammas) gamma = p.gammas[m];
-      }
-      const bool store_row = row_live && dst >= 0;
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc >> 1) & 1u, ctl, 501));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * BLOCK_N;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
-        uint32_t raw[32];
-        tmem_ld32(taddr + (uint32_t)c0, raw);
-        tmem_ld_wait();
-        if (!store_row || n0 + c0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int jx = 0; jx < 32; ++jx) {
-          float a = __uint_as_float(raw[jx]) + s_bias[c0 + jx] * beta;
-          if (p.has_out_alpha) a *= p.out_alpha;
-          v[jx] = a;
+      for (int h = 0; h < halves; ++h) {
+        const int r = h * HALF_M + q * 32 + lane;   // accumulator row = token row inside the tile
+        const int64_t m = row0 + r;
+        const bool row_live = r < rows;
+        int64_t dst = m;
+        float beta = 1.0f, gamma = 1.0f;
+        if (row_live) {
+          if (p.scatter_indx) dst = p.scatter_indx[m];
+          if (p.betas) beta = p.betas[m];
+          if (p.gammas) gamma = p.gammas[m];
         }
-        const int ncols = min(32, p.N - (n0 + c0));
-        if (swiglu) {
-          float o[16];
+        const bool store_row = row_live && dst >= 0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * (MH * BLOCK_N) + h * BLOCK_N;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+          uint32_t raw[32];
+          tmem_ld32(taddr + (uint32_t)c0, raw);
+          tmem_ld_wait();
+          if (!store_row || n0 + c0 >= p.N) continue;
+          float v[32];
 #pragma unroll
-          for (int jx = 0; jx < 16; ++jx)
-            o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
-          store_out<TY, 16>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 32, ncols >> 1);
-        } else {
+          for (int jx = 0; jx < 32; ++jx) {
+            float a = __uint_as_float(raw[jx]) + s_bias[c0 + jx] * beta;
+            if (p.has_out_alpha) a *= p.out_alpha;
+            v[jx] = a;
+          }
+          const int ncols = min(32, p.N - (n0 + c0));
+          if (swiglu) {
+            float o[16];
 #pragma unroll
-          for (int jx = 0; jx < 32; ++jx) v[jx] *= gamma;
-          store_out<TY, 32>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 32, ncols);
+            for (int jx = 0; jx < 16; ++jx)
+              o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
+            store_out<TY, 16>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 32, ncols >> 1);
+          } else {
+#pragma unroll
+            for (int jx = 0; jx < 32; ++jx) v[jx] *= gamma;
+            store_out<TY, 32>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 32, ncols);
+          }
         }
       }
       tc_fence_before();
@@ -532,37 +593,45 @@ bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why) {
   if ((uintptr_t)a.x % 16 != 0 || a.ld_x % 8 != 0) { *why = "activation rows are not 16-byte aligned"; return false; }
   if ((uintptr_t)a.w % 16 != 0 || (uintptr_t)a.w_scale % 16 != 0) { *why = "weights are not 16-byte aligned"; return false; }
   if ((double)a.rows_x * (double)a.ld_x * 2.0 >= 68719476736.0 * 0.99) { *why = "activations exceed 64 GB"; return false; }
+  if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256) { *why = "tile_m must be 0, 128 or 256"; return false; }
   *why = "";
   return true;
 }
 
-static int64_t n_blocks_bound128(int64_t n_slices, int64_t n_rows) {
+// upper bound on the number of row blocks of `block` rows (triton_kernels tensor_details/ragged_tensor.py:73-77)
+static int64_t n_blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
   if (n_rows <= n_slices) return n_rows;
   const int64_t a = n_rows + 1 - n_slices;   // -(n_slices - n_rows - 1)
-  return n_slices - 1 + (a + 127) / 128;
+  return n_slices - 1 + (a + block - 1) / block;
+}
+
+template <typename TY, int MH>
+static int launch_tc(const GemmParams& p, int64_t grid_m, int64_t N, cudaStream_t st) {
+  const int64_t tiles = grid_m * cdiv64(N, BLOCK_N);
+  const int sms = moe_sm_count();
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TY, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MH>::SMEM_ALLOC));
+  gemm_tc_kernel<TY, MH><<<grid, NUM_THREADS, Cfg<MH>::SMEM_ALLOC, st>>>(p, grid_m);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
 }
 
 int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_t st) {
   GemmParams p = p_in;
+  // 256-row token tiles halve the dequantiser work per FLOP; they pay off once experts hold more than a
+  // block or two of rows.  128-row tiles keep small problems (decode) spread over more CTAs.
+  int mh = a.tile_m == 256 ? 2 : (a.tile_m == 128 ? 1 : ((a.M / (a.E > 0 ? a.E : 1)) >= 192 ? 2 : 1));
+  if (mh == 2 && a.slice_sizes && a.E > MAX_PREFIX_EXPERTS) mh = 1;
   int64_t grid_m;
   if (a.slice_sizes) {
     p.block_offs = a.block_offs_16 + 3 * a.ld_block_offs;      // block size 128
     p.block_sched = a.block_sched_16 + 3 * a.ld_block_sched;
-    grid_m = n_blocks_bound128(a.E, a.M);
+    grid_m = n_blocks_bound(a.E, a.M, 128 * mh);
   } else {
-    grid_m = cdiv64(a.M, BLOCK_M);
+    grid_m = cdiv64(a.M, 128 * mh);
   }
   if (grid_m == 0) return MOE_OK;
-  const int64_t tiles = grid_m * cdiv64(a.N, BLOCK_N);
-  const int sms = moe_sm_count();
-  const int grid = (int)(tiles < sms ? tiles : sms);
-  if (a.y_dtype == MOE_BF16) {
-    MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-    gemm_tc_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_ALLOC, st>>>(p, grid_m);
-  } else {
-    MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-    gemm_tc_kernel<float><<<grid, NUM_THREADS, SMEM_ALLOC, st>>>(p, grid_m);
-  }
-  MOE_CHECK_LAUNCH();
-  return MOE_OK;
+  if (a.y_dtype == MOE_BF16)
+    return mh == 2 ? launch_tc<__nv_bfloat16, 2>(p, grid_m, a.N, st) : launch_tc<__nv_bfloat16, 1>(p, grid_m, a.N, st);
+  return mh == 2 ? launch_tc<float, 2>(p, grid_m, a.N, st) : launch_tc<float, 1>(p, grid_m, a.N, st);
 }

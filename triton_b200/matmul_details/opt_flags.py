@@ -49,6 +49,12 @@ def scoped_opt_flags_constraints(constraints):
         _opt_flags_constraints.reset(token)
 
 
+def resolve_tile_m() -> int:
+    """`block_m` constraint -> token rows per tile of the tensor-core kernel (0 = heuristic)."""
+    bm = get_opt_flags_constraints().get("block_m")
+    return bm if bm in (128, 256) else 0
+
+
 def resolve_kernel_choice() -> str:
     c = get_opt_flags_constraints()
     for k, v in c.items():
