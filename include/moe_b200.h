@@ -173,6 +173,7 @@ typedef struct {
   /* tuning */
   int kernel;                                      /* MOE_GEMM_* */
   int tile_m;                                      /* token rows per tile of the tcgen05 kernel: 0 auto, 128, 256 */
+  int tile_n;                                      /* weight rows per tile: 0 auto, 128, 256 (256 needs tile_m 256) */
   int32_t* status;                                 /* device word, set non-zero when a bounded wait expires */
 } MoeGemmArgs;
 int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);

@@ -51,7 +51,7 @@ def reference(p, fp32_act=True):
     return y
 
 
-def run(p, device, layout, kernel="auto", block_m=None):
+def run(p, device, layout, kernel="auto", block_m=None, block_n=None):
     dev = lambda t: None if t is None else t.to(device)
     wq = wrap_torch_tensor(dev(p["wq"]), dtype=FP4)
     ws = wrap_torch_tensor(dev(p["ws"]))
@@ -68,6 +68,8 @@ def run(p, device, layout, kernel="auto", block_m=None):
     cons = {"kernel": kernel}
     if block_m:
         cons["block_m"] = block_m
+    if block_n:
+        cons["block_n"] = block_n
     with tb.scoped_opt_flags_constraints(cons):
         y = tb.matmul(dev(p["x"]), wq, dev(p["bias"]), md, None, dev(p["gather"]), dev(p["scatter"]), pc,
                       betas=dev(p["betas"]), gammas=dev(p["gammas"]), fused_activation=fa)
@@ -97,16 +99,18 @@ SMALL = [
 
 @pytest.mark.parametrize("case", SMALL)
 @pytest.mark.parametrize("mode", ["plain", "gather", "scatter_w", "swiglu", "all"])
-@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256"])
+@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256", "tcgen05-256x256"])
 def test_grouped_gemm(case, mode, path, device):
     E, K, N, sizes, T = case
     opts = dict(plain=dict(gather=False), gather=dict(gather=True),
                 scatter_w=dict(gather=True, scatter=True, weights=True), swiglu=dict(gather=True, act=True),
                 all=dict(gather=True, scatter=True, weights=True, act=True))[mode]
     p = make_problem(E, K, N, sizes, T, seed=hash((E, K, N, mode)) % 1000, device=device, **opts)
-    layout, kernel, block_m = {"simt-canonical": ("canonical", "simt", None), "simt-blackwell": ("blackwell", "simt", None),
-                               "tcgen05": ("b200", "tcgen05", 128), "tcgen05-256": ("b200", "tcgen05", 256)}[path]
-    y = run(p, device, layout, kernel, block_m)
+    layout, kernel, block_m, block_n = {
+        "simt-canonical": ("canonical", "simt", None, None), "simt-blackwell": ("blackwell", "simt", None, None),
+        "tcgen05": ("b200", "tcgen05", 128, 128), "tcgen05-256": ("b200", "tcgen05", 256, 128),
+        "tcgen05-256x256": ("b200", "tcgen05", 256, 256)}[path]
+    y = run(p, device, layout, kernel, block_m, block_n)
     check(p, y)
 
 

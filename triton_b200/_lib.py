@@ -8,8 +8,11 @@ from pathlib import Path
 
 import torch
 
+import os
+
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libmoe_b200.so"
+# MOE_B200_LIB points at an alternative build of the library (e.g. an instrumented one)
+LIB_PATH = Path(os.environ["MOE_B200_LIB"]) if os.environ.get("MOE_B200_LIB") else _HERE / "libmoe_b200.so"
 
 MOE_F32, MOE_F16, MOE_BF16 = 0, 1, 2
 MOE_ROUND_UP, MOE_ROUND_DOWN = 0, 1
@@ -40,7 +43,7 @@ class MoeGemmArgs(C.Structure):
         ("out_alpha", f32), ("has_out_alpha", i32),
         ("activation", i32), ("act_alpha", f32), ("act_limit", f32), ("act_has_limit", i32),
         ("y", vp), ("y_dtype", i32), ("ld_y", i64),
-        ("kernel", i32), ("tile_m", i32), ("status", vp),
+        ("kernel", i32), ("tile_m", i32), ("tile_n", i32), ("status", vp),
     ]
 
 

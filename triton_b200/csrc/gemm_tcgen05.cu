@@ -23,35 +23,58 @@
 // returns, so a protocol error can not hang the device.
 #include "gemm_common.cuh"
 
+// Compile-time switches that knock out one pipeline role at a time (results become wrong); used only to
+// attribute time while tuning.  All zero in the shipped library.
+#ifndef MOE_PROBE_NO_A
+#define MOE_PROBE_NO_A 0
+#endif
+#ifndef MOE_PROBE_NO_DEQ
+#define MOE_PROBE_NO_DEQ 0
+#endif
+#ifndef MOE_PROBE_NO_MMA
+#define MOE_PROBE_NO_MMA 0
+#endif
+#ifndef MOE_PROBE_NO_EPI
+#define MOE_PROBE_NO_EPI 0
+#endif
+
 namespace {
 
 constexpr int HALF_M = 128;           // token rows of one MMA (MMA M)
-constexpr int BLOCK_N = 128;          // weight rows per tile (MMA N)
+constexpr int HALF_N = 128;           // weight rows of one weight tile in memory; a CTA tile spans NH of them
 constexpr int BLOCK_K = 64;           // k per pipeline stage: one 128-byte swizzle row of bf16
 constexpr int TILE_K = 128;           // k extent of a weight tile in global memory (two stages)
 constexpr int NUM_THREADS = 576;
 constexpr int LOADER_WARPS = 4, DEQUANT_WARPS = 8;
 constexpr int WARP_LOADER0 = 2, WARP_DEQ0 = 6, WARP_EPI0 = 14;
 constexpr int SUBTILE_BYTES = 128 * 128;                 // 128 rows x 128 bytes (64 bf16)
-constexpr int B_STAGE_BYTES = SUBTILE_BYTES;             // 16 KB
-constexpr int RAWV_BYTES = BLOCK_N * BLOCK_K / 2;        // 4 KB: half of an 8 KB weight tile ([2 groups][128 rows][16 B])
-constexpr int RAWS_BYTES = BLOCK_N * 4;                  // 512 B: the scale tile of the whole 128-k weight tile
+constexpr int RAWV_BYTES = HALF_N * BLOCK_K / 2;        // 4 KB: half of an 8 KB weight tile ([2 groups][128 rows][16 B])
+constexpr int RAWS_BYTES = HALF_N * 4;                  // 512 B: the scale tile of the whole 128-k weight tile
 constexpr int TMEM_COLS = 512;                           // two accumulator buffers of MH x 128 columns (256 used when MH = 1)
-constexpr int MAX_PREFIX_EXPERTS = 2048;                 // experts the 256-row tile schedule can index
+constexpr int MAX_PREFIX_EXPERTS = 512;                  // experts the 256-row tile schedule can index
+constexpr int PREFETCH_AHEAD = 12;                       // k steps the producer prefetches packed weights into L2
 
-// Shared-memory map for a tile of MH x 128 token rows.  MH = 1: 6 stages; MH = 2: 4 stages (the two halves
-// of a token tile share every dequantised weight stage, which halves the dequantiser work per FLOP).
-template <int MH> struct Cfg {
-  static constexpr int BLOCK_M = HALF_M * MH;
-  static constexpr int STAGES = MH == 1 ? 6 : 4;
+// Shared-memory map for a CTA tile of (MH x 128 token rows) x (NH x 128 weight rows), 64 k per stage.
+//   MH = 1, NH = 1: 6 stages, two accumulator buffers   (small problems: many CTAs, short tiles)
+//   MH = 2, NH = 1: 4 stages, two accumulator buffers
+//   MH = 2, NH = 2: 3 stages, one accumulator buffer    (prefill: most MMA work per pipeline hand-off)
+// The MH halves of a token tile share every dequantised weight stage, the NH halves share every activation stage.
+template <int MH, int NH> struct Cfg {
+  static constexpr int STAGES = (MH == 1) ? 6 : (NH == 1 ? 4 : 3);
+  static constexpr int RAW_STAGES = (NH == 1) ? 6 : 3;                  // ring of packed weight stages
+  static constexpr int ACC_BUFS = (MH * NH * 128 <= 256) ? 2 : 1;       // accumulator buffers in the 512 TMEM columns
+  static constexpr int ACC_COLS = MH * NH * 128;
   static constexpr int A_STAGE_BYTES = MH * SUBTILE_BYTES;
+  static constexpr int B_STAGE_BYTES = NH * SUBTILE_BYTES;
+  static constexpr int RAWV_STAGE = NH * RAWV_BYTES;
+  static constexpr int RAWS_STAGE = NH * RAWS_BYTES;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_STAGE_BYTES;
   static constexpr int OFF_RAWV = OFF_B + STAGES * B_STAGE_BYTES;
-  static constexpr int OFF_RAWS = OFF_RAWV + STAGES * RAWV_BYTES;
-  static constexpr int OFF_BIAS = OFF_RAWS + STAGES * RAWS_BYTES;       // float bias, [4 epilogue warps][128]
-  static constexpr int OFF_BAR = OFF_BIAS + 4 * BLOCK_N * 4;            // mbarriers
-  static constexpr int NUM_BARS = 5 * STAGES + 4 + 1;
+  static constexpr int OFF_RAWS = OFF_RAWV + RAW_STAGES * RAWV_STAGE;
+  static constexpr int OFF_BIAS = OFF_RAWS + RAW_STAGES * RAWS_STAGE;   // float bias, [4 epilogue warps][NH * 128]
+  static constexpr int OFF_BAR = OFF_BIAS + 4 * NH * HALF_N * 4;        // mbarriers
+  static constexpr int NUM_BARS = 3 * STAGES + 2 * RAW_STAGES + 4 + 1;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;               // tmem base, abort flag
   static constexpr int OFF_PREFIX = OFF_MISC + 16;                      // MH = 2: int32 tile prefix over experts
   static constexpr int SMEM_BYTES = OFF_PREFIX + (MH == 2 ? (MAX_PREFIX_EXPERTS + 1) * 4 : 0);
@@ -131,6 +154,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
@@ -154,15 +180,17 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 }
 
 // instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
-                           ((uint32_t)(HALF_M >> 4) << 24);
+__device__ __forceinline__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(HALF_M >> 4) << 24);
+}
 
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -257,10 +285,13 @@ __device__ __forceinline__ bool map_tile(const GemmParams& p, const int32_t* pre
   }
 }
 
-template <typename TY, int MH>
+template <typename TY, int MH, int NH>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static) {
-  using C = Cfg<MH>;
+  using C = Cfg<MH, NH>;
   constexpr int STAGES = C::STAGES;
+  constexpr int RAW_STAGES = C::RAW_STAGES;
+  constexpr int ACC_BUFS = C::ACC_BUFS;
+  constexpr int B_STAGE_BYTES = C::B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -268,13 +299,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
 
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR_RAW_FULL = [&](int s) { return bar0 + 8u * (uint32_t)s; };
-  auto BAR_RAW_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
-  auto BAR_A_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(2 * STAGES + s); };
-  auto BAR_B_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(3 * STAGES + s); };
-  auto BAR_AB_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(4 * STAGES + s); };
-  auto BAR_ACC_FULL = [&](int a) { return bar0 + 8u * (uint32_t)(5 * STAGES + a); };
-  auto BAR_ACC_EMPTY = [&](int a) { return bar0 + 8u * (uint32_t)(5 * STAGES + 2 + a); };
-  const uint32_t BAR_DRAIN = bar0 + 8u * (uint32_t)(5 * STAGES + 4);
+  auto BAR_RAW_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(RAW_STAGES + s); };
+  auto BAR_A_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(2 * RAW_STAGES + s); };
+  auto BAR_B_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(2 * RAW_STAGES + STAGES + s); };
+  auto BAR_AB_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(2 * RAW_STAGES + 2 * STAGES + s); };
+  auto BAR_ACC_FULL = [&](int a) { return bar0 + 8u * (uint32_t)(2 * RAW_STAGES + 3 * STAGES + a); };
+  auto BAR_ACC_EMPTY = [&](int a) { return bar0 + 8u * (uint32_t)(2 * RAW_STAGES + 3 * STAGES + 2 + a); };
+  const uint32_t BAR_DRAIN = bar0 + 8u * (uint32_t)(2 * RAW_STAGES + 3 * STAGES + 4);
 
   volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
@@ -282,9 +313,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   Ctl ctl{s_abort, p.status};
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < RAW_STAGES; ++s) {
       mbar_init(BAR_RAW_FULL(s), 1);
       mbar_init(BAR_RAW_EMPTY(s), DEQUANT_WARPS);
+    }
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(BAR_A_FULL(s), LOADER_WARPS * 32);
       mbar_init(BAR_B_FULL(s), DEQUANT_WARPS);
       mbar_init(BAR_AB_EMPTY(s), 1);
@@ -325,7 +358,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   const uint32_t tmem_base = *s_tmem;
 
   // ---- tile schedule shared by every role -----------------------------------------------------------
-  const int NT = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int NT128 = (p.N + HALF_N - 1) / HALF_N;        // weight tiles along n in memory
+  const int NT = (NT128 + NH - 1) / NH;                  // CTA tiles along n
   const int KT = (p.K + BLOCK_K - 1) / BLOCK_K;           // 64-k steps
   const int KT_TILES = (p.K + TILE_K - 1) / TILE_K;      // 128-k weight tiles per (expert, n tile)
   int64_t useful_m = grid_m_static;
@@ -341,11 +375,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         int e; int64_t row0; int rows;
         if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
         const int halves = rows > HALF_M ? 2 : 1;
-        const uint32_t ab = tc & 1u;
-        ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc >> 1) & 1u) ^ 1u, ctl, 101);
+        const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
+        const uint32_t idesc = make_idesc(nh_live * HALF_N);
+        const uint32_t ab = tc % ACC_BUFS;
+        ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc / ACC_BUFS) & 1u) ^ 1u, ctl, 101);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + ab * (MH * BLOCK_N);
+        const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -356,11 +392,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           const uint64_t adesc = make_desc(sbase + C::OFF_A + s * C::A_STAGE_BYTES);
           const uint64_t bdesc = make_desc(sbase + C::OFF_B + s * B_STAGE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), (kt | kk) ? 1u : 0u);
+          for (int kk = 0; kk < (MOE_PROBE_NO_MMA ? 0 : 4); ++kk) {
+            mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
             if (MH == 2 && halves == 2)
-              mma_bf16(d_tmem + BLOCK_N, adesc + (uint64_t)((SUBTILE_BYTES >> 4) + kk * 2), bdesc + (uint64_t)(kk * 2),
-                       (kt | kk) ? 1u : 0u);
+              mma_bf16(d_tmem + NH * HALF_N, adesc + (uint64_t)((SUBTILE_BYTES >> 4) + kk * 2),
+                       bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
           }
           mma_commit(BAR_AB_EMPTY(s));
         }
@@ -381,23 +417,45 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int e; int64_t row0; int rows;
         if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
-        const int nt = (int)(tile % NT);
-        const int64_t tile0 = ((int64_t)e * NT + nt) * KT_TILES;
+        const int nt0 = (int)(tile % NT) * NH;                   // first weight tile along n
+        const int nh_live = min(NH, NT128 - nt0);
+        const int64_t tile0 = ((int64_t)e * NT128 + nt0) * KT_TILES;
+        // the next tile of this CTA, so that its first weight stages can be pulled into L2 ahead of time
+        const uint8_t* next_wv = nullptr;
+        {
+          int e2; int64_t r2; int n2;
+          const int64_t t2 = tile + gridDim.x;
+          if (t2 < n_tiles && map_tile<MH>(p, s_prefix, t2 / NT, e2, r2, n2))
+            next_wv = wv + (((int64_t)e2 * NT128 + (int)(t2 % NT) * NH) * KT_TILES) * (2 * RAWV_BYTES);
+        }
+        const uint8_t* cur_wv = wv + tile0 * (2 * RAWV_BYTES);
+        const int64_t half_stride = (int64_t)KT_TILES * (2 * RAWV_BYTES);     // next weight tile along n
         for (int kt = 0; kt < KT; ++kt, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 201);
+          const int s = it % RAW_STAGES;
+          ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / RAW_STAGES) & 1u) ^ 1u, ctl, 201);
           if (!ok) break;
-          mbar_expect_tx(BAR_RAW_FULL(s), RAWV_BYTES + RAWS_BYTES);
+          {
+            const int kp = kt + PREFETCH_AHEAD;
+            for (int h = 0; h < nh_live; ++h) {
+              if (kp < KT) l2_prefetch(cur_wv + h * half_stride + (int64_t)kp * RAWV_BYTES, RAWV_BYTES);
+              else if (next_wv && kp - KT < KT) l2_prefetch(next_wv + h * half_stride + (int64_t)(kp - KT) * RAWV_BYTES, RAWV_BYTES);
+            }
+          }
+          mbar_expect_tx(BAR_RAW_FULL(s), (uint32_t)nh_live * (RAWV_BYTES + RAWS_BYTES));
           // stage kt is half (kt & 1) of weight tile kt >> 1: 4 KB of values, plus the tile's 512 scale bytes
-          bulk_g2s(sbase + C::OFF_RAWV + s * RAWV_BYTES, wv + (tile0 * 2 + kt) * RAWV_BYTES, RAWV_BYTES, BAR_RAW_FULL(s));
-          bulk_g2s(sbase + C::OFF_RAWS + s * RAWS_BYTES, ws + (tile0 + (kt >> 1)) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
+          for (int h = 0; h < nh_live; ++h) {
+            bulk_g2s(sbase + C::OFF_RAWV + s * C::RAWV_STAGE + h * RAWV_BYTES, cur_wv + h * half_stride + (int64_t)kt * RAWV_BYTES,
+                     RAWV_BYTES, BAR_RAW_FULL(s));
+            bulk_g2s(sbase + C::OFF_RAWS + s * C::RAWS_STAGE + h * RAWS_BYTES,
+                     ws + (tile0 + (int64_t)h * KT_TILES + (kt >> 1)) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
+          }
         }
       }
       if (!ok) {
         // aborting: let the copies that were already issued land before the CTA leaves
-        const uint32_t lo = it > (uint32_t)STAGES ? it - STAGES : 0;
+        const uint32_t lo = it > (uint32_t)RAW_STAGES ? it - RAW_STAGES : 0;
         for (uint32_t j = lo; j < it; ++j)
-          for (uint32_t i = 0; i < (1u << 16) && !mbar_test(BAR_RAW_FULL(j % STAGES), (j / STAGES) & 1u); ++i) __nanosleep(64);
+          for (uint32_t i = 0; i < (1u << 16) && !mbar_test(BAR_RAW_FULL(j % RAW_STAGES), (j / RAW_STAGES) & 1u); ++i) __nanosleep(64);
       }
     }
     __syncwarp();
@@ -448,7 +506,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         const uint32_t kc16 = (uint32_t)(k >> 3);
 #pragma unroll
         for (int i = 0; i < NR; ++i) {
-          if (i < nr_live) {
+          if (i < nr_live && !MOE_PROBE_NO_A) {
             const bool live = src16[i] != 0xFFFFFFFFu && kbytes;
             const uint8_t* g = live ? Xb + ((uint64_t)(src16[i] + kc16) << 4) : Xb;
             cp_async16(stage + dst_off[i], g, live ? kbytes : 0u);
@@ -460,52 +518,68 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     cp_async_wait_all();
   } else if (warp < WARP_EPI0) {
     // ================================= dequantiser ======================================================
-    // 256 threads, one (row, 32-k scale group) unit each per stage: one 16-byte load, one scale byte, four
-    // 16-byte swizzled stores.  A quarter-warp holds one group of 8 consecutive rows, which keeps the load
-    // (128 contiguous bytes) and the stores (8 distinct 16-byte columns) free of bank conflicts.
+    // 256 threads; a unit is one (weight row, 32-k scale group): one 16-byte load, one scale byte, four 16-byte
+    // swizzled stores.  Every thread takes one unit of each of the NH weight tiles of the stage.  A quarter-warp
+    // holds one group of 8 consecutive rows, which keeps the load (128 contiguous bytes) and the stores
+    // (8 distinct 16-byte columns) free of bank conflicts.
     const int dw = warp - WARP_DEQ0;                // 0..7
     const int g = (lane >> 3) & 1;                  // scale group inside the 64-k stage
     const int r = dw * 16 + (lane >> 4) * 8 + (lane & 7);
     const int x7 = r & 7;
-    const uint32_t row_off = (uint32_t)(r * 128);
     uint32_t it = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int e; int64_t row0; int rows;
       if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
+      const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
-        ok = __all_sync(0xFFFFFFFFu,
-                        mbar_wait(BAR_RAW_FULL(s), ph, ctl, 401) && mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
+        const int rs = it % RAW_STAGES;
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_RAW_FULL(rs), (it / RAW_STAGES) & 1u, ctl, 401) &&
+                                         mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
         if (!ok) break;
-        const uint4 raw = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + s * RAWV_BYTES)[g * BLOCK_N + r];
-        const uint32_t sb = (smem + C::OFF_RAWS + s * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
-        uint8_t* row = smem + C::OFF_B + s * B_STAGE_BYTES + row_off;
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        if (sb <= 128u) {
-          const uint32_t c = sb ? ((sb + 126u) << 7) : 0u;
-          const uint32_t c2 = c * 0x10001u;
+        uint4 raw[NH];
+        uint32_t sb[NH];
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
-        } else {
+        for (int h = 0; h < NH; ++h) {
+          if (h < nh_live) {
+            raw[h] = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE + h * RAWV_BYTES)[g * HALF_N + r];
+            sb[h] = (smem + C::OFF_RAWS + rs * C::RAWS_STAGE + h * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
+          }
+        }
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sb);
+        for (int h = 0; h < NH; ++h) {
+          if (h < nh_live) {
+            uint8_t* row = smem + C::OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES + r * 128;
+            const uint32_t w[4] = {raw[h].x, raw[h].y, raw[h].z, raw[h].w};
+            if (MOE_PROBE_NO_DEQ) {
+            } else if (sb[h] <= 128u) {
+              const uint32_t c = sb[h] ? ((sb[h] + 126u) << 7) : 0u;
+              const uint32_t c2 = c * 0x10001u;
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sb[h]);
+            }
+          }
         }
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(BAR_B_FULL(s));
-          mbar_arrive(BAR_RAW_EMPTY(s));
+          mbar_arrive(BAR_RAW_EMPTY(rs));
         }
       }
     }
   } else {
     // ================================= epilogue =========================================================
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
-    float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + q * BLOCK_N;   // private to this warp
+    constexpr int TILE_N = NH * HALF_N;
+    float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + q * TILE_N;    // private to this warp
     TY* Y = (TY*)p.y;
     const bool swiglu = p.activation == MOE_ACT_SWIGLU;
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
@@ -515,17 +589,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       int e; int64_t row0; int rows;
       if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
       const int halves = rows > HALF_M ? 2 : 1;
-      const int n0 = (int)(tile % NT) * BLOCK_N;
-      const uint32_t ab = tc & 1u;
+      const int n0 = (int)(tile % NT) * TILE_N;
+      const uint32_t ab = tc % ACC_BUFS;
       // stage this tile's bias columns (each warp keeps its own copy: no CTA-level barrier in this role)
       __syncwarp();
 #pragma unroll
-      for (int jb = 0; jb < BLOCK_N / 32; ++jb) {
+      for (int jb = 0; jb < TILE_N / 32; ++jb) {
         const int gn = n0 + jb * 32 + lane;
         s_bias[jb * 32 + lane] = (p.bias && gn < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + gn) : 0.0f;
       }
       __syncwarp();
-      ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc >> 1) & 1u, ctl, 501));
+      ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc / ACC_BUFS) & 1u, ctl, 501));
       if (!ok) break;
       tc_fence_after();
       for (int h = 0; h < halves; ++h) {
@@ -540,13 +614,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           if (p.gammas) gamma = p.gammas[m];
         }
         const bool store_row = row_live && dst >= 0;
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * (MH * BLOCK_N) + h * BLOCK_N;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * C::ACC_COLS + h * TILE_N;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+        for (int c0 = 0; c0 < TILE_N; c0 += 32) {
           uint32_t raw[32];
           tmem_ld32(taddr + (uint32_t)c0, raw);
           tmem_ld_wait();
-          if (!store_row || n0 + c0 >= p.N) continue;
+          if (!store_row || n0 + c0 >= p.N || MOE_PROBE_NO_EPI) continue;
           float v[32];
 #pragma unroll
           for (int jx = 0; jx < 32; ++jx) {
@@ -594,6 +668,7 @@ bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why) {
   if ((uintptr_t)a.w % 16 != 0 || (uintptr_t)a.w_scale % 16 != 0) { *why = "weights are not 16-byte aligned"; return false; }
   if ((double)a.rows_x * (double)a.ld_x * 2.0 >= 68719476736.0 * 0.99) { *why = "activations exceed 64 GB"; return false; }
   if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256) { *why = "tile_m must be 0, 128 or 256"; return false; }
+  if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256) { *why = "tile_n must be 0, 128 or 256"; return false; }
   *why = "";
   return true;
 }
@@ -605,23 +680,35 @@ static int64_t n_blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
   return n_slices - 1 + (a + block - 1) / block;
 }
 
-template <typename TY, int MH>
+template <typename TY, int MH, int NH>
 static int launch_tc(const GemmParams& p, int64_t grid_m, int64_t N, cudaStream_t st) {
-  const int64_t tiles = grid_m * cdiv64(N, BLOCK_N);
+  const int64_t tiles = grid_m * cdiv64(N, HALF_N * NH);
   const int sms = moe_sm_count();
   const int grid = (int)(tiles < sms ? tiles : sms);
-  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TY, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MH>::SMEM_ALLOC));
-  gemm_tc_kernel<TY, MH><<<grid, NUM_THREADS, Cfg<MH>::SMEM_ALLOC, st>>>(p, grid_m);
+  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TY, MH, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg<MH, NH>::SMEM_ALLOC));
+  gemm_tc_kernel<TY, MH, NH><<<grid, NUM_THREADS, Cfg<MH, NH>::SMEM_ALLOC, st>>>(p, grid_m);
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }
 
+template <typename TY>
+static int launch_tc_shape(const GemmParams& p, int mh, int nh, int64_t grid_m, int64_t N, cudaStream_t st) {
+  if (mh == 2 && nh == 2) return launch_tc<TY, 2, 2>(p, grid_m, N, st);
+  if (mh == 2) return launch_tc<TY, 2, 1>(p, grid_m, N, st);
+  return launch_tc<TY, 1, 1>(p, grid_m, N, st);
+}
+
 int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_t st) {
   GemmParams p = p_in;
-  // 256-row token tiles halve the dequantiser work per FLOP; they pay off once experts hold more than a
-  // block or two of rows.  128-row tiles keep small problems (decode) spread over more CTAs.
-  int mh = a.tile_m == 256 ? 2 : (a.tile_m == 128 ? 1 : ((a.M / (a.E > 0 ? a.E : 1)) >= 192 ? 2 : 1));
+  // Tile shape.  256-row token tiles halve the dequantiser work per FLOP and 256-wide weight tiles halve the
+  // activation traffic and double the MMA work per pipeline hand-off; both pay off once experts hold more than
+  // a block or two of rows.  128 x 128 tiles keep small problems (decode) spread over more CTAs.
+  const int64_t rows_per_expert = a.M / (a.E > 0 ? a.E : 1);
+  int mh = a.tile_m == 256 ? 2 : (a.tile_m == 128 ? 1 : (rows_per_expert >= 192 ? 2 : 1));
   if (mh == 2 && a.slice_sizes && a.E > MAX_PREFIX_EXPERTS) mh = 1;
+  int nh = a.tile_n == 256 ? 2 : (a.tile_n == 128 ? 1 : ((mh == 2 && a.N >= 1024) ? 2 : 1));
+  if (mh == 1) nh = 1;
   int64_t grid_m;
   if (a.slice_sizes) {
     p.block_offs = a.block_offs_16 + 3 * a.ld_block_offs;      // block size 128
@@ -631,7 +718,6 @@ int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
     grid_m = cdiv64(a.M, 128 * mh);
   }
   if (grid_m == 0) return MOE_OK;
-  if (a.y_dtype == MOE_BF16)
-    return mh == 2 ? launch_tc<__nv_bfloat16, 2>(p, grid_m, a.N, st) : launch_tc<__nv_bfloat16, 1>(p, grid_m, a.N, st);
-  return mh == 2 ? launch_tc<float, 2>(p, grid_m, a.N, st) : launch_tc<float, 1>(p, grid_m, a.N, st);
+  if (a.y_dtype == MOE_BF16) return launch_tc_shape<__nv_bfloat16>(p, mh, nh, grid_m, a.N, st);
+  return launch_tc_shape<float>(p, mh, nh, grid_m, a.N, st);
 }

@@ -13,7 +13,8 @@ import torch
 
 from . import _lib
 from .matmul_details.opt_flags import (InapplicableConstraint, reset_opt_flags_constraints,  # noqa: F401
-                                       resolve_kernel_choice, resolve_tile_m, scoped_opt_flags_constraints, set_idle_sms,
+                                       resolve_kernel_choice, resolve_tile_m, resolve_tile_n,
+                                       scoped_opt_flags_constraints, set_idle_sms,
                                        update_opt_flags_constraints)
 from .numerics import InFlexData, OutFlexData
 from .specialize import FnSpecs
@@ -282,7 +283,7 @@ def matmul(a, b, bias,
         args.act_limit, args.act_has_limit = (float(limit), 1) if limit is not None else (0.0, 0)
     args.y, args.y_dtype, args.ld_y = c.data_ptr(), _lib.dtype_code(c.dtype), c.stride(0)
     args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05}[kernel_choice]
-    args.tile_m = resolve_tile_m()
+    args.tile_m, args.tile_n = resolve_tile_m(), resolve_tile_n()
     args.status = _status_word(dev).data_ptr()
     st = lib.moe_grouped_gemm(args, _lib.stream())
     if st == 3:

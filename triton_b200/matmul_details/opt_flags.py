@@ -55,6 +55,12 @@ def resolve_tile_m() -> int:
     return bm if bm in (128, 256) else 0
 
 
+def resolve_tile_n() -> int:
+    """`block_n` constraint -> weight rows per tile of the tensor-core kernel (0 = heuristic)."""
+    bn = get_opt_flags_constraints().get("block_n")
+    return bn if bn in (128, 256) else 0
+
+
 def resolve_kernel_choice() -> str:
     c = get_opt_flags_constraints()
     for k, v in c.items():
