@@ -69,7 +69,7 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            time.sleep(0.05)
+            time.sleep(0.005)
 
     def __enter__(self):
         if self.nv is not None:
@@ -288,14 +288,22 @@ def main():
     barrier()
     gemm_ms = [sum(e0.elapsed_time(e1) for e0, e1 in gt.spans)]
     n_gemm = [len(gt.spans)]
-    rows_local = T * world * TOP_K / world        # routed rows this rank multiplies (uniform expert ownership: average)
-    if world == 1:
-        rows_local = T * TOP_K
+    rows_local = T * TOP_K                        # routed rows this rank multiplies (average under uniform ownership)
     flop_per_step = rows_local * (FLOP_PER_ROW_FC1 + FLOP_PER_ROW_FC2)
     gemm_ms_per_step = gemm_ms[0] / args.steps
     achieved_tflops = flop_per_step / (gemm_ms_per_step * 1e-3) / 1e12
     peaks = measured_peaks()
     traffic = gemm_traffic_note()
+    # weight streaming: bytes of the experts that received at least one row (W1 + S1 + W2 + S2 + biases), per step
+    sp = tb.topk(logits, TOP_K) if world == 1 else None
+    if sp is not None:
+        n_active = int((sp.mask_metadata.col_sum > 0).sum().item())
+    else:
+        n_active = E_local
+    bytes_per_expert = (D_MODEL * 2 * D_FF + D_FF * D_MODEL) // 2 + (D_MODEL * 2 * D_FF + D_FF * D_MODEL) // 32 + \
+        (2 * D_FF + D_MODEL) * 2
+    act_bytes = rows_local * (D_MODEL * 2 + D_FF * 2 * 2 + D_MODEL * 2)
+    stream_gbs = (n_active * bytes_per_expert + act_bytes) / (gemm_ms_per_step * 1e-3) / 1e9
     roofline = {
         "bound": "tensor", "kernel": "gemm_tc_kernel (fc1 + fc2 launches of a step, bf16 kind::f16 after in-SM dequant)",
         "achieved": achieved_tflops, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
@@ -303,7 +311,13 @@ def main():
         "traffic": None if traffic is None else traffic.get("dram_bytes_per_step"),
         "ms_per_step_in_kernel": gemm_ms_per_step, "launches_per_step": n_gemm[0] / args.steps,
         "frac_of_inferred_mxfp4_peak": achieved_tflops / (4 * peaks["bf16_tflops_sustained"]),
+        "hbm": {"active_experts": n_active, "algorithmic_gbs": stream_gbs, "peak_gbs": peaks["hbm_gbs"],
+                "frac": stream_gbs / peaks["hbm_gbs"]},
     }
+    if T <= 256:        # decode regime: the grouped GEMM streams weights, HBM is the bound
+        roofline.update({"bound": "hbm", "achieved": stream_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": stream_gbs / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth",
+                         "tflops": achieved_tflops})
 
     # ---- end to end: host buffers in, host result out, through the public API ---------------------------
     e2e = None

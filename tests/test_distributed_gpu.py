@@ -1,0 +1,81 @@
+"""Expert-parallel MoE layer on 2 (or 4) GPUs, one process per GPU over NCCL, against the single-GPU layer
+(the reference's tests/test_distributed.py:325-342 compares the same pair)."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import oracle
+        import triton_b200 as tb
+        from triton_b200.moe import MoeLayerWeights, moe_layer_forward, moe_layer_forward_ep
+        from triton_b200.testing import make_synthetic_layer
+        from triton_b200.tensor import FP4, convert_layout, wrap_torch_tensor
+        from triton_b200.tensor_details.layout import B200MXScaleLayout, B200MXValueLayout
+        torch.manual_seed(0)
+        lw = make_synthetic_layer(n_expts, d_model, d_ff, dev, seed=0, keep_canonical=True)     # same on every rank
+        x = torch.randn(n_tokens, d_model, device=dev).bfloat16()
+        logits = torch.randn(n_tokens, n_expts, device=dev)
+        z_ref = moe_layer_forward(x, logits, lw, k)
+        expt_dict = (tb.make_expt_dict_uniform if mode == "uniform" else tb.make_expt_dict_random)(world, n_expts)
+        assign = tb.make_expt_assignment(world, n_expts, expt_dict, dev)
+        mine = assign.expt_boolmask[rank]
+
+        def shard(q, s):
+            tq = convert_layout(wrap_torch_tensor(q[mine].transpose(1, 2).contiguous().transpose(1, 2), dtype=FP4), B200MXValueLayout())
+            ts = convert_layout(wrap_torch_tensor(s[mine].transpose(1, 2).contiguous().transpose(1, 2)), B200MXScaleLayout())
+            return tq, ts
+
+        w1, s1 = shard(lw.w1_q, lw.w1_s)
+        w2, s2 = shard(lw.w2_q, lw.w2_s)
+        lw_local = MoeLayerWeights(w1, s1, lw.b1[mine].contiguous(), w2, s2, lw.b2[mine].contiguous())
+        pool = tb.SymmetricMemoryPool(tb.Mesh(dist.group.WORLD))
+        pool.initialize_matmul(n_tokens, d_model, d_model, k, n_expts, torch.bfloat16, dev)
+        T_local = n_tokens // world
+        sl = slice(rank * T_local, (rank + 1) * T_local)
+        for _ in range(2):                                  # twice: buffers and plans are rebuilt per call
+            z_loc = moe_layer_forward_ep(x[sl].contiguous(), logits[sl].contiguous(), lw_local, k, assign, pool)
+        tb.matmul_check_status()
+        z_all = torch.empty_like(z_ref)
+        dist.all_gather_into_tensor(z_all, z_loc)
+        oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3, what="EP vs single GPU")
+        ret[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("n_tokens, d_model, d_ff, n_expts, k, mode", [
+    (16, 64, 64, 4, 4, "uniform"),
+    (128, 512, 256, 16, 4, "random"),
+    (4096, 2880, 2880, 128, 4, "uniform"),
+])
+def test_expert_parallel_layer_matches_single_gpu(world, n_tokens, d_model, d_ff, n_expts, k, mode):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = 29700 + (os.getpid() + world * 7 + n_tokens) % 2000
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    codes = [p.exitcode for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert codes == [0] * world, codes
+    assert sorted(ret.keys()) == list(range(world))
