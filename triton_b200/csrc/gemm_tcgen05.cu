@@ -264,7 +264,7 @@ template <typename TY, int N> __device__ __forceinline__ void store_out(TY* dst,
 // =========================================================================================================
 // Token-tile -> (expert, first row, valid rows).  MH = 1 follows the block schedule for blocks of 128 rows.
 // MH = 2 pairs consecutive 128-row blocks of one expert: tile j of expert e covers rows [256 j, 256 j + 256);
-// `prefix` (shared memory) holds the exclusive prefix of ceil(blocks128(e) / 2) over experts.
+// `prefix` (shared memory) holds the exclusive prefix of ceil(slice_sizes[e] / 256) over experts.
 template <int MH>
 __device__ __forceinline__ bool map_tile(const GemmParams& p, const int32_t* prefix, int64_t pid_m, int& e,
                                          int64_t& row0, int& rows) {
@@ -337,10 +337,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if constexpr (MH == 2) {
-    // tile prefix over experts: number of 256-row tiles of expert e = ceil(blocks128(e) / 2)
+    // tile prefix over experts: expert e has ceil(slice_sizes[e] / 256) tiles.  (Taken from the sizes, not from
+    // differences of block_offs: after an expert-parallel remap block_offs keeps global cumulative values.)
     if (p.slice_sizes != nullptr) {
       for (int e = threadIdx.x; e < p.E; e += NUM_THREADS)
-        s_prefix[e + 1] = (p.block_offs[e + 1] - p.block_offs[e] + 1) >> 1;
+        s_prefix[e + 1] = (max(p.slice_sizes[e], 0) + 2 * HALF_M - 1) / (2 * HALF_M);
       __syncthreads();
       if (threadIdx.x == 0) {
         int run = 0;

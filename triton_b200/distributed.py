@@ -103,9 +103,16 @@ class SymmetricMemoryPool:
         """In-place all-gather of the routing outputs: rank r's rows are [r * T_local, (r+1) * T_local)."""
         g = self.mesh.process_group
         W = self.mesh.world_size
-        dist.all_gather_into_tensor(y_vals, y_vals[rank * T_local:(rank + 1) * T_local].clone(), group=g)
+
+        def gather_rows(buf):
+            # byte views: NCCL has no 16-bit integer type
+            full = buf[:W * T_local].view(torch.uint8)
+            mine = buf[rank * T_local:(rank + 1) * T_local].view(torch.uint8).clone()
+            dist.all_gather_into_tensor(full.reshape(-1), mine.reshape(-1), group=g)
+
+        gather_rows(y_vals)
         if y_indx is not None:
-            dist.all_gather_into_tensor(y_indx[:W * T_local], y_indx[rank * T_local:(rank + 1) * T_local].clone(), group=g)
+            gather_rows(y_indx)
         words = bm_store.shape[0]
         loc = bm_store[:, rank * T_local:(rank + 1) * T_local].t().contiguous()      # [T_local, words]
         allr = torch.empty((W * T_local, words), dtype=bm_store.dtype, device=bm_store.device)
