@@ -182,6 +182,12 @@ int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
  * Local halves of convert_dp_to_ep / convert_ep_to_dp (distributed.py:176-211, 256-283): the
  * exchange itself is an NCCL all-to-all issued by the host shim; these kernels pack rows into
  * per-destination contiguous, expert-sorted order and unpack them.                                 */
+/* Exchange keys: keys[p] = (home rank of the token at expert-sorted position p) * world + (rank owning its
+ * expert), -1 for padding.  col_sorted is the global col_sorted_indx [n], expt_indx the global [T, k] int16
+ * expert ids (flat), owner[e] the rank of expert e, entries_per_rank = T_local * k.  Sorting the positions by
+ * this key (moe_bitmatrix_metadata with E = world^2, k = 1) yields the order rows travel in.           */
+int moe_ep_keys(const int32_t* col_sorted, const int16_t* expt_indx, const int32_t* owner, int64_t n,
+                int entries_per_rank, int world, int16_t* keys, void* stream);
 int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
                     void* dst, int64_t ld_dst, void* stream);
 int moe_scatter_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_in, int64_t row_bytes,

@@ -79,3 +79,23 @@ def test_expert_parallel_layer_matches_single_gpu(world, n_tokens, d_model, d_ff
             p.kill()
     assert codes == [0] * world, codes
     assert sorted(ret.keys()) == list(range(world))
+
+
+@pytest.mark.parametrize("T_global, E, k, W", [(64, 16, 4, 4), (4096, 128, 4, 8), (1000, 37, 2, 2)])
+def test_cuda_exchange_plan_equals_torch_plan(T_global, E, k, W):
+    """The CUDA plan (key kernel + counting sort) against the index arithmetic written with torch ops."""
+    import triton_b200 as tb
+    from triton_b200.distributed import expert_owner, make_exchange_plan, make_exchange_plan_cuda
+    dev = "cuda"
+    torch.manual_seed(T_global)
+    logits = torch.randn(T_global, E, device=dev)
+    sp = tb.topk(logits, k)
+    col = sp.mask_metadata.col_sorted_indx
+    assign = tb.make_expt_assignment(W, E, tb.make_expt_dict_random(W, E), dev)
+    T_local = T_global // W
+    plan = make_exchange_plan_cuda(sp.indx, col, assign, W, T_local)
+    order, counts, flat = make_exchange_plan(sp.indx, col.long(), expert_owner(assign), W, T_local)
+    n = order.numel()
+    assert torch.equal(plan.order[:n].long(), order) and (plan.order[n:] == -1).all()
+    assert torch.equal(plan.flat[:n].long(), flat)
+    assert torch.equal(plan.counts_host, counts.cpu())

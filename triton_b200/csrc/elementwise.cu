@@ -242,3 +242,37 @@ extern "C" __attribute__((visibility("default"))) int moe_scatter_rows(const voi
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Expert-parallel exchange keys.  For every expert-sorted position p (col_sorted[p] = flat token * k + slot, or
+// -1): key[p] = source_rank * world + destination_rank, where the source rank is the home of the token and the
+// destination rank the owner of the expert.  A stable sort of the positions by this key (done with the same
+// counting sort as the expert sort) is the order in which rows travel in both all-to-all exchanges.
+namespace {
+__global__ void __launch_bounds__(256) ep_keys_kernel(const int32_t* __restrict__ col_sorted,
+                                                      const int16_t* __restrict__ expt_indx,
+                                                      const int32_t* __restrict__ owner, int64_t n, int entries_per_rank,
+                                                      int world, int16_t* __restrict__ keys) {
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t flat = col_sorted[p];
+    int16_t key = -1;
+    if (flat >= 0) {
+      const int e = expt_indx[flat];
+      key = (int16_t)((flat / entries_per_rank) * world + owner[e]);
+    }
+    keys[p] = key;
+  }
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_ep_keys(const int32_t* col_sorted, const int16_t* expt_indx,
+                                                                  const int32_t* owner, int64_t n, int entries_per_rank,
+                                                                  int world, int16_t* keys, void* stream) {
+  MOE_CHECK_ARG(n >= 0 && entries_per_rank > 0 && world > 0 && world * world < 32768, "moe_ep_keys: bad extents");
+  if (n == 0) return MOE_OK;
+  MOE_CHECK_ARG(col_sorted && expt_indx && owner && keys, "moe_ep_keys: NULL pointer");
+  ep_keys_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(col_sorted, expt_indx, owner, n, entries_per_rank,
+                                                                      world, keys);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}

@@ -157,17 +157,67 @@ def _starts(counts):
     return (torch.cumsum(c, 0) - c).view_as(counts)
 
 
+@dataclass
+class ExchangePlan:
+    """Everything both exchanges of a layer need, computed once from the replicated routing metadata."""
+    order: torch.Tensor        # [n] int32: expert-sorted positions in travel order (source, destination, position); -1 tail
+    flat: torch.Tensor         # [n] int32: flat (token * k + slot) index of order[i]
+    counts_host: torch.Tensor  # [W, W] int64 on the host: rows rank s sends to rank d
+    starts_host: torch.Tensor  # [W, W] exclusive prefix of counts in (s, d) order
+
+
+def make_exchange_plan_cuda(expt_indx, col_sorted_indx, expt_assignment, world_size, n_tokens_local) -> ExchangePlan:
+    """CUDA version of `make_exchange_plan`: one key kernel, then the library's stable counting sort with
+    world^2 buckets; the only host synchronisation is the read of the W x W count matrix."""
+    lib = _lib.load()
+    dev = col_sorted_indx.device
+    k = expt_indx.shape[1]
+    n = col_sorted_indx.numel()
+    owner = expert_owner(expt_assignment).to(torch.int32)
+    indx16 = expt_indx if expt_indx.dtype == torch.int16 else expt_indx.to(torch.int16)
+    indx16 = indx16.contiguous()
+    col = col_sorted_indx.reshape(-1).to(torch.int32).contiguous()
+    keys = torch.empty(n, dtype=torch.int16, device=dev)
+    _lib.check(lib.moe_ep_keys(_lib.ptr(col), _lib.ptr(indx16), _lib.ptr(owner), n, k * n_tokens_local, world_size,
+                               _lib.ptr(keys), _lib.stream()), "moe_ep_keys")
+    buckets = world_size * world_size
+    counts = torch.empty(buckets, dtype=torch.int32, device=dev)
+    order = torch.empty(n, dtype=torch.int32, device=dev)
+    rank_of = torch.empty(n, dtype=torch.int32, device=dev)
+    ws_bytes = lib.moe_bitmatrix_metadata_workspace(n, buckets, 1)
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    _lib.check(lib.moe_bitmatrix_metadata(_lib.ptr(keys), 1, n, buckets, 1, None, _lib.ptr(counts), _lib.ptr(order),
+                                          _lib.ptr(rank_of), _lib.ptr(ws), ws_bytes, _lib.stream()),
+               "moe_bitmatrix_metadata (exchange plan)")
+    flat = col[order.long().clamp_min(0)]
+    counts_h = counts.cpu().to(torch.int64).view(world_size, world_size)
+    return ExchangePlan(order, flat, counts_h, _starts(counts_h))
+
+
+def _plan_from_torch(expt_indx, col_sorted_indx, expt_assignment, W, T_local) -> ExchangePlan:
+    order, counts, flat = make_exchange_plan(expt_indx, col_sorted_indx.reshape(-1), expert_owner(expt_assignment), W, T_local)
+    counts_h = counts.cpu()
+    return ExchangePlan(order.to(torch.int32), flat.to(torch.int32), counts_h, _starts(counts_h))
+
+
 def _rows_call(fn, src, indx, n, dst):
     row_bytes = src.shape[1] * src.element_size()
     _lib.check(fn(_lib.ptr(src), src.stride(0) * src.element_size(), _lib.ptr(indx), n, row_bytes, _lib.ptr(dst),
                   dst.stride(0) * dst.element_size(), _lib.stream()), "moe_gather_rows/moe_scatter_rows")
 
 
+def _segments(plan, rank, W, column):
+    """travel-order slices [start, start + count) that rank `rank` receives (column=True: from every source s)
+    or holds as an expert owner; concatenated in rank order"""
+    return [(int(plan.starts_host[s, rank]), int(plan.counts_host[s, rank])) for s in range(W)]
+
+
 def convert_dp_to_ep(src, expt_assignment, expt_indx, gate_indx, symm_mem_pool: SymmetricMemoryPool,
-                     col_sorted_indx=None):
+                     col_sorted_indx=None, plan: ExchangePlan | None = None):
     """src [T_local, d] (this rank's tokens) -> [T_global * k, d] in global expert-sorted order, filled at
     the rows whose expert lives on this rank (other rows are left unwritten).  `gate_indx` is the global
-    row_sorted_indx (flat index -> sorted position); `col_sorted_indx` (its inverse) is derived when absent."""
+    row_sorted_indx (flat index -> sorted position); `col_sorted_indx` (its inverse) is derived when absent.
+    `plan` (from `make_exchange_plan_cuda`) is computed here when not supplied."""
     lib = _lib.load()
     mesh = symm_mem_pool.mesh
     W, rank = mesh.world_size, mesh.local_rank
@@ -176,40 +226,38 @@ def convert_dp_to_ep(src, expt_assignment, expt_indx, gate_indx, symm_mem_pool: 
     assert T_local * W <= T_global
     dev = src.device
     n = T_global * k
-    if col_sorted_indx is None:
-        col_sorted_indx = torch.full((n,), -1, dtype=torch.int64, device=dev)
-        g = gate_indx.reshape(-1).long()
-        ok = g >= 0
-        col_sorted_indx[g[ok]] = torch.nonzero(ok).flatten()
-    owner = expert_owner(expt_assignment)
-    order, counts, flat = make_exchange_plan(expt_indx, col_sorted_indx.reshape(-1), owner, W, T_local)
-    counts_h = counts.cpu()
-    starts_h = _starts(counts_h)
+    if plan is None:
+        if col_sorted_indx is None:
+            col_sorted_indx = torch.full((n,), -1, dtype=torch.int32, device=dev)
+            g = gate_indx.reshape(-1).long()
+            ok = g >= 0
+            col_sorted_indx[g[ok]] = torch.nonzero(ok).flatten().to(torch.int32)
+        plan = make_exchange_plan_cuda(expt_indx, col_sorted_indx, expt_assignment, W, T_local)
     dst = torch.empty((n, d), dtype=src.dtype, device=dev)
-    send_lo = int(starts_h[rank, 0])
-    n_send = int(counts_h[rank].sum())
+    send_counts = plan.counts_host[rank].tolist()
+    send_lo, n_send = int(plan.starts_host[rank, 0]), sum(send_counts)
     # pack: local token of each outgoing row, in (destination, position) order
-    tok_local = (torch.div(flat[send_lo:send_lo + n_send], k, rounding_mode="floor") - rank * T_local).to(torch.int32)
+    tok_local = torch.div(plan.flat[send_lo:send_lo + n_send], k, rounding_mode="floor") - rank * T_local
     sendbuf = torch.empty((n_send, d), dtype=src.dtype, device=dev)
     if n_send:
-        _rows_call(lib.moe_gather_rows, src, tok_local, n_send, sendbuf)
-    recv_counts = counts_h[:, rank].tolist()
+        _rows_call(lib.moe_gather_rows, src, tok_local.to(torch.int32), n_send, sendbuf)
+    recv_counts = plan.counts_host[:, rank].tolist()
     n_recv = sum(recv_counts)
-    recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
     if W > 1:
-        dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=recv_counts,
-                               input_split_sizes=counts_h[rank].tolist(), group=mesh.process_group)
+        recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
+        dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                               group=mesh.process_group)
     else:
         recvbuf = sendbuf
     # unpack: received row i belongs at sorted position pos[i]
-    pos = torch.cat([order[int(starts_h[s, rank]):int(starts_h[s, rank]) + recv_counts[s]] for s in range(W)]) \
-        if n_recv else torch.empty(0, dtype=torch.int64, device=dev)
     if n_recv:
-        _rows_call(lib.moe_scatter_rows, recvbuf, pos.to(torch.int32), n_recv, dst)
+        pos = torch.cat([plan.order[lo:lo + c] for lo, c in _segments(plan, rank, W, True)])
+        _rows_call(lib.moe_scatter_rows, recvbuf, pos, n_recv, dst)
     return dst
 
 
-def convert_ep_to_dp(src, expt_assignment, expt_indx, topk_indx, symm_mem_pool: SymmetricMemoryPool):
+def convert_ep_to_dp(src, expt_assignment, expt_indx, topk_indx, symm_mem_pool: SymmetricMemoryPool,
+                     plan: ExchangePlan | None = None):
     """src [T_global * k, d] in expert-sorted order (valid at this rank's experts) -> [T_local * k, d]: row
     (t_local * k + slot) is the output of the expert in that slot.  `topk_indx` is the global
     col_sorted_indx (sorted position -> flat index)."""
@@ -220,29 +268,26 @@ def convert_ep_to_dp(src, expt_assignment, expt_indx, topk_indx, symm_mem_pool: 
     T_global, k = expt_indx.shape
     T_local = T_global // W
     dev = src.device
-    owner = expert_owner(expt_assignment)
-    order, counts, flat = make_exchange_plan(expt_indx, topk_indx.reshape(-1), owner, W, T_local)
-    counts_h = counts.cpu()
-    starts_h = _starts(counts_h)
-    # this rank (as expert owner d) returns to each home rank s the rows order[start(s, d) : +counts[s, d]]
-    send_counts = counts_h[:, rank].tolist()
+    if plan is None:
+        plan = make_exchange_plan_cuda(expt_indx, topk_indx, expt_assignment, W, T_local)
+    # this rank (as expert owner) returns to each home rank s the rows order[start(s, rank) : +counts[s, rank]]
+    send_counts = plan.counts_host[:, rank].tolist()
     n_send = sum(send_counts)
-    pos = torch.cat([order[int(starts_h[s, rank]):int(starts_h[s, rank]) + send_counts[s]] for s in range(W)]) \
-        if n_send else torch.empty(0, dtype=torch.int64, device=dev)
     sendbuf = torch.empty((n_send, d), dtype=src.dtype, device=dev)
     if n_send:
-        _rows_call(lib.moe_gather_rows, src, pos.to(torch.int32), n_send, sendbuf)
-    recv_counts = counts_h[rank].tolist()
+        pos = torch.cat([plan.order[lo:lo + c] for lo, c in _segments(plan, rank, W, True)])
+        _rows_call(lib.moe_gather_rows, src, pos, n_send, sendbuf)
+    recv_counts = plan.counts_host[rank].tolist()
     n_recv = sum(recv_counts)
-    recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
     if W > 1:
+        recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
         dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=recv_counts, input_split_sizes=send_counts,
                                group=mesh.process_group)
     else:
         recvbuf = sendbuf
     dst = torch.zeros((T_local * k, d), dtype=src.dtype, device=dev)
-    lo = int(starts_h[rank, 0])
-    where = (flat[lo:lo + n_recv] - rank * T_local * k).to(torch.int32)
+    lo = int(plan.starts_host[rank, 0])
     if n_recv:
-        _rows_call(lib.moe_scatter_rows, recvbuf, where, n_recv, dst)
+        where = plan.flat[lo:lo + n_recv] - rank * T_local * k
+        _rows_call(lib.moe_scatter_rows, recvbuf, where.to(torch.int32), n_recv, dst)
     return dst

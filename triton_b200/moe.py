@@ -94,14 +94,15 @@ def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: in
     """Expert-parallel layer: tokens are sharded over ranks (x_local [T_local, d_model]), experts over ranks
     (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered, token
     rows travel to the expert owners and back by one NCCL all-to-all each way."""
-    from .distributed import convert_dp_to_ep, convert_ep_to_dp
+    from .distributed import convert_dp_to_ep, convert_ep_to_dp, make_exchange_plan_cuda
     rank = pool.mesh.local_rank
     sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
     md = sparse.mask_metadata
     n_entries = md.row_sorted_indx.shape[0]
     meta_global = make_ragged_tensor_metadata(md.col_sum, n_entries)
-    x_ep = convert_dp_to_ep(x_local, expt_assignment, sparse.indx, md.row_sorted_indx, pool,
-                            col_sorted_indx=md.col_sorted_indx)
+    plan = make_exchange_plan_cuda(sparse.indx, md.col_sorted_indx, expt_assignment, pool.mesh.world_size,
+                                   x_local.shape[0])
+    x_ep = convert_dp_to_ep(x_local, expt_assignment, sparse.indx, md.row_sorted_indx, pool, plan=plan)
     meta_local = remap_ragged_tensor_metadata(meta_global, expt_assignment.expt_map[rank, :])
     gammas = sparse.vals.reshape(-1)[md.col_sorted_indx.long().clamp_min(0)]
     pc1 = PrecisionConfig(b_mx_scale=lw_local.w1_scale, b_microblock_size=32)
@@ -111,6 +112,6 @@ def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: in
                    fused_activation=_activation(lw_local))
     with _span(gemm_timer):
         y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas)
-    y_dp = convert_ep_to_dp(y, expt_assignment, sparse.indx, md.col_sorted_indx, pool)
+    y_dp = convert_ep_to_dp(y, expt_assignment, sparse.indx, md.col_sorted_indx, pool, plan=plan)
     z, _ = reduce(y_dp.view(x_local.shape[0], k, -1), dim=1)
     return z
