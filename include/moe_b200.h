@@ -190,6 +190,10 @@ int moe_ep_keys(const int32_t* col_sorted, const int16_t* expt_indx, const int32
                 int entries_per_rank, int world, int16_t* keys, void* stream);
 int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
                     void* dst, int64_t ld_dst, void* stream);
+/* y[t, :] = sum over j < k of src[row_indx[t * k + j], :] (negative index: skipped); bf16 rows, fp32 sum.  The
+ * k-way combine (reduce.py:1143-1165 with dim = 1) read through an index, used after the combine exchange.   */
+int moe_gather_reduce_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t T, int k, int64_t d,
+                           void* y, int64_t ld_y, void* stream);
 int moe_scatter_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_in, int64_t row_bytes,
                      void* dst, int64_t ld_dst, void* stream);
 

@@ -44,12 +44,14 @@ def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
         pool.initialize_matmul(n_tokens, d_model, d_model, k, n_expts, torch.bfloat16, dev)
         T_local = n_tokens // world
         sl = slice(rank * T_local, (rank + 1) * T_local)
-        for _ in range(2):                                  # twice: buffers and plans are rebuilt per call
-            z_loc = moe_layer_forward_ep(x[sl].contiguous(), logits[sl].contiguous(), lw_local, k, assign, pool)
-        tb.matmul_check_status()
-        z_all = torch.empty_like(z_ref)
-        dist.all_gather_into_tensor(z_all, z_loc)
-        oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3, what="EP vs single GPU")
+        for fused in (False, True, True):                   # the reference's composition, then the fused exchange twice
+            z_loc = moe_layer_forward_ep(x[sl].contiguous(), logits[sl].contiguous(), lw_local, k, assign, pool,
+                                         fused_exchange=fused)
+            tb.matmul_check_status()
+            z_all = torch.empty_like(z_ref)
+            dist.all_gather_into_tensor(z_all, z_loc)
+            oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3,
+                                       what=f"EP (fused={fused}) vs single GPU")
         ret[rank] = 1
     finally:
         dist.destroy_process_group()

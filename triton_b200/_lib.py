@@ -71,6 +71,7 @@ PROTOTYPES = {
     "moe_grouped_gemm": (i32, [C.POINTER(MoeGemmArgs), vp]),
     "moe_ep_keys": (i32, [vp, vp, vp, i64, i32, i32, vp, vp]),
     "moe_gather_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
+    "moe_gather_reduce_rows": (i32, [vp, i64, vp, i64, i32, i64, vp, i64, vp]),
     "moe_scatter_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
 }
 

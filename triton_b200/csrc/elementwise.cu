@@ -276,3 +276,48 @@ extern "C" __attribute__((visibility("default"))) int moe_ep_keys(const int32_t*
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// y[t, :] = sum_{j < k} src[row_indx[t * k + j], :]   (row_indx < 0: skipped), fp32 accumulation, bf16 rows.
+// The k-way combine of an expert-parallel layer read straight out of the receive buffer of the combine
+// exchange, without first scattering the rows back into token order.
+namespace {
+__global__ void __launch_bounds__(256) gather_reduce_kernel(const __nv_bfloat16* __restrict__ src, int64_t ld_src,
+                                                            const int32_t* __restrict__ row_indx, int64_t T, int k,
+                                                            int64_t d, __nv_bfloat16* __restrict__ y, int64_t ld_y) {
+  const int64_t vec_per_row = d >> 3;
+  const int64_t total = T * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / vec_per_row, c = (i - t * vec_per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (int s = 0; s < k; ++s) {
+      const int32_t r = row_indx[t * k + s];
+      if (r < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + (int64_t)r * ld_src + c);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]);
+    }
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
+    *reinterpret_cast<uint4*>(y + t * ld_y + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_gather_reduce_rows(const void* src, int64_t ld_src,
+                                                                             const int32_t* row_indx, int64_t T, int k,
+                                                                             int64_t d, void* y, int64_t ld_y, void* stream) {
+  MOE_CHECK_ARG(T >= 0 && k > 0 && d >= 0, "moe_gather_reduce_rows: bad extents");
+  if (T == 0 || d == 0) return MOE_OK;
+  MOE_CHECK_ARG(src && row_indx && y, "moe_gather_reduce_rows: NULL pointer");
+  MOE_CHECK_ARG(d % 8 == 0 && ld_src % 8 == 0 && ld_y % 8 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)y % 16 == 0,
+                "moe_gather_reduce_rows: bf16 rows must be 16-byte aligned multiples of 8 elements");
+  gather_reduce_kernel<<<grid_for(T * (d / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, ld_src, row_indx, T, k, d, (__nv_bfloat16*)y, ld_y);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}

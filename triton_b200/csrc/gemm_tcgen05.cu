@@ -25,6 +25,12 @@
 
 // Compile-time switches that knock out one pipeline role at a time (results become wrong); used only to
 // attribute time while tuning.  All zero in the shipped library.
+#ifndef MOE_STAGES_SMALL
+#define MOE_STAGES_SMALL 5
+#endif
+#ifndef MOE_RAW_STAGES_SMALL
+#define MOE_RAW_STAGES_SMALL 6
+#endif
 #ifndef MOE_PROBE_NO_A
 #define MOE_PROBE_NO_A 0
 #endif
@@ -52,21 +58,23 @@ constexpr int RAWV_BYTES = HALF_N * BLOCK_K / 2;        // 4 KB: half of an 8 KB
 constexpr int RAWS_BYTES = HALF_N * 4;                  // 512 B: the scale tile of the whole 128-k weight tile
 constexpr int TMEM_COLS = 512;                           // two accumulator buffers of MH x 128 columns (256 used when MH = 1)
 constexpr int MAX_PREFIX_EXPERTS = 512;                  // experts the 256-row tile schedule can index
-constexpr int PREFETCH_AHEAD = 12;                       // k steps the producer prefetches packed weights into L2
-
 // Shared-memory map for a CTA tile of (MH x 128 token rows) x (NH x 128 weight rows), 64 k per stage.
 //   MH = 1, NH = 1: 6 stages, two accumulator buffers   (small problems: many CTAs, short tiles)
 //   MH = 2, NH = 1: 4 stages, two accumulator buffers
 //   MH = 2, NH = 2: 3 stages, one accumulator buffer    (prefill: most MMA work per pipeline hand-off)
 // The MH halves of a token tile share every dequantised weight stage, the NH halves share every activation stage.
 template <int MH, int NH> struct Cfg {
-  static constexpr int STAGES = (MH == 1) ? 6 : (NH == 1 ? 4 : 3);
-  static constexpr int RAW_STAGES = (NH == 1) ? 6 : 3;                  // ring of packed weight stages
+  static constexpr int STAGES = (MH == 1) ? MOE_STAGES_SMALL : (NH == 1 ? 4 : 3);
+  // Packed weights travel in stages of RAWK 64-k steps: a whole 128-k weight tile (one 8 KB + one 512 B bulk copy)
+  // when the CTA tile is one weight tile wide, so that the single producer thread spends half as many
+  // operations per byte; 64 k per stage (two n halves) for the 256-wide CTA tile.
+  static constexpr int RAWK = (NH == 1) ? 2 : 1;
+  static constexpr int RAW_STAGES = (MH == 1) ? MOE_RAW_STAGES_SMALL : 3;
   static constexpr int ACC_BUFS = (MH * NH * 128 <= 256) ? 2 : 1;       // accumulator buffers in the 512 TMEM columns
   static constexpr int ACC_COLS = MH * NH * 128;
   static constexpr int A_STAGE_BYTES = MH * SUBTILE_BYTES;
   static constexpr int B_STAGE_BYTES = NH * SUBTILE_BYTES;
-  static constexpr int RAWV_STAGE = NH * RAWV_BYTES;
+  static constexpr int RAWV_STAGE = NH * RAWV_BYTES * RAWK;
   static constexpr int RAWS_STAGE = NH * RAWS_BYTES;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_STAGE_BYTES;
@@ -153,9 +161,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
-}
-__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -373,9 +378,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       uint32_t it = 0, tc = 0;
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
-        int e; int64_t row0; int rows;
-        if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
-        const int halves = rows > HALF_M ? 2 : 1;
+        int halves = 1;
+        if constexpr (MH == 2) {            // only the 256-row tile needs to know how many rows are live
+          int e; int64_t row0; int rows;
+          map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
+          halves = rows > HALF_M ? 2 : 1;
+        }
         const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
         const uint32_t idesc = make_idesc(nh_live * HALF_N);
         const uint32_t ab = tc % ACC_BUFS;
@@ -417,38 +425,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       const uint8_t* ws = p.w_scale;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int e; int64_t row0; int rows;
-        if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
+        map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);     // every tile below n_tiles is a real one
         const int nt0 = (int)(tile % NT) * NH;                   // first weight tile along n
         const int nh_live = min(NH, NT128 - nt0);
         const int64_t tile0 = ((int64_t)e * NT128 + nt0) * KT_TILES;
-        // the next tile of this CTA, so that its first weight stages can be pulled into L2 ahead of time
-        const uint8_t* next_wv = nullptr;
-        {
-          int e2; int64_t r2; int n2;
-          const int64_t t2 = tile + gridDim.x;
-          if (t2 < n_tiles && map_tile<MH>(p, s_prefix, t2 / NT, e2, r2, n2))
-            next_wv = wv + (((int64_t)e2 * NT128 + (int)(t2 % NT) * NH) * KT_TILES) * (2 * RAWV_BYTES);
-        }
         const uint8_t* cur_wv = wv + tile0 * (2 * RAWV_BYTES);
         const int64_t half_stride = (int64_t)KT_TILES * (2 * RAWV_BYTES);     // next weight tile along n
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        constexpr int RAWK = C::RAWK;
+        const int n_raw = RAWK == 2 ? KT_TILES : KT;                          // raw stages of this tile
+        for (int rt = 0; rt < n_raw; ++rt, ++it) {
           const int s = it % RAW_STAGES;
           ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / RAW_STAGES) & 1u) ^ 1u, ctl, 201);
           if (!ok) break;
-          {
-            const int kp = kt + PREFETCH_AHEAD;
-            for (int h = 0; h < nh_live; ++h) {
-              if (kp < KT) l2_prefetch(cur_wv + h * half_stride + (int64_t)kp * RAWV_BYTES, RAWV_BYTES);
-              else if (next_wv && kp - KT < KT) l2_prefetch(next_wv + h * half_stride + (int64_t)(kp - KT) * RAWV_BYTES, RAWV_BYTES);
-            }
-          }
-          mbar_expect_tx(BAR_RAW_FULL(s), (uint32_t)nh_live * (RAWV_BYTES + RAWS_BYTES));
-          // stage kt is half (kt & 1) of weight tile kt >> 1: 4 KB of values, plus the tile's 512 scale bytes
+          mbar_expect_tx(BAR_RAW_FULL(s), (uint32_t)nh_live * (RAWK * RAWV_BYTES + RAWS_BYTES));
           for (int h = 0; h < nh_live; ++h) {
-            bulk_g2s(sbase + C::OFF_RAWV + s * C::RAWV_STAGE + h * RAWV_BYTES, cur_wv + h * half_stride + (int64_t)kt * RAWV_BYTES,
-                     RAWV_BYTES, BAR_RAW_FULL(s));
+            bulk_g2s(sbase + C::OFF_RAWV + s * C::RAWV_STAGE + h * (RAWK * RAWV_BYTES),
+                     cur_wv + h * half_stride + (int64_t)rt * (RAWK * RAWV_BYTES), RAWK * RAWV_BYTES, BAR_RAW_FULL(s));
             bulk_g2s(sbase + C::OFF_RAWS + s * C::RAWS_STAGE + h * RAWS_BYTES,
-                     ws + (tile0 + (int64_t)h * KT_TILES + (kt >> 1)) * RAWS_BYTES, RAWS_BYTES, BAR_RAW_FULL(s));
+                     ws + (tile0 + (int64_t)h * KT_TILES + (RAWK == 2 ? rt : (rt >> 1))) * RAWS_BYTES, RAWS_BYTES,
+                     BAR_RAW_FULL(s));
           }
         }
       }
@@ -480,11 +475,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     }
     uint32_t it = 0;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    // source rows of a tile: looked up one tile ahead, so that the dependent loads (schedule -> offsets ->
+    // gather index) of the next tile fly while the current tile streams
+    auto load_rows = [&](int64_t tile, uint32_t (&src16)[NR], int& nr_live) {
       int e; int64_t row0; int rows;
-      if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
-      const int nr_live = (MH == 2 && rows > HALF_M) ? NR : 8;   // the MMA skips an empty second half
-      uint32_t src16[NR];                           // 0xFFFFFFFF: no source row
+      map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
+      nr_live = (MH == 2 && rows > HALF_M) ? NR : 8;            // the MMA skips an empty second half
 #pragma unroll
       for (int i = 0; i < NR; ++i) {
         const int r = rbase + 16 * i;
@@ -494,8 +490,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           src = p.gather_indx ? (int64_t)p.gather_indx[m] : m;
           if (src >= p.rows_x) src = -1;
         }
-        src16[i] = src < 0 ? 0xFFFFFFFFu : (uint32_t)src * ld16;
+        src16[i] = src < 0 ? 0xFFFFFFFFu : (uint32_t)src * ld16;   // 0xFFFFFFFF: no source row
       }
+    };
+    uint32_t src16[NR], nxt16[NR];
+    int nr_live = 8, nxt_live = 8;
+    if ((int64_t)blockIdx.x < n_tiles) load_rows(blockIdx.x, src16, nr_live);
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const int64_t t2 = tile + gridDim.x;
+      if (t2 < n_tiles) load_rows(t2, nxt16, nxt_live);
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % STAGES;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_AB_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 301));
@@ -515,6 +518,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         }
         cp_async_arrive_noinc(BAR_A_FULL(s));
       }
+#pragma unroll
+      for (int i = 0; i < NR; ++i) src16[i] = nxt16[i];
+      nr_live = nxt_live;
     }
     cp_async_wait_all();
   } else if (warp < WARP_EPI0) {
@@ -527,25 +533,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     const int g = (lane >> 3) & 1;                  // scale group inside the 64-k stage
     const int r = dw * 16 + (lane >> 4) * 8 + (lane & 7);
     const int x7 = r & 7;
-    uint32_t it = 0;
+    constexpr int RAWK = C::RAWK;
+    uint32_t it = 0, itr = 0;                       // operand-ring step, packed-weight-ring stage
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      int e; int64_t row0; int rows;
-      if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
       const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
-        const int rs = it % RAW_STAGES;
-        ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_RAW_FULL(rs), (it / RAW_STAGES) & 1u, ctl, 401) &&
-                                         mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402));
+        const int rs = itr % RAW_STAGES;
+        const bool first_half = RAWK == 1 || !(kt & 1);
+        const bool last_half = RAWK == 1 || (kt & 1) || kt == KT - 1;
+        bool got = mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402);
+        if (first_half) got = got && mbar_wait(BAR_RAW_FULL(rs), (itr / RAW_STAGES) & 1u, ctl, 401);
+        ok = __all_sync(0xFFFFFFFFu, got);
         if (!ok) break;
+        const uint32_t half_off = (RAWK == 2 && (kt & 1)) ? RAWV_BYTES : 0;
         uint4 raw[NH];
         uint32_t sb[NH];
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
           if (h < nh_live) {
-            raw[h] = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE + h * RAWV_BYTES)[g * HALF_N + r];
+            raw[h] = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE + h * (RAWK * RAWV_BYTES) +
+                                                    half_off)[g * HALF_N + r];
             sb[h] = (smem + C::OFF_RAWS + rs * C::RAWS_STAGE + h * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
           }
         }
@@ -572,8 +582,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(BAR_B_FULL(s));
-          mbar_arrive(BAR_RAW_EMPTY(rs));
+          if (last_half) mbar_arrive(BAR_RAW_EMPTY(rs));
         }
+        if (last_half) ++itr;
       }
     }
   } else {
@@ -588,7 +599,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
       int e; int64_t row0; int rows;
-      if (!map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows)) continue;
+      map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
       const int halves = rows > HALF_M ? 2 : 1;
       const int n0 = (int)(tile % NT) * TILE_N;
       const uint32_t ab = tc % ACC_BUFS;

@@ -291,3 +291,68 @@ def convert_ep_to_dp(src, expt_assignment, expt_indx, topk_indx, symm_mem_pool: 
         where = plan.flat[lo:lo + n_recv] - rank * T_local * k
         _rows_call(lib.moe_scatter_rows, recvbuf, where.to(torch.int32), n_recv, dst)
     return dst
+
+
+# ---------------------------------------------------------------------------------------------------------
+# fused form used by moe_layer_forward_ep: the GEMMs read / write the exchange buffers through index maps, so
+# the rows are never copied into (or out of) the [T_global * k, d] expert-sorted buffer
+# ---------------------------------------------------------------------------------------------------------
+
+def ep_dispatch_packed(src, k, symm_mem_pool: SymmetricMemoryPool, plan: ExchangePlan):
+    """-> (recvbuf [n_recv, d], row_of_position [T_global * k] int32): row_of_position[p] is the row of recvbuf that
+    holds the token of expert-sorted position p (-1 where p's expert lives on another rank).  Feed it to `matmul`
+    as gather_indx."""
+    lib = _lib.load()
+    mesh = symm_mem_pool.mesh
+    W, rank = mesh.world_size, mesh.local_rank
+    T_local, d = src.shape
+    dev = src.device
+    n = plan.order.numel()
+    send_counts = plan.counts_host[rank].tolist()
+    send_lo, n_send = int(plan.starts_host[rank, 0]), sum(send_counts)
+    tok_local = torch.div(plan.flat[send_lo:send_lo + n_send], k, rounding_mode="floor") - rank * T_local
+    sendbuf = torch.empty((n_send, d), dtype=src.dtype, device=dev)
+    if n_send:
+        _rows_call(lib.moe_gather_rows, src, tok_local.to(torch.int32), n_send, sendbuf)
+    recv_counts = plan.counts_host[:, rank].tolist()
+    n_recv = sum(recv_counts)
+    if W > 1:
+        recvbuf = torch.empty((n_recv, d), dtype=src.dtype, device=dev)
+        dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                               group=mesh.process_group)
+    else:
+        recvbuf = sendbuf
+    row_of_position = torch.full((n,), -1, dtype=torch.int32, device=dev)
+    if n_recv:
+        pos = torch.cat([plan.order[lo:lo + c] for lo, c in _segments(plan, rank, W, True)])
+        row_of_position[pos.long()] = torch.arange(n_recv, dtype=torch.int32, device=dev)
+    return recvbuf, row_of_position, n_recv
+
+
+def ep_combine_packed(y_packed, k, T_local, symm_mem_pool: SymmetricMemoryPool, plan: ExchangePlan):
+    """y_packed [n_recv_of_dispatch, d]: expert outputs in the row order of `ep_dispatch_packed`'s recvbuf (what
+    `matmul(..., scatter_indx=row_of_position)` writes).  Sends every row home and sums the k rows of each local
+    token straight out of the receive buffer.  -> [T_local, d]."""
+    lib = _lib.load()
+    mesh = symm_mem_pool.mesh
+    W, rank = mesh.world_size, mesh.local_rank
+    d = y_packed.shape[1]
+    dev = y_packed.device
+    send_counts = plan.counts_host[:, rank].tolist()
+    recv_counts = plan.counts_host[rank].tolist()
+    n_recv = sum(recv_counts)
+    if W > 1:
+        recvbuf = torch.empty((n_recv, d), dtype=y_packed.dtype, device=dev)
+        dist.all_to_all_single(recvbuf, y_packed, output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                               group=mesh.process_group)
+    else:
+        recvbuf = y_packed
+    lo = int(plan.starts_host[rank, 0])
+    row_of_flat = torch.full((T_local * k,), -1, dtype=torch.int32, device=dev)
+    if n_recv:
+        where = (plan.flat[lo:lo + n_recv] - rank * T_local * k).long()
+        row_of_flat[where] = torch.arange(n_recv, dtype=torch.int32, device=dev)
+    z = torch.empty((T_local, d), dtype=y_packed.dtype, device=dev)
+    _lib.check(lib.moe_gather_reduce_rows(_lib.ptr(recvbuf), recvbuf.stride(0), _lib.ptr(row_of_flat), T_local, k, d,
+                                          _lib.ptr(z), z.stride(0), _lib.stream()), "moe_gather_reduce_rows")
+    return z

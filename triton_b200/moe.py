@@ -90,28 +90,43 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
 
 
 def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: int, expt_assignment, pool,
-                         gemm_timer=None):
+                         gemm_timer=None, fused_exchange=True):
     """Expert-parallel layer: tokens are sharded over ranks (x_local [T_local, d_model]), experts over ranks
     (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered, token
-    rows travel to the expert owners and back by one NCCL all-to-all each way."""
-    from .distributed import convert_dp_to_ep, convert_ep_to_dp, make_exchange_plan_cuda
+    rows travel to the expert owners and back by one NCCL all-to-all each way.
+
+    With `fused_exchange` the two GEMMs read and write the exchange buffers through index maps (fc1 gathers from
+    the receive buffer, fc2 scatters into the send buffer) and the k-way combine reads the returned rows in
+    place; without it the layer is the reference's composition convert_dp_to_ep -> matmul -> matmul ->
+    convert_ep_to_dp -> reduce (python/triton_kernels/tests/test_distributed.py:223-247)."""
+    from .distributed import (convert_dp_to_ep, convert_ep_to_dp, ep_combine_packed, ep_dispatch_packed,
+                              make_exchange_plan_cuda)
     rank = pool.mesh.local_rank
+    T_local = x_local.shape[0]
     sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
     md = sparse.mask_metadata
     n_entries = md.row_sorted_indx.shape[0]
     meta_global = make_ragged_tensor_metadata(md.col_sum, n_entries)
-    plan = make_exchange_plan_cuda(sparse.indx, md.col_sorted_indx, expt_assignment, pool.mesh.world_size,
-                                   x_local.shape[0])
-    x_ep = convert_dp_to_ep(x_local, expt_assignment, sparse.indx, md.row_sorted_indx, pool, plan=plan)
+    plan = make_exchange_plan_cuda(sparse.indx, md.col_sorted_indx, expt_assignment, pool.mesh.world_size, T_local)
     meta_local = remap_ragged_tensor_metadata(meta_global, expt_assignment.expt_map[rank, :])
     gammas = sparse.vals.reshape(-1)[md.col_sorted_indx.long().clamp_min(0)]
     pc1 = PrecisionConfig(b_mx_scale=lw_local.w1_scale, b_microblock_size=32)
     pc2 = PrecisionConfig(b_mx_scale=lw_local.w2_scale, b_microblock_size=32)
+    if fused_exchange:
+        recvbuf, row_of_position, n_recv = ep_dispatch_packed(x_local, k, pool, plan)
+        with _span(gemm_timer):
+            h = matmul(recvbuf, lw_local.w1, lw_local.b1, a_ragged_metadata=meta_local, gather_indx=row_of_position,
+                       precision_config=pc1, fused_activation=_activation(lw_local))
+        with _span(gemm_timer):
+            y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, scatter_indx=row_of_position,
+                       precision_config=pc2, gammas=gammas)
+        return ep_combine_packed(y[:n_recv], k, T_local, pool, plan)
+    x_ep = convert_dp_to_ep(x_local, expt_assignment, sparse.indx, md.row_sorted_indx, pool, plan=plan)
     with _span(gemm_timer):
         h = matmul(x_ep, lw_local.w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
                    fused_activation=_activation(lw_local))
     with _span(gemm_timer):
         y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas)
     y_dp = convert_ep_to_dp(y, expt_assignment, sparse.indx, md.col_sorted_indx, pool, plan=plan)
-    z, _ = reduce(y_dp.view(x_local.shape[0], k, -1), dim=1)
+    z, _ = reduce(y_dp.view(T_local, k, -1), dim=1)
     return z
