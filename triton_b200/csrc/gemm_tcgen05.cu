@@ -44,6 +44,26 @@
 #define MOE_PROBE_NO_EPI 0
 #endif
 
+#ifndef MOE_TC_STATS
+#define MOE_TC_STATS 0
+#endif
+#if MOE_TC_STATS
+// instrumented build only: cycles per CTA and role spent waiting on each barrier / working
+__device__ long long g_tc_stats[160][16];
+#define STAT_T0() long long _st0 = clock64()
+#define STAT_ADD(slot) do { long long _n = clock64(); _stat[slot] += _n - _st0; _st0 = _n; } while (0)
+#define STAT_DECL() long long _stat[4] = {0, 0, 0, 0}
+#define STAT_FLUSH(base) do { for (int _i = 0; _i < 4; ++_i) g_tc_stats[blockIdx.x][(base) + _i] = _stat[_i]; } while (0)
+extern "C" __attribute__((visibility("default"))) int moe_tc_stats_read(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_tc_stats, sizeof(g_tc_stats));
+}
+#else
+#define STAT_T0()
+#define STAT_ADD(slot)
+#define STAT_DECL()
+#define STAT_FLUSH(base)
+#endif
+
 namespace {
 
 constexpr int HALF_M = 128;           // token rows of one MMA (MMA M)
@@ -85,7 +105,13 @@ template <int MH, int NH> struct Cfg {
   static constexpr int NUM_BARS = 3 * STAGES + 2 * RAW_STAGES + 4 + 1;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;               // tmem base, abort flag
   static constexpr int OFF_PREFIX = OFF_MISC + 16;                      // MH = 2: int32 tile prefix over experts
-  static constexpr int SMEM_BYTES = OFF_PREFIX + (MH == 2 ? (MAX_PREFIX_EXPERTS + 1) * 4 : 0);
+  static constexpr int OFF_ROWS = OFF_PREFIX;                           // MH = 1: source rows, [4 loader warps][2][128]
+  static constexpr int SMEM_BYTES = OFF_PREFIX + (MH == 2 ? (MAX_PREFIX_EXPERTS + 1) * 4 : 4 * 2 * 128 * 4);
+  // MH = 1 interleaves pipeline steps over the warps of a role (see the loader and the dequantiser)
+  static constexpr int DEQ_GROUPS = (MH == 1) ? 4 : 1;
+  static constexpr int A_FULL_COUNT = (MH == 1) ? 32 : LOADER_WARPS * 32;
+  static constexpr int B_FULL_COUNT = DEQUANT_WARPS / DEQ_GROUPS;
+  static constexpr int RAW_EMPTY_COUNT = (DEQUANT_WARPS / DEQ_GROUPS) * ((NH == 1 && DEQ_GROUPS > 1) ? 2 : 1);
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;                  // slack for 1024-byte alignment
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
 };
@@ -320,11 +346,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
   if (threadIdx.x == 0) {
     for (int s = 0; s < RAW_STAGES; ++s) {
       mbar_init(BAR_RAW_FULL(s), 1);
-      mbar_init(BAR_RAW_EMPTY(s), DEQUANT_WARPS);
+      mbar_init(BAR_RAW_EMPTY(s), C::RAW_EMPTY_COUNT);
     }
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(BAR_A_FULL(s), LOADER_WARPS * 32);
-      mbar_init(BAR_B_FULL(s), DEQUANT_WARPS);
+      mbar_init(BAR_A_FULL(s), C::A_FULL_COUNT);
+      mbar_init(BAR_B_FULL(s), C::B_FULL_COUNT);
       mbar_init(BAR_AB_EMPTY(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -377,40 +403,61 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     if (lane == 0) {
       uint32_t it = 0, tc = 0;
       bool ok = true;
+      STAT_DECL();
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
-        int halves = 1;
-        if constexpr (MH == 2) {            // only the 256-row tile needs to know how many rows are live
-          int e; int64_t row0; int rows;
-          map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
-          halves = rows > HALF_M ? 2 : 1;
+        int halves = 1, rows_cur = HALF_M;
+        {
+          int e; int64_t row0;
+          map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows_cur);
+          halves = (MH == 2 && rows_cur > HALF_M) ? 2 : 1;
         }
         const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
-        const uint32_t idesc = make_idesc(nh_live * HALF_N);
+        // MH == 1 swaps the operands: the dequantised weight tile is the M = 128 operand and the token tile the
+        // N operand, with N = the tile's rows rounded up to 16, so that a tile of a few tokens costs a few columns
+        // of MMA time instead of a full 128 x 128 product.  The accumulator is then [weight row][token].
+        const int n_tok = max(16, (min(rows_cur, HALF_M) + 15) & ~15);
+        const uint32_t idesc = make_idesc(MH == 1 ? n_tok : nh_live * HALF_N);
         const uint32_t ab = tc % ACC_BUFS;
+        STAT_T0();
         ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc / ACC_BUFS) & 1u) ^ 1u, ctl, 101);
         if (!ok) break;
+        STAT_ADD(0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 102) && mbar_wait(BAR_B_FULL(s), ph, ctl, 103);
+          ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 102);
+          STAT_ADD(1);
+          ok = ok && mbar_wait(BAR_B_FULL(s), ph, ctl, 103);
+          STAT_ADD(2);
           if (!ok) break;
           fence_proxy_async();          // the A tile was written by cp.async (generic proxy) of other threads
           tc_fence_after();
+#if MOE_TC_STATS == 2
+          STAT_ADD(0);
+#endif
           const uint64_t adesc = make_desc(sbase + C::OFF_A + s * C::A_STAGE_BYTES);
           const uint64_t bdesc = make_desc(sbase + C::OFF_B + s * B_STAGE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < (MOE_PROBE_NO_MMA ? 0 : 4); ++kk) {
-            mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
+            if constexpr (MH == 1)
+              mma_bf16(d_tmem, bdesc + (uint64_t)(kk * 2), adesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
+            else
+              mma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
             if (MH == 2 && halves == 2)
               mma_bf16(d_tmem + NH * HALF_N, adesc + (uint64_t)((SUBTILE_BYTES >> 4) + kk * 2),
                        bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
           }
+#if MOE_TC_STATS == 2
+          STAT_ADD(2);
+#endif
           mma_commit(BAR_AB_EMPTY(s));
+          STAT_ADD(3);
         }
         if (ok) mma_commit(BAR_ACC_FULL(ab));
       }
+      STAT_FLUSH(0);
       // make sure every MMA issued by this thread has retired before tensor memory is freed
       mma_commit(BAR_DRAIN);
       mbar_wait(BAR_DRAIN, 0, ctl, 104);
@@ -421,6 +468,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      STAT_DECL();
       const uint8_t* wv = (const uint8_t*)p.w;
       const uint8_t* ws = p.w_scale;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -435,8 +483,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         const int n_raw = RAWK == 2 ? KT_TILES : KT;                          // raw stages of this tile
         for (int rt = 0; rt < n_raw; ++rt, ++it) {
           const int s = it % RAW_STAGES;
+          STAT_T0();
           ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / RAW_STAGES) & 1u) ^ 1u, ctl, 201);
           if (!ok) break;
+          STAT_ADD(0);
           mbar_expect_tx(BAR_RAW_FULL(s), (uint32_t)nh_live * (RAWK * RAWV_BYTES + RAWS_BYTES));
           for (int h = 0; h < nh_live; ++h) {
             bulk_g2s(sbase + C::OFF_RAWV + s * C::RAWV_STAGE + h * (RAWK * RAWV_BYTES),
@@ -445,8 +495,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
                      ws + (tile0 + (int64_t)h * KT_TILES + (RAWK == 2 ? rt : (rt >> 1))) * RAWS_BYTES, RAWS_BYTES,
                      BAR_RAW_FULL(s));
           }
+          STAT_ADD(1);
         }
       }
+      STAT_FLUSH(4);
       if (!ok) {
         // aborting: let the copies that were already issued land before the CTA leaves
         const uint32_t lo = it > (uint32_t)RAW_STAGES ? it - RAW_STAGES : 0;
@@ -457,6 +509,67 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     __syncwarp();
   } else if (warp < WARP_DEQ0) {
     // ================================= activation loader ==============================================
+    if constexpr (MH == 1) {
+      // Small-tile variant: each of the four loader warps takes every fourth pipeline step and moves that whole
+      // stage by itself, so four stages are in flight inside the role and the per-step latency of one warp
+      // (barrier wake-up, address arithmetic) is hidden.  Lane l owns 16-byte chunk (l & 7) of rows (l >> 3) + 4 i.
+      // Only rows that exist are copied: the MMA rows of missing tokens read whatever the stage held before,
+      // which only reaches accumulator rows that are never stored.  Each warp keeps its own table of the tile's
+      // source rows in shared memory (double-buffered by tile, filled one tile ahead).
+      const int lw = warp - WARP_LOADER0;             // 0..3
+      const int c8 = lane & 7;
+      const int rq = lane >> 3;
+      const uint8_t* Xb = (const uint8_t*)p.x;
+      const uint32_t ld16 = (uint32_t)(p.ld_x >> 3);
+      uint32_t* tab = reinterpret_cast<uint32_t*>(smem + C::OFF_ROWS) + lw * 256;
+      auto fill_table = [&](int64_t tile, int buf) -> int {
+        int e; int64_t row0; int rows;
+        map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = lane + 32 * j;
+          int64_t src = -1;
+          if (r < rows) {
+            const int64_t m = row0 + r;
+            src = p.gather_indx ? (int64_t)p.gather_indx[m] : m;
+            if (src >= p.rows_x) src = -1;
+          }
+          tab[buf * 128 + r] = src < 0 ? 0xFFFFFFFFu : (uint32_t)src * ld16;
+        }
+        return rows;
+      };
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      int rows = 0, rows_next = 0;
+      if ((int64_t)blockIdx.x < n_tiles) rows = fill_table(blockIdx.x, 0);
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int buf = tcount & 1;
+        const int64_t t2 = tile + gridDim.x;
+        if (t2 < n_tiles) rows_next = fill_table(t2, buf ^ 1);
+        __syncwarp();
+        const uint32_t* trow = tab + buf * 128;
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          if ((int)(it & 3u) != lw) continue;
+          const int s = it % STAGES;
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_AB_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 301));
+          if (!ok) break;
+          const int k = kt * BLOCK_K + c8 * 8;
+          const int kleft = p.K - k;
+          const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
+          const uint32_t stage = sbase + C::OFF_A + s * C::A_STAGE_BYTES;
+          const uint32_t kc16 = (uint32_t)(k >> 3);
+          for (int r = rq; r < rows && !MOE_PROBE_NO_A; r += 4) {
+            const uint32_t so = trow[r];
+            const bool live = so != 0xFFFFFFFFu && kbytes;
+            const uint8_t* g = live ? Xb + ((uint64_t)(so + kc16) << 4) : Xb;
+            cp_async16(stage + (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4)), g, live ? kbytes : 0u);
+          }
+          cp_async_arrive_noinc(BAR_A_FULL(s));
+        }
+        rows = rows_next;
+      }
+      cp_async_wait_all();
+    } else {
     // 128 threads move the (MH x 128) x 128-byte stage: thread t owns 16-byte chunk (t & 7) of rows
     // (t >> 3) + 16 i.  The source of each row (byte offset / 16 into x, or none) is kept in registers for the
     // whole tile.  A stage is published by cp.async.mbarrier.arrive.noinc: the barrier completes when the
@@ -523,58 +636,82 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
       nr_live = nxt_live;
     }
     cp_async_wait_all();
+    }
   } else if (warp < WARP_EPI0) {
     // ================================= dequantiser ======================================================
-    // 256 threads; a unit is one (weight row, 32-k scale group): one 16-byte load, one scale byte, four 16-byte
-    // swizzled stores.  Every thread takes one unit of each of the NH weight tiles of the stage.  A quarter-warp
-    // holds one group of 8 consecutive rows, which keeps the load (128 contiguous bytes) and the stores
-    // (8 distinct 16-byte columns) free of bank conflicts.
-    const int dw = warp - WARP_DEQ0;                // 0..7
-    const int g = (lane >> 3) & 1;                  // scale group inside the 64-k stage
-    const int r = dw * 16 + (lane >> 4) * 8 + (lane & 7);
-    const int x7 = r & 7;
+    // A unit is one (weight row, 32-k scale group): one 16-byte load, one scale byte, four 16-byte swizzled stores;
+    // a stage holds 256 units per weight tile.  The eight warps work in G groups and group (step mod G) converts
+    // the whole stage: G = 1 for the large tiles (all 256 threads on every stage: shortest latency per stage),
+    // G = 4 for the small-tile configuration, where the hand-off latency of a stage, not the arithmetic, bounds
+    // the step rate and four stages in flight hide it.  A quarter-warp holds one scale group of 8 consecutive
+    // rows, which keeps the load (128 contiguous bytes) and the stores (8 distinct 16-byte columns) free of bank
+    // conflicts.
+    constexpr int G = C::DEQ_GROUPS;
+    constexpr int WPG = DEQUANT_WARPS / G;          // warps per group
+    constexpr int U = G;                            // units per thread, weight tile and stage
     constexpr int RAWK = C::RAWK;
-    uint32_t it = 0, itr = 0;                       // operand-ring step, packed-weight-ring stage
+    const int dw = warp - WARP_DEQ0;                // 0..7
+    const int grp = dw / WPG, gw = dw % WPG;
+    const int g = (lane >> 3) & 1;                  // scale group inside the 64-k stage
+    const int r0 = gw * 16 + (lane >> 4) * 8 + (lane & 7);   // rows r0 + 16 WPG u
+    const int n_raw = RAWK == 2 ? KT_TILES : KT;    // packed-weight stages per tile
+    uint32_t it = 0, raw_base = 0;                  // operand-ring step; packed-weight stage of the tile's first step
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    STAT_DECL();
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, raw_base += n_raw) {
       const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
       for (int kt = 0; kt < KT; ++kt, ++it) {
+        if (G > 1 && (int)(it % G) != grp) continue;
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
+        const uint32_t itr = raw_base + (RAWK == 2 ? (kt >> 1) : kt);
         const int rs = itr % RAW_STAGES;
-        const bool first_half = RAWK == 1 || !(kt & 1);
-        const bool last_half = RAWK == 1 || (kt & 1) || kt == KT - 1;
+        STAT_T0();
         bool got = mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402);
-        if (first_half) got = got && mbar_wait(BAR_RAW_FULL(rs), (itr / RAW_STAGES) & 1u, ctl, 401);
+        STAT_ADD(0);
+        got = got && mbar_wait(BAR_RAW_FULL(rs), (itr / RAW_STAGES) & 1u, ctl, 401);
         ok = __all_sync(0xFFFFFFFFu, got);
+        STAT_ADD(1);
         if (!ok) break;
         const uint32_t half_off = (RAWK == 2 && (kt & 1)) ? RAWV_BYTES : 0;
-        uint4 raw[NH];
-        uint32_t sb[NH];
+        uint4 raw[NH][U];
+        uint32_t sb[NH][U];
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
           if (h < nh_live) {
-            raw[h] = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE + h * (RAWK * RAWV_BYTES) +
-                                                    half_off)[g * HALF_N + r];
-            sb[h] = (smem + C::OFF_RAWS + rs * C::RAWS_STAGE + h * RAWS_BYTES)[r * 4 + (kt & 1) * 2 + g];
+            const uint4* rv = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE +
+                                                             h * (RAWK * RAWV_BYTES) + half_off) + g * HALF_N;
+            const uint8_t* rsc = smem + C::OFF_RAWS + rs * C::RAWS_STAGE + h * RAWS_BYTES + (kt & 1) * 2 + g;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int r = r0 + 16 * WPG * u;
+              raw[h][u] = rv[r];
+              sb[h][u] = rsc[r * 4];
+            }
           }
         }
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
           if (h < nh_live) {
-            uint8_t* row = smem + C::OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES + r * 128;
-            const uint32_t w[4] = {raw[h].x, raw[h].y, raw[h].z, raw[h].w};
-            if (MOE_PROBE_NO_DEQ) {
-            } else if (sb[h] <= 128u) {
-              const uint32_t c = sb[h] ? ((sb[h] + 126u) << 7) : 0u;
-              const uint32_t c2 = c * 0x10001u;
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
-            } else {
+            for (int u = 0; u < U; ++u) {
+              const int r = r0 + 16 * WPG * u;
+              const int x7 = r & 7;
+              uint8_t* row = smem + C::OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES + r * 128;
+              const uint32_t w[4] = {raw[h][u].x, raw[h][u].y, raw[h][u].z, raw[h][u].w};
+              const uint32_t sbu = sb[h][u];
+              if (MOE_PROBE_NO_DEQ) {
+              } else if (sbu <= 128u) {
+                const uint32_t c = sbu ? ((sbu + 126u) << 7) : 0u;
+                const uint32_t c2 = c * 0x10001u;
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sb[h]);
+                for (int q = 0; q < 4; ++q)
+                  *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
+              } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sbu);
+              }
             }
           }
         }
@@ -582,11 +719,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(BAR_B_FULL(s));
-          if (last_half) mbar_arrive(BAR_RAW_EMPTY(rs));
+          // the packed stage is released by whoever read it: with G > 1 the two halves of a 128-k stage are read by
+          // two different groups (each arrives), and the lone first half at the end of an odd tile arrives twice
+          if (G > 1) {
+            mbar_arrive(BAR_RAW_EMPTY(rs));
+            if (RAWK == 2 && kt == KT - 1 && !(kt & 1)) mbar_arrive(BAR_RAW_EMPTY(rs));
+          } else if (RAWK == 1 || (kt & 1) || kt == KT - 1) {
+            mbar_arrive(BAR_RAW_EMPTY(rs));
+          }
         }
-        if (last_half) ++itr;
+        STAT_ADD(2);
       }
     }
+    if (dw == 0 && lane == 0) STAT_FLUSH(8);
   } else {
     // ================================= epilogue =========================================================
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
@@ -597,7 +742,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
     uint32_t tc = 0;
     bool ok = true;
+    STAT_DECL();
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
+      STAT_T0();
       int e; int64_t row0; int rows;
       map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
       const int halves = rows > HALF_M ? 2 : 1;
@@ -611,8 +758,57 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         s_bias[jb * 32 + lane] = (p.bias && gn < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + gn) : 0.0f;
       }
       __syncwarp();
+      STAT_ADD(0);
+      if constexpr (MH == 1) {
+        // Transposed accumulator [weight row = lane][token = column].  Lane l of warp quarter q owns output column
+        // n0 + 32 q + l; token parameters (destination row, beta, gamma) sit one token per lane and are broadcast
+        // by shuffle; for SwiGLU the even lane holds the gate and the odd lane the linear half of a pair.
+        const int n = n0 + q * 32 + lane;
+        const float bias_n = s_bias[q * 32 + lane];
+        const int n_tok = max(16, (min(rows, HALF_M) + 15) & ~15);
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc / ACC_BUFS) & 1u, ctl, 501));
+        if (!ok) break;
+        STAT_ADD(1);
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * C::ACC_COLS;
+        for (int c0 = 0; c0 < n_tok; c0 += 32) {
+          uint32_t raw[32];
+          tmem_ld32(taddr + (uint32_t)c0, raw);
+          tmem_ld_wait();
+          // parameters of token c0 + lane
+          const int tj = c0 + lane;
+          int64_t dst_l = -1;
+          float beta_l = 1.0f, gamma_l = 1.0f;
+          if (tj < rows) {
+            const int64_t m = row0 + tj;
+            dst_l = p.scatter_indx ? (int64_t)p.scatter_indx[m] : m;
+            if (p.betas) beta_l = p.betas[m];
+            if (p.gammas) gamma_l = p.gammas[m];
+          }
+          const int jmax = min(32, rows - c0);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < jmax) {                                   // warp-uniform
+              const int64_t dst = __shfl_sync(0xFFFFFFFFu, dst_l, j);
+              const float beta = __shfl_sync(0xFFFFFFFFu, beta_l, j);
+              const float gamma = __shfl_sync(0xFFFFFFFFu, gamma_l, j);
+              float a = __uint_as_float(raw[j]) + bias_n * beta;
+              if (p.has_out_alpha) a *= p.out_alpha;
+              if (swiglu) {
+                const float other = __shfl_xor_sync(0xFFFFFFFFu, a, 1);
+                if (!(lane & 1) && dst >= 0 && n + 1 < p.N)
+                  Y[dst * p.ld_y + (n >> 1)] =
+                      from_f32<TY>(gemm_swiglu(a, other, p.act_alpha, p.act_limit, p.act_has_limit) * gamma);
+              } else if (dst >= 0 && n < p.N) {
+                Y[dst * p.ld_y + n] = from_f32<TY>(a * gamma);
+              }
+            }
+          }
+        }
+      } else {
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc / ACC_BUFS) & 1u, ctl, 501));
       if (!ok) break;
+      STAT_ADD(1);
       tc_fence_after();
       for (int h = 0; h < halves; ++h) {
         const int r = h * HALF_M + q * 32 + lane;   // accumulator row = token row inside the tile
@@ -654,10 +850,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR_ACC_EMPTY(ab));
+      STAT_ADD(2);
     }
+    if (q == 0 && lane == 0) STAT_FLUSH(12);
   }
 
   // ---- teardown ----------------------------------------------------------------------------------------
