@@ -42,7 +42,8 @@ __device__ __forceinline__ float gemm_swiglu(float g, float l, float alpha, floa
     g = fminf(g, limit);
     l = fminf(fmaxf(l, -limit), limit);
   }
-  const float s = g / (1.0f + gemm_ex2(-alpha * g * 1.4426950408889634f));
+  // approximate reciprocal: an IEEE division would take its slow path whenever the exponential overflows
+  const float s = __fdividef(g, 1.0f + gemm_ex2(-alpha * g * 1.4426950408889634f));
   return fmaf(s, l, s);
 }
 

@@ -240,6 +240,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- weight dequantisation ---------------------------------------------------------------------------
@@ -823,31 +832,40 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tc_kernel(const GemmParam
         }
         const bool store_row = row_live && dst >= 0;
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * C::ACC_COLS + h * TILE_N;
-#pragma unroll 1
-        for (int c0 = 0; c0 < TILE_N; c0 += 32) {
-          uint32_t raw[32];
-          tmem_ld32(taddr + (uint32_t)c0, raw);
-          tmem_ld_wait();
-          if (!store_row || n0 + c0 >= p.N || MOE_PROBE_NO_EPI) continue;
-          float v[32];
+        // two register buffers: the tensor-memory load of the next 16 columns is in flight while this one is
+        // turned into output
+        auto emit = [&](const uint32_t (&raw)[16], int c0) {
+          if (!store_row || n0 + c0 >= p.N || MOE_PROBE_NO_EPI) return;
+          float v[16];
 #pragma unroll
-          for (int jx = 0; jx < 32; ++jx) {
+          for (int jx = 0; jx < 16; ++jx) {
             float a = __uint_as_float(raw[jx]) + s_bias[c0 + jx] * beta;
             if (p.has_out_alpha) a *= p.out_alpha;
             v[jx] = a;
           }
-          const int ncols = min(32, p.N - (n0 + c0));
+          const int ncols = min(16, p.N - (n0 + c0));
           if (swiglu) {
-            float o[16];
+            float o[8];
 #pragma unroll
-            for (int jx = 0; jx < 16; ++jx)
+            for (int jx = 0; jx < 8; ++jx)
               o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
-            store_out<TY, 16>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 32, ncols >> 1);
+            store_out<TY, 8>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 16, ncols >> 1);
           } else {
 #pragma unroll
-            for (int jx = 0; jx < 32; ++jx) v[jx] *= gamma;
-            store_out<TY, 32>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 32, ncols);
+            for (int jx = 0; jx < 16; ++jx) v[jx] *= gamma;
+            store_out<TY, 16>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 16, ncols);
           }
+        };
+        uint32_t raw0[16], raw1[16];
+        tmem_ld16(taddr, raw0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+          tmem_ld_wait();
+          tmem_ld16(taddr + (uint32_t)(c0 + 16), raw1);
+          emit(raw0, c0);
+          tmem_ld_wait();
+          if (c0 + 32 < TILE_N) tmem_ld16(taddr + (uint32_t)(c0 + 32), raw0);
+          emit(raw1, c0 + 16);
         }
       }
       }
