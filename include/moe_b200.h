@@ -29,7 +29,7 @@ enum { MOE_ACT_NONE = 0, MOE_ACT_SWIGLU = 1 };
 enum { MOE_W_DENSE = 0,          /* w[e,k,n] in the activation dtype, arbitrary element strides */
        MOE_W_MX4_CANONICAL = 1,  /* e2m1x2 bytes packed along K (K contiguous) + e8m0 scales, byte strides */
        MOE_W_MX4_B200 = 2        /* tile-contiguous values + scales made by moe_weight_layout_to_b200 */ };
-enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2 };
+enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3 };
 
 const char* moe_last_error(void);
 int moe_abi_version(void);
@@ -175,6 +175,10 @@ typedef struct {
   int tile_m;                                      /* token rows per tile of the tcgen05 kernel: 0 auto, 128, 256 */
   int tile_n;                                      /* weight rows per tile: 0 auto, 128, 256 (256 needs tile_m 256) */
   int32_t* status;                                 /* device word, set non-zero when a bounded wait expires */
+  void* gather_scratch;                            /* optional device buffer of gather_scratch_bytes >= M * K * 2: with it, */
+  int64_t gather_scratch_bytes;                    /* large gathered problems first copy the gathered rows there (one pass
+                                                      over x) and the tensor-core kernel then streams consecutive rows by
+                                                      TMA instead of gathering 16 bytes at a time.  NULL: gather in-kernel. */
 } MoeGemmArgs;
 int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
 

@@ -99,7 +99,7 @@ SMALL = [
 
 @pytest.mark.parametrize("case", SMALL)
 @pytest.mark.parametrize("mode", ["plain", "gather", "scatter_w", "swiglu", "all"])
-@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256", "tcgen05-256x256"])
+@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256", "tcgen05-256x256", "tcgen05-pair"])
 def test_grouped_gemm(case, mode, path, device):
     E, K, N, sizes, T = case
     opts = dict(plain=dict(gather=False), gather=dict(gather=True),
@@ -109,8 +109,19 @@ def test_grouped_gemm(case, mode, path, device):
     layout, kernel, block_m, block_n = {
         "simt-canonical": ("canonical", "simt", None, None), "simt-blackwell": ("blackwell", "simt", None, None),
         "tcgen05": ("b200", "tcgen05", 128, 128), "tcgen05-256": ("b200", "tcgen05", 256, 128),
-        "tcgen05-256x256": ("b200", "tcgen05", 256, 256)}[path]
+        "tcgen05-256x256": ("b200", "tcgen05", 256, 256), "tcgen05-pair": ("b200", "tcgen05-pair", 0, 0)}[path]
     y = run(p, device, layout, kernel, block_m, block_n)
+    check(p, y)
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05-pair"])
+@pytest.mark.parametrize("mode", ["gather", "all"])
+def test_grouped_gemm_pregathered_rows(kernel, mode, device):
+    """2048+ gathered rows with large experts: the rows are first copied into the scratch buffer the host passes and
+    the kernel streams them by TMA tile copies."""
+    opts = dict(gather=dict(gather=True), all=dict(gather=True, scatter=True, weights=True, act=True))[mode]
+    p = make_problem(4, 320, 256, [900, 700, 385, 127], 800, seed=11, device=device, **opts)
+    y = run(p, device, "b200", kernel, 0, 0)
     check(p, y)
 
 

@@ -4,6 +4,8 @@
 int moe_gemm_simt_launch(const GemmParams& p, int x_dtype, int y_dtype, int w_kind, int64_t grid_m, cudaStream_t st);
 int moe_gemm_tc_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st);
 bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why);
+int moe_gemm_tc_pair_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st);
+bool moe_gemm_tc_pair_supported(const MoeGemmArgs& a, const char** why);
 
 // upper bound on the number of row blocks (triton_kernels tensor_details/ragged_tensor.py:73-77)
 static int64_t n_blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
@@ -48,12 +50,31 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
 
   const char* why = "";
   bool tc = moe_gemm_tc_supported(*a, &why);
-  if (a->kernel == MOE_GEMM_TCGEN05 && !tc) {
+  if ((a->kernel == MOE_GEMM_TCGEN05 || a->kernel == MOE_GEMM_TCGEN05_PAIR) && !tc) {
     moe_set_error("moe_grouped_gemm: tcgen05 kernel not applicable: %s", why);
     return MOE_ERR_UNSUPPORTED;
   }
   if (a->kernel == MOE_GEMM_SIMT) tc = false;
-  if (tc) return moe_gemm_tc_launch(p, *a, st);
+  if (tc) {
+    // Large problems run on pairs of SMs (256 x 256 tiles, cta_group::2); small ones and explicit tile requests on
+    // the single-SM kernel.
+    bool pair = moe_gemm_tc_pair_supported(*a, &why);
+    if (a->kernel == MOE_GEMM_TCGEN05_PAIR && !pair) {
+      moe_set_error("moe_grouped_gemm: SM-pair tcgen05 kernel not applicable: %s", why);
+      return MOE_ERR_UNSUPPORTED;
+    }
+    if (a->kernel != MOE_GEMM_TCGEN05_PAIR) pair = false;
+    // Large gathered problems: copy the gathered rows once into the caller's scratch, then stream them by TMA.
+    const bool big = a->tile_m != 128 && (a->tile_m == 256 || a->M / (a->E > 0 ? a->E : 1) >= 192);
+    if (a->gather_indx && a->gather_scratch && big && a->gather_scratch_bytes >= (int64_t)a->M * a->K * 2) {
+      const int rc = moe_gather_rows(a->x, a->ld_x * 2, a->gather_indx, a->M, (int64_t)a->K * 2, a->gather_scratch,
+                                     (int64_t)a->K * 2, stream);
+      if (rc != MOE_OK) return rc;
+      p.x = a->gather_scratch; p.ld_x = a->K; p.rows_x = a->M; p.gather_indx = nullptr;
+    }
+    if (pair) return moe_gemm_tc_pair_launch(p, *a, st);
+    return moe_gemm_tc_launch(p, *a, st);
+  }
 
   MOE_CHECK_ARG(a->w_kind == MOE_W_DENSE || a->w_kind == MOE_W_MX4_CANONICAL,
                 "moe_grouped_gemm: the SIMT kernel takes dense or canonical MXFP4 weights (%s)", why);

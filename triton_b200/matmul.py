@@ -282,9 +282,14 @@ def matmul(a, b, bias,
         args.activation, args.act_alpha = _lib.MOE_ACT_SWIGLU, float(alpha)
         args.act_limit, args.act_has_limit = (float(limit), 1) if limit is not None else (0.0, 0)
     args.y, args.y_dtype, args.ld_y = c.data_ptr(), _lib.dtype_code(c.dtype), c.stride(0)
-    args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05}[kernel_choice]
+    args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05,
+                   "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR}[kernel_choice]
     args.tile_m, args.tile_n = resolve_tile_m(), resolve_tile_n()
     args.status = _status_word(dev).data_ptr()
+    if gather_indx is not None and args.w_kind == _lib.MOE_W_MX4_B200 and a.dtype == torch.bfloat16 and M >= 2048:
+        scratch = torch.empty(M * K, dtype=torch.bfloat16, device=dev)   # the library decides whether to use it
+        keep.append(scratch)
+        args.gather_scratch, args.gather_scratch_bytes = scratch.data_ptr(), scratch.numel() * 2
     st = lib.moe_grouped_gemm(args, _lib.stream())
     if st == 3:
         raise InapplicableConstraint(lib.moe_last_error().decode(errors="replace"))
