@@ -178,15 +178,74 @@ def gemm_traffic_note():
     return None
 
 
+def micro_bench(args):
+    """Standalone routing / MXFP4 quantiser timings against the measured copy bandwidth.
+
+    Every timed call runs after a 512 MB write that evicts its inputs from L2; the time is the mean of per-call CUDA
+    event pairs.  Bytes are algorithmic: what the operator must read and write once."""
+    import triton_b200 as tb
+    from triton_b200.numerics_details.mxfp import downcast_to_mxfp, upcast_from_mxfp
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        ts = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sum(ts) / len(ts)
+
+    out = {"micro": args.micro, "steps": args.steps, "l2": "flushed by a 512 MB write before every timed call",
+           "peak_gbs": peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth", "kernels": {}}
+
+    def add(name, ms, nbytes):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out["kernels"][name] = {"ms": ms, "algorithmic_bytes": nbytes, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]}
+
+    if args.micro == "routing":
+        T, E, k = 16384, N_EXPTS, TOP_K
+        logits = torch.randn(T, E, device=dev, generator=g)
+        sp = tb.topk(logits, k)
+        add("topk [16384,128] fp32 -> top-4 values, indices, bitmatrix", timed(lambda: tb.topk(logits, k)),
+            T * E * 4 + T * k * (4 + 2) + T * (E // 8))
+        add("routing (topk + expert sort + ragged metadata)", timed(lambda: tb.routing(logits, k)),
+            T * E * 4 + T * k * (4 + 2) + T * (E // 8) + T * k * (2 + 4 + 4) + E * 4 * 12)
+    else:
+        R = C = 8192
+        x = torch.randn(R, C, device=dev, generator=g)
+        x = torch.where(torch.rand(R, C, device=dev, generator=g) < 0.01, x * 100, x).bfloat16()
+        q, sc = downcast_to_mxfp(x, torch.uint8, axis=1)
+        add("downcast_to_mxfp bf16 [8192,8192] axis 1", timed(lambda: downcast_to_mxfp(x, torch.uint8, axis=1)),
+            R * C * 2 + R * C // 2 + R * C // 32)
+        add("upcast_from_mxfp -> bf16 [8192,8192] axis 1", timed(lambda: upcast_from_mxfp(q, sc, torch.bfloat16, axis=1)),
+            R * C * 2 + R * C // 2 + R * C // 32)
+        q0, sc0 = downcast_to_mxfp(x, torch.uint8, axis=0)
+        add("downcast_to_mxfp bf16 [8192,8192] axis 0 (strided)", timed(lambda: downcast_to_mxfp(x, torch.uint8, axis=0)),
+            R * C * 2 + R * C // 2 + R * C // 32)
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=16384, help="tokens per rank")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--micro", default=None, choices=["routing", "mxfp"],
+                    help="time the memory-bound kernels on their standalone configuration instead of the layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -195,6 +254,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.micro:
+        if rank == 0:
+            micro_bench(args)
         return
     if world != args.gpus:
         if args.gpus != 1 or world != 1:
@@ -356,7 +419,7 @@ def main():
         cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": cpu_sample_desc(),
                         "s_per_step": dt}
 
-    launches_per_step = 8 if world == 1 else 13     # topk, 3 sort passes, ragged, 2 GEMMs, reduce (+ remap, 4 row moves)
+    launches_per_step = 9 if world == 1 else 16     # topk, 3 sort passes, ragged, row gather, 2 GEMMs, reduce (+ exchange plan, remap, row moves)
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

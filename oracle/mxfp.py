@@ -91,7 +91,8 @@ def upcast_from_mxfp_oracle(q: torch.Tensor, scale: torch.Tensor, dtype: torch.d
 
     The fp32 product of the e2m1 value and 2^(byte-127) is clamped to the finite
     range of `dtype` and then cast; a scale byte of 0 is the bit pattern 0 << 23,
-    i.e. +0.0 (so the whole block dequantises to zero), as in the reference.
+    i.e. +0.0 (so the whole block dequantises to zero), as in the reference; a scale
+    byte of 0xFF turns its whole group into NaN.
     """
     axis = axis % q.ndim
     qn = q.transpose(axis, -1).contiguous().numpy()
@@ -110,6 +111,9 @@ def upcast_from_mxfp_oracle(q: torch.Tensor, scale: torch.Tensor, dtype: torch.d
     with np.errstate(over="ignore", invalid="ignore"):
         out = vals.reshape(vals.shape[:-1] + (-1, MX_BLOCK)) * s[..., None]
     fi = torch.finfo(dtype)
-    out = np.clip(out, np.float32(fi.min), np.float32(fi.max)).reshape(vals.shape)[..., :L]
+    out = np.clip(out, np.float32(fi.min), np.float32(fi.max))
+    # the e8m0 byte 0xFF encodes NaN: the reference's kernel overwrites the whole group
+    # (mxfp_details/_upcast_from_mxfp.py:85), where its torch restatement leaves +-max and NaN only for zero codes
+    out = np.where((sn == 0xFF)[..., None], np.float32(np.nan), out).reshape(vals.shape)[..., :L]
     t = torch.from_numpy(np.ascontiguousarray(out)).to(dtype)
     return t.transpose(axis, -1)

@@ -64,6 +64,21 @@ def test_extreme_values_and_exact_round_trip(dt, device):
     assert torch.equal(upcast_from_mxfp(q, s, dt, axis=1), w)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+def test_upcast_every_scale_byte_and_code(dt, device):
+    """All 256 e8m0 bytes x all 16 e2m1 codes: zero scale, denormal results, saturation at the largest scales and the
+    NaN byte, bit for bit against the oracle."""
+    codes = torch.arange(16, dtype=torch.uint8)
+    row = (codes | (codes.flip(0) << 4)).repeat(1)            # 16 bytes = 32 codes, every code in both nibbles
+    q = row.repeat(256, 1)                                    # one 32-group per scale byte
+    s = torch.arange(256, dtype=torch.int32).to(torch.uint8).view(256, 1)
+    want = oracle.upcast_from_mxfp_oracle(q, s, dt, axis=1)
+    got = upcast_from_mxfp(q.to(device), s.to(device), dt, axis=1).cpu()
+    nan = torch.isnan(want.float())
+    assert torch.equal(torch.isnan(got.float()), nan)
+    assert torch.equal(bits(want.contiguous())[~nan], bits(got.contiguous())[~nan])
+
+
 def test_pitched_input(device):
     # reference tests/test_mxfp.py:208-220
     torch.manual_seed(0)

@@ -12,6 +12,7 @@
 // Both kernels are HBM-bound: 16-byte loads/stores, four threads per 32-group on the contiguous path.
 #include "common.cuh"
 #include <cuda_fp4.h>
+#include <type_traits>
 
 namespace {
 
@@ -24,10 +25,25 @@ __device__ __forceinline__ uint32_t scale_bits(float m, int mode) {
   return __float_as_uint(ds) & 0x7F800000u;
 }
 
+// 1 / u for u = 2^(e - 127) stored as e << 23: the exponent mirrored around the bias, exactly what an IEEE division
+// returns.  e = 0 (group of zeros) gives 0 as in the reference; e <= 253 always holds because max|x| / 4 < 2^127.
 __device__ __forceinline__ float inv_scale(uint32_t u) {
-  float f = __uint_as_float(u);
-  return (f == 0.0f) ? 0.0f : __fdiv_rn(1.0f, f);
+  return (u == 0u) ? 0.0f : __uint_as_float(0x7F000000u - u);
 }
+
+// Position of a grid-stride loop over [rows][chunks per row] without a division per iteration.
+struct RowCursor {
+  int64_t row, c, step_row, step_c, per_row;
+  __device__ __forceinline__ RowCursor(int64_t first, int64_t stride, int64_t chunks_per_row) {
+    per_row = chunks_per_row;
+    row = first / chunks_per_row; c = first - row * chunks_per_row;
+    step_row = stride / chunks_per_row; step_c = stride - step_row * chunks_per_row;
+  }
+  __device__ __forceinline__ void next() {
+    row += step_row; c += step_c;
+    if (c >= per_row) { c -= per_row; ++row; }
+  }
+};
 
 // two fp32 -> one byte: `lo` in bits 0..3, `hi` in bits 4..7 (round-to-nearest-even, saturating)
 __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
@@ -40,49 +56,63 @@ template <> struct Vec16<__half> { static constexpr int N = 8; };
 template <> struct Vec16<float> { static constexpr int N = 4; };
 
 // ---- contiguous path: quant axis has unit stride, rows 16-byte aligned ------------------------------
-// One thread owns 8 consecutive elements; 4 consecutive lanes own one 32-group.
+// One thread owns 8 consecutive elements; 4 consecutive lanes own one 32-group.  A block walks tiles of
+// ROWS_UNROLL x 256 chunks and every thread issues the loads of its ROWS_UNROLL chunks before it converts the first,
+// so that enough bytes are in flight per SM to cover the HBM latency.
+constexpr int ROWS_UNROLL = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(256) downcast_rows_kernel(const T* __restrict__ x, int64_t n_rows, int64_t quant,
                                                             int64_t outer, int64_t sx_batch, int64_t sx_outer,
                                                             uint8_t* __restrict__ q, uint8_t* __restrict__ scale,
                                                             int mode) {
+  constexpr int VPC = sizeof(T) == 2 ? 1 : 2;            // 16-byte vectors per 8-element chunk
   const int64_t chunks_per_row = quant >> 3;
   const int64_t total = n_rows * chunks_per_row;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t stride = (int64_t)gridDim.x * (ROWS_UNROLL * 256);
+  const int64_t tile0 = (int64_t)blockIdx.x * (ROWS_UNROLL * 256);
+  RowCursor cur[ROWS_UNROLL] = {RowCursor(tile0 + threadIdx.x, stride, chunks_per_row),
+                                RowCursor(tile0 + 256 + threadIdx.x, stride, chunks_per_row),
+                                RowCursor(tile0 + 512 + threadIdx.x, stride, chunks_per_row),
+                                RowCursor(tile0 + 768 + threadIdx.x, stride, chunks_per_row)};
+  const bool one_batch = outer == n_rows;
   // every lane of a warp runs the same trip count (the shuffles below need the whole warp); lanes past the
   // end compute on zeros and store nothing
-  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31); i0 < total; i0 += stride) {
-    const int64_t i = i0 + (threadIdx.x & 31);
-    const bool live = i < total;
-    const int64_t ii = live ? i : 0;
-    const int64_t row = ii / chunks_per_row;
-    const int64_t c = ii - row * chunks_per_row;
-    const int64_t b = row / outer, o = row - b * outer;
-    const T* src = x + b * sx_batch + o * sx_outer + c * 8;
-    float v[8];
-    if constexpr (sizeof(T) == 2) {
-      uint4 raw = *reinterpret_cast<const uint4*>(src);
-      const T* e = reinterpret_cast<const T*>(&raw);
+  for (int64_t tile = tile0; tile < total; tile += stride) {
+    uint4 raw[ROWS_UNROLL][VPC];
+    bool live[ROWS_UNROLL];
+#pragma unroll
+    for (int u = 0; u < ROWS_UNROLL; ++u) {
+      live[u] = tile + u * 256 + threadIdx.x < total;
+      const int64_t row = live[u] ? cur[u].row : 0, c = live[u] ? cur[u].c : 0;
+      int64_t b = 0, o = row;
+      if (!one_batch) { b = row / outer; o = row - b * outer; }
+      const uint4* src = reinterpret_cast<const uint4*>(x + b * sx_batch + o * sx_outer + c * 8);
+#pragma unroll
+      for (int k = 0; k < VPC; ++k) raw[u][k] = src[k];
+    }
+#pragma unroll
+    for (int u = 0; u < ROWS_UNROLL; ++u) {
+      float v[8];
+      const T* e = reinterpret_cast<const T*>(&raw[u][0]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
-    } else {
-      float4 a = *reinterpret_cast<const float4*>(src);
-      float4 bb = *reinterpret_cast<const float4*>(src + 4);
-      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = bb.x; v[5] = bb.y; v[6] = bb.z; v[7] = bb.w;
-    }
-    float m = 0.0f;
+      float m = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
-    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
-    const uint32_t u = scale_bits(m, mode);
-    const float inv = inv_scale(u);
-    uint32_t packed = 0;
+      for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+      m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+      const uint32_t sc = scale_bits(m, mode);
+      const float inv = inv_scale(sc);
+      uint32_t packed = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) packed |= e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
-    if (live) {
-      *reinterpret_cast<uint32_t*>(q + row * (quant >> 1) + c * 4) = packed;
-      if ((c & 3) == 0) scale[row * (quant >> 5) + (c >> 2)] = (uint8_t)(u >> 23);
+      for (int j = 0; j < 4; ++j) packed |= e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
+      if (live[u]) {
+        const int64_t row = cur[u].row, c = cur[u].c;
+        *reinterpret_cast<uint32_t*>(q + row * (quant >> 1) + c * 4) = packed;
+        if ((c & 3) == 0) scale[row * (quant >> 5) + (c >> 2)] = (uint8_t)(sc >> 23);
+      }
+      cur[u].next();
     }
   }
 }
@@ -146,7 +176,37 @@ __device__ __forceinline__ T dequant_one(uint32_t code, float s, bool nan_scale)
   return from_f32<T>(r);
 }
 
-// contiguous output: thread owns 8 elements (4 input bytes)
+// bf16 fast path: the three magnitude bits of a code placed at bf16 bits 8:6 are value * 2^-126, and one
+// bf16x2 multiply by 2^(sb - 1) gives value * 2^(sb - 127) exactly (every product is representable; sb = 0 multiplies
+// by zero as the reference's scale bits 0 << 23 do).  Scale bytes from 253 up can overflow and take the general path.
+__device__ __forceinline__ uint32_t bf16x2_mul_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// codes k and k + 4 of word w (nibble p holds element p) -> bf16x2 (low half: element k) of value * 2^-126
+template <int K> __device__ __forceinline__ uint32_t e2m1_pair_k(uint32_t w) {
+  const uint32_t mag = (K < 2 ? (w << (6 - 4 * K)) : (w >> (4 * K - 6))) & 0x01C001C0u;
+  const uint32_t sgn = (w << (12 - 4 * K)) & 0x80008000u;
+  return mag | sgn;
+}
+__device__ __forceinline__ uint4 upcast8_bf16(uint32_t w, uint32_t sb) {
+  uint32_t c2, r[4];
+  if (sb <= 128u) {
+    c2 = (sb ? ((sb + 126u) << 7) : 0u) * 0x10001u;
+    r[0] = bf16x2_mul_rn(e2m1_pair_k<0>(w), c2); r[1] = bf16x2_mul_rn(e2m1_pair_k<1>(w), c2);
+    r[2] = bf16x2_mul_rn(e2m1_pair_k<2>(w), c2); r[3] = bf16x2_mul_rn(e2m1_pair_k<3>(w), c2);
+  } else {                                           // 2^(sb - 1) is not a bf16: multiply by 2^126, then by 2^(sb - 127)
+    const uint32_t k2 = 0x7E807E80u, s2 = (sb << 7) * 0x10001u;
+    r[0] = bf16x2_mul_rn(bf16x2_mul_rn(e2m1_pair_k<0>(w), k2), s2); r[1] = bf16x2_mul_rn(bf16x2_mul_rn(e2m1_pair_k<1>(w), k2), s2);
+    r[2] = bf16x2_mul_rn(bf16x2_mul_rn(e2m1_pair_k<2>(w), k2), s2); r[3] = bf16x2_mul_rn(bf16x2_mul_rn(e2m1_pair_k<3>(w), k2), s2);
+  }
+  // r[k] = (element k, element k + 4): back to element order
+  return make_uint4(__byte_perm(r[0], r[1], 0x5410), __byte_perm(r[2], r[3], 0x5410), __byte_perm(r[0], r[1], 0x7632),
+                    __byte_perm(r[2], r[3], 0x7632));
+}
+
+// contiguous output: thread owns 8 elements (4 input bytes) of each of ROWS_UNROLL chunks per iteration
 template <typename T>
 __global__ void __launch_bounds__(256) upcast_rows_kernel(const uint8_t* __restrict__ q,
                                                           const uint8_t* __restrict__ scale, T* __restrict__ out,
@@ -154,24 +214,48 @@ __global__ void __launch_bounds__(256) upcast_rows_kernel(const uint8_t* __restr
                                                           int64_t so_batch, int64_t so_outer) {
   const int64_t chunks_per_row = quant >> 3;
   const int64_t total = n_rows * chunks_per_row;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int64_t row = i / chunks_per_row;
-    const int64_t c = i - row * chunks_per_row;
-    const int64_t b = row / outer, o = row - b * outer;
-    const uint32_t w = *reinterpret_cast<const uint32_t*>(q + row * (quant >> 1) + c * 4);
-    const uint32_t sb = scale[row * (quant >> 5) + (c >> 2)];
-    const float s = __uint_as_float(sb << 23);
-    const bool nan_scale = sb == 0xFFu;
-    T* dst = out + b * so_batch + o * so_outer + c * 8;
-    T e[8];
+  const int64_t stride = (int64_t)gridDim.x * (ROWS_UNROLL * 256);
+  const int64_t tile0 = (int64_t)blockIdx.x * (ROWS_UNROLL * 256);
+  RowCursor cur[ROWS_UNROLL] = {RowCursor(tile0 + threadIdx.x, stride, chunks_per_row),
+                                RowCursor(tile0 + 256 + threadIdx.x, stride, chunks_per_row),
+                                RowCursor(tile0 + 512 + threadIdx.x, stride, chunks_per_row),
+                                RowCursor(tile0 + 768 + threadIdx.x, stride, chunks_per_row)};
+  const bool one_batch = outer == n_rows;
+  for (int64_t tile = tile0; tile < total; tile += stride) {
+    uint32_t w[ROWS_UNROLL], sb[ROWS_UNROLL];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) e[j] = dequant_one<T>((w >> (4 * j)) & 0xFu, s, nan_scale);
-    if constexpr (sizeof(T) == 2) {
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(e);
-    } else {
-      *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(e);
-      *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(e + 4);
+    for (int u = 0; u < ROWS_UNROLL; ++u) {
+      const bool live = tile + u * 256 + threadIdx.x < total;
+      const int64_t row = live ? cur[u].row : 0, c = live ? cur[u].c : 0;
+      w[u] = *reinterpret_cast<const uint32_t*>(q + row * (quant >> 1) + c * 4);
+      sb[u] = scale[row * (quant >> 5) + (c >> 2)];
+    }
+#pragma unroll
+    for (int u = 0; u < ROWS_UNROLL; ++u) {
+      const bool live = tile + u * 256 + threadIdx.x < total;
+      const int64_t row = cur[u].row, c = cur[u].c;
+      cur[u].next();
+      if (!live) continue;
+      int64_t b = 0, o = row;
+      if (!one_batch) { b = row / outer; o = row - b * outer; }
+      T* dst = out + b * so_batch + o * so_outer + c * 8;
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (sb[u] < 253u) {
+          *reinterpret_cast<uint4*>(dst) = upcast8_bf16(w[u], sb[u]);
+          continue;
+        }
+      }
+      const float s = __uint_as_float(sb[u] << 23);
+      const bool nan_scale = sb[u] == 0xFFu;
+      T e[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = dequant_one<T>((w[u] >> (4 * j)) & 0xFu, s, nan_scale);
+      if constexpr (sizeof(T) == 2) {
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(e);
+      } else {
+        *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(e);
+        *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(e + 4);
+      }
     }
   }
 }
@@ -226,7 +310,7 @@ extern "C" __attribute__((visibility("default"))) int moe_downcast_mxfp4(const v
                          (sx_batch % align == 0) && ((uintptr_t)q % 4 == 0);
     if (rows_ok) {
       const int64_t total = batch * outer * (quant >> 3);
-      downcast_rows_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, batch * outer, quant, outer, sx_batch,
+      downcast_rows_kernel<T><<<grid_for(total, ROWS_UNROLL * 256), 256, 0, st>>>((const T*)x, batch * outer, quant, outer, sx_batch,
                                                                     sx_outer, q, scale, rounding_mode);
     } else {
       MOE_CHECK_ARG((uintptr_t)q % 16 == 0, "moe_downcast_mxfp4: q must be 16-byte aligned");
@@ -253,7 +337,7 @@ extern "C" __attribute__((visibility("default"))) int moe_upcast_mxfp4(const uin
                          (so_batch % align == 0) && ((uintptr_t)q % 4 == 0);
     if (rows_ok) {
       const int64_t total = batch * outer * (quant >> 3);
-      upcast_rows_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(q, scale, (T*)out, batch * outer, quant, outer,
+      upcast_rows_kernel<T><<<grid_for(total, ROWS_UNROLL * 256), 256, 0, st>>>(q, scale, (T*)out, batch * outer, quant, outer,
                                                                   so_batch, so_outer);
     } else {
       MOE_CHECK_ARG((uintptr_t)q % 16 == 0, "moe_upcast_mxfp4: q must be 16-byte aligned");
