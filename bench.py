@@ -244,6 +244,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=16384, help="tokens per rank")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="expert-parallel exchange: kernels over peer-mapped buffers, or NCCL all-to-all")
     ap.add_argument("--micro", default=None, choices=["routing", "mxfp"],
                     help="time the memory-bound kernels on their standalone configuration instead of the layer")
     args = ap.parse_args()
@@ -290,10 +292,12 @@ def main():
         assignment = tb.make_expt_assignment(world, N_EXPTS, tb.make_expt_dict_uniform(world, N_EXPTS), dev)
         pool = tb.SymmetricMemoryPool(tb.Mesh(dist.group.WORLD))
         pool.initialize_matmul(T * world, D_MODEL, D_MODEL, TOP_K, N_EXPTS, torch.bfloat16, dev)
+        if args.exchange != "nccl":
+            pool.enable_peer_buffers(T, D_MODEL, D_MODEL, TOP_K, torch.bfloat16, dev)
 
     def step(xi, li, timer=None):
         if world > 1:
-            return moe_layer_forward_ep(xi, li, lw, TOP_K, assignment, pool, gemm_timer=timer)
+            return moe_layer_forward_ep(xi, li, lw, TOP_K, assignment, pool, gemm_timer=timer, exchange=args.exchange)
         return moe_layer_forward(xi, li, lw, TOP_K, gemm_timer=timer)
 
     def barrier():
@@ -425,7 +429,10 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(T, world), "l2": "inputs larger than L2 (weights streamed once per step)",
+            "config": {"workload": workload_name(T, world),
+                       "exchange": None if world == 1 else ("peer-mapped buffers" if pool.peer_ok else
+                                                            f"NCCL all-to-all ({pool.peer_error})"),
+                       "l2": "inputs larger than L2 (weights streamed once per step)",
                        "tflops_per_step_algorithmic": flop_per_step * world / 1e12 if world > 1 else flop_per_step / 1e12},
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline, "cpu_baseline": cpu_baseline,

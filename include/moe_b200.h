@@ -29,6 +29,7 @@ enum { MOE_ACT_NONE = 0, MOE_ACT_SWIGLU = 1 };
 enum { MOE_W_DENSE = 0,          /* w[e,k,n] in the activation dtype, arbitrary element strides */
        MOE_W_MX4_CANONICAL = 1,  /* e2m1x2 bytes packed along K (K contiguous) + e8m0 scales, byte strides */
        MOE_W_MX4_B200 = 2        /* tile-contiguous values + scales made by moe_weight_layout_to_b200 */ };
+#define MOE_MAX_PEERS 16
 enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3 };
 
 const char* moe_last_error(void);
@@ -175,6 +176,10 @@ typedef struct {
   int tile_m;                                      /* token rows per tile of the tcgen05 kernel: 0 auto, 128, 256 */
   int tile_n;                                      /* weight rows per tile: 0 auto, 128, 256 (256 needs tile_m 256) */
   int32_t* status;                                 /* device word, set non-zero when a bounded wait expires */
+  void* y_peers[MOE_MAX_PEERS];                    /* optional: output rows live on n_y_peers devices.  Output row index r */
+  int n_y_peers;                                   /* (m, or scatter_indx[m]) is row r % y_rows_per_peer of the buffer */
+  int64_t y_rows_per_peer;                         /* y_peers[r / y_rows_per_peer] (peer-mapped memory, same ld_y and dtype);
+                                                      the epilogue stores there directly.  n_y_peers = 0: everything goes to y. */
   void* gather_scratch;                            /* optional device buffer of gather_scratch_bytes >= M * K * 2: with it, */
   int64_t gather_scratch_bytes;                    /* large gathered problems first copy the gathered rows there (one pass
                                                       over x) and the tensor-core kernel then streams consecutive rows by
@@ -194,6 +199,13 @@ int moe_ep_keys(const int32_t* col_sorted, const int16_t* expt_indx, const int32
                 int entries_per_rank, int world, int16_t* keys, void* stream);
 int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
                     void* dst, int64_t ld_dst, void* stream);
+/* moe_gather_rows over rows that live on several devices: global row g = row_indx[r] is row g % rows_per_peer of
+ * src_peers[g / rows_per_peer] (a host array of n_peers <= MOE_MAX_PEERS device pointers, peer-mapped memory
+ * included; same pitch ld_src bytes); g = -1 writes zeros, g = -2 leaves the output row untouched.  The pull half of the expert-parallel dispatch
+ * (distributed.py:176-211 does the same exchange with peer stores).                                            */
+int moe_gather_rows_peers(const void* const* src_peers, int n_peers, int64_t rows_per_peer, int64_t ld_src,
+                          const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes, void* dst, int64_t ld_dst,
+                          void* stream);
 /* y[t, :] = sum over j < k of src[row_indx[t * k + j], :] (negative index: skipped); bf16 rows, fp32 sum.  The
  * k-way combine (reduce.py:1143-1165 with dim = 1) read through an index, used after the combine exchange.   */
 int moe_gather_reduce_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t T, int k, int64_t d,

@@ -44,14 +44,19 @@ def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
         pool.initialize_matmul(n_tokens, d_model, d_model, k, n_expts, torch.bfloat16, dev)
         T_local = n_tokens // world
         sl = slice(rank * T_local, (rank + 1) * T_local)
-        for fused in (False, True, True):                   # the reference's composition, then the fused exchange twice
+        # the reference's composition, the fused NCCL exchange twice, then the peer-memory exchange twice
+        variants = [("nccl", False), ("nccl", True), ("nccl", True)]
+        if pool.enable_peer_buffers(T_local, d_model, d_model, k, torch.bfloat16, dev):
+            variants += [("peer", True), ("peer", True)]
+        ret[f"peer{rank}"] = pool.peer_ok or pool.peer_error
+        for exchange, fused in variants:
             z_loc = moe_layer_forward_ep(x[sl].contiguous(), logits[sl].contiguous(), lw_local, k, assign, pool,
-                                         fused_exchange=fused)
+                                         fused_exchange=fused, exchange=exchange)
             tb.matmul_check_status()
             z_all = torch.empty_like(z_ref)
             dist.all_gather_into_tensor(z_all, z_loc)
             oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3,
-                                       what=f"EP (fused={fused}) vs single GPU")
+                                       what=f"EP ({exchange}, fused={fused}) vs single GPU")
         ret[rank] = 1
     finally:
         dist.destroy_process_group()
@@ -80,7 +85,8 @@ def test_expert_parallel_layer_matches_single_gpu(world, n_tokens, d_model, d_ff
         if p.is_alive():
             p.kill()
     assert codes == [0] * world, codes
-    assert sorted(ret.keys()) == list(range(world))
+    assert sorted(k for k in ret.keys() if isinstance(k, int)) == list(range(world))
+    print("peer exchange:", {k: v for k, v in ret.items() if not isinstance(k, int)})
 
 
 @pytest.mark.parametrize("T_global, E, k, W", [(64, 16, 4, 4), (4096, 128, 4, 8), (1000, 37, 2, 2)])

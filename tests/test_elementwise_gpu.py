@@ -48,3 +48,26 @@ def test_reduce(shape, dim, mask_mode, device):
     y, _ = tb.reduce(x, dim, mask=mask, scale=scale)
     ref = oracle.reduce_oracle(x.cpu(), dim, None if mask is None else mask.cpu(), None if scale is None else scale.cpu())
     torch.testing.assert_close(y.cpu().float(), ref.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_gather_rows_over_peer_buffers(device):
+    """moe_gather_rows_peers with three buffers on one device standing in for three ranks: -1 writes zeros, -2 leaves
+    the row untouched."""
+    import ctypes
+    from triton_b200 import _lib
+    torch.manual_seed(0)
+    rows_per_peer, d = 37, 96
+    bufs = [torch.randn(rows_per_peer, d, device=device).bfloat16() for _ in range(3)]
+    allrows = torch.cat(bufs)
+    idx = torch.randint(0, 3 * rows_per_peer, (500,), device=device, dtype=torch.int32)
+    idx[::7] = -1
+    idx[3::11] = -2
+    out = torch.full((500, d), 7.0, device=device).bfloat16()
+    lib = _lib.load()
+    ptrs = (ctypes.c_void_p * 3)(*[b.data_ptr() for b in bufs])
+    _lib.check(lib.moe_gather_rows_peers(ptrs, 3, rows_per_peer, d * 2, _lib.ptr(idx), 500, d * 2, _lib.ptr(out), d * 2,
+                                         _lib.stream()), "moe_gather_rows_peers")
+    want = allrows[idx.long().clamp_min(0)]
+    want[idx == -1] = 0
+    want[idx == -2] = 7.0
+    assert torch.equal(out, want)

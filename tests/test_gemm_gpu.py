@@ -125,6 +125,34 @@ def test_grouped_gemm_pregathered_rows(kernel, mode, device):
     check(p, y)
 
 
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
+@pytest.mark.parametrize("sizes, T", [([13, 0, 29, 8], 50), ([600, 256, 257, 511], 700)])
+def test_fused_comm_block_rows(kernel, sizes, T, device):
+    """Output rows spread over three buffers (here all on one device): row r of the scattered output lands in row
+    r % rows_per_shard of buffer r // rows_per_shard."""
+    p = make_problem(4, 320, 128, sizes, T, seed=5, device=device, gather=True, scatter=True, weights=True)
+    M = p["M"]
+    shards = 3
+    rows_per_shard = (M + shards - 1) // shards
+    bufs = [torch.zeros(rows_per_shard, 128, dtype=torch.bfloat16, device=device) for _ in range(shards)]
+    dev = lambda t: None if t is None else t.to(device)
+    layout = "canonical" if kernel == "simt" else "b200"
+    wq = wrap_torch_tensor(dev(p["wq"]), dtype=FP4)
+    ws = wrap_torch_tensor(dev(p["ws"]))
+    if layout == "b200":
+        wq, ws = convert_layout(wq, B200MXValueLayout()), convert_layout(ws, B200MXScaleLayout())
+    md = tb.make_ragged_tensor_metadata(dev(p["sizes"]), M)
+    pc = tb.PrecisionConfig(b_mx_scale=ws, b_microblock_size=32)
+    fc = tb.FusedComm([b.data_ptr() for b in bufs], rows_per_shard, bufs[0])
+    with tb.scoped_opt_flags_constraints({"kernel": kernel}):
+        y0 = tb.matmul(dev(p["x"]), wq, dev(p["bias"]), md, None, dev(p["gather"]), dev(p["scatter"]), pc,
+                       betas=dev(p["betas"]), gammas=dev(p["gammas"]), fused_comm=fc)
+    tb.matmul_check_status()
+    assert y0.data_ptr() == bufs[0].data_ptr()
+    y = torch.cat(bufs)[:M]
+    check(p, y)
+
+
 def test_against_reference_fixture(golden, device):
     g = golden("gemm_small")
     wq = wrap_torch_tensor(g["wq"].to(device).transpose(1, 2).contiguous().transpose(1, 2), dtype=FP4)

@@ -5,7 +5,7 @@ dispatch / combine) as hand-written CUDA for sm_100a behind a C ABI (include/moe
 Importing the package does not need a GPU; calling an operator does, and needs libmoe_b200.so
 (``python -m triton_b200.build``).  There is no fallback path."""
 from . import _lib  # noqa: F401
-from .matmul import (Epilogue, FlexCtx, FnName, FusedActivation, InapplicableConstraint, PrecisionConfig,  # noqa: F401
+from .matmul import (Epilogue, FlexCtx, FnName, FusedActivation, FusedComm, InapplicableConstraint, PrecisionConfig,  # noqa: F401
                      matmul, matmul_check_status, matmul_ogs, matmul_set_idle_sms, reset_opt_flags_constraints,
                      scoped_opt_flags_constraints, update_opt_flags_constraints)
 from .numerics import InFlexData, OutFlexData  # noqa: F401

@@ -19,6 +19,7 @@ MOE_ROUND_UP, MOE_ROUND_DOWN = 0, 1
 MOE_ACT_NONE, MOE_ACT_SWIGLU = 0, 1
 MOE_W_DENSE, MOE_W_MX4_CANONICAL, MOE_W_MX4_B200 = 0, 1, 2
 MOE_GEMM_AUTO, MOE_GEMM_SIMT, MOE_GEMM_TCGEN05, MOE_GEMM_TCGEN05_PAIR = 0, 1, 2, 3
+MOE_MAX_PEERS = 16
 
 _DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: MOE_BF16}
 
@@ -44,6 +45,7 @@ class MoeGemmArgs(C.Structure):
         ("activation", i32), ("act_alpha", f32), ("act_limit", f32), ("act_has_limit", i32),
         ("y", vp), ("y_dtype", i32), ("ld_y", i64),
         ("kernel", i32), ("tile_m", i32), ("tile_n", i32), ("status", vp),
+        ("y_peers", vp * 16), ("n_y_peers", i32), ("y_rows_per_peer", i64),
         ("gather_scratch", vp), ("gather_scratch_bytes", i64),
     ]
 
@@ -72,6 +74,7 @@ PROTOTYPES = {
     "moe_grouped_gemm": (i32, [C.POINTER(MoeGemmArgs), vp]),
     "moe_ep_keys": (i32, [vp, vp, vp, i64, i32, i32, vp, vp]),
     "moe_gather_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
+    "moe_gather_rows_peers": (i32, [vp, i32, i64, i64, vp, i64, i64, vp, i64, vp]),
     "moe_gather_reduce_rows": (i32, [vp, i64, vp, i64, i32, i64, vp, i64, vp]),
     "moe_scatter_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
 }

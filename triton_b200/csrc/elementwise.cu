@@ -123,6 +123,28 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
   }
 }
 
+// Rows spread over several devices: global row g lives in buffer g / rows_per_peer at row g % rows_per_peer.
+struct PeerBases { const uint8_t* base[MOE_MAX_PEERS]; };
+
+// dst[r, :] = peers[indx[r] / rows_per_peer][indx[r] % rows_per_peer, :]; indx -1: zeros, indx -2: row left untouched.
+// One block walks whole rows, so a skipped row costs one index read per block.
+__global__ void __launch_bounds__(128) gather_rows_peers_kernel(PeerBases peers, int64_t rows_per_peer, int64_t ld_src,
+                                                                const int32_t* __restrict__ indx, int64_t n_out,
+                                                                int64_t row_bytes, uint8_t* __restrict__ dst, int64_t ld_dst) {
+  const int vec_per_row = (int)(row_bytes >> 4);
+  for (int64_t r = blockIdx.x; r < n_out; r += gridDim.x) {
+    const int32_t s = indx[r];
+    if (s == -2) continue;
+    const uint4* src = nullptr;
+    if (s >= 0) {
+      const int64_t peer = s / rows_per_peer;
+      src = reinterpret_cast<const uint4*>(peers.base[peer] + (s - peer * rows_per_peer) * ld_src);
+    }
+    uint4* out = reinterpret_cast<uint4*>(dst + r * ld_dst);
+    for (int c = threadIdx.x; c < vec_per_row; c += 128) out[c] = src ? src[c] : make_uint4(0, 0, 0, 0);
+  }
+}
+
 // dst[indx[i], :] = src[i, :]   (indx < 0: dropped)
 __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint8_t* __restrict__ src, int64_t ld_src,
                                                            const int32_t* __restrict__ indx, int64_t n_in,
@@ -225,6 +247,29 @@ extern "C" __attribute__((visibility("default"))) int moe_gather_rows(const void
                 "moe_gather_rows: rows must be 16-byte aligned multiples of 16 bytes");
   gather_rows_kernel<<<grid_for(n_rows_out * (row_bytes / 16), 256), 256, 0, (cudaStream_t)stream>>>(
       (const uint8_t*)src, ld_src, row_indx, n_rows_out, row_bytes, (uint8_t*)dst, ld_dst);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_gather_rows_peers(const void* const* src_peers, int n_peers, int64_t rows_per_peer,
+                                     int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
+                                     void* dst, int64_t ld_dst, void* stream) {
+  MOE_CHECK_ARG(n_rows_out >= 0 && row_bytes >= 0, "moe_gather_rows_peers: negative extent");
+  if (n_rows_out == 0 || row_bytes == 0) return MOE_OK;
+  MOE_CHECK_ARG(src_peers && dst && row_indx, "moe_gather_rows_peers: NULL pointer");
+  MOE_CHECK_ARG(n_peers >= 1 && n_peers <= MOE_MAX_PEERS && rows_per_peer > 0,
+                "moe_gather_rows_peers: need 1..%d peers and rows_per_peer > 0", MOE_MAX_PEERS);
+  MOE_CHECK_ARG(row_bytes % 16 == 0 && ld_src % 16 == 0 && ld_dst % 16 == 0 && (uintptr_t)dst % 16 == 0,
+                "moe_gather_rows_peers: rows must be 16-byte aligned multiples of 16 bytes");
+  PeerBases pb;
+  for (int i = 0; i < MOE_MAX_PEERS; ++i) {
+    pb.base[i] = i < n_peers ? (const uint8_t*)src_peers[i] : nullptr;
+    MOE_CHECK_ARG(i >= n_peers || (pb.base[i] && (uintptr_t)pb.base[i] % 16 == 0),
+                  "moe_gather_rows_peers: peer buffer %d is NULL or not 16-byte aligned", i);
+  }
+  const int64_t max_blocks = (int64_t)moe_sm_count() * 16;
+  gather_rows_peers_kernel<<<(int)(n_rows_out < max_blocks ? n_rows_out : max_blocks), 128, 0, (cudaStream_t)stream>>>(
+      pb, rows_per_peer, ld_src, row_indx, n_rows_out, row_bytes, (uint8_t*)dst, ld_dst);
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }

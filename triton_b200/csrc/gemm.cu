@@ -20,7 +20,7 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
   MOE_CHECK_ARG(a->E > 0 && a->K >= 0 && a->N >= 0 && a->M >= 0, "moe_grouped_gemm: bad extents E=%d K=%d N=%d M=%lld",
                 a->E, a->K, a->N, (long long)a->M);
   if (a->M == 0 || a->N == 0) return MOE_OK;
-  MOE_CHECK_ARG(a->x && a->w && a->y, "moe_grouped_gemm: NULL x / w / y");
+  MOE_CHECK_ARG(a->x && a->w && (a->y || a->n_y_peers > 0), "moe_grouped_gemm: NULL x / w / y");
   MOE_CHECK_ARG(a->w_kind == MOE_W_DENSE || a->w_scale, "moe_grouped_gemm: MXFP4 weights need w_scale");
   MOE_CHECK_ARG(a->w_kind == MOE_W_DENSE || a->K % 32 == 0, "moe_grouped_gemm: MXFP4 weights need K %% 32 == 0 (K=%d)", a->K);
   MOE_CHECK_ARG(a->activation == MOE_ACT_NONE || (a->activation == MOE_ACT_SWIGLU && a->N % 2 == 0),
@@ -47,6 +47,16 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
   p.activation = a->activation; p.act_alpha = a->act_alpha; p.act_limit = a->act_limit; p.act_has_limit = a->act_has_limit;
   p.y = a->y; p.ld_y = a->ld_y;
   p.status = a->status;
+  MOE_CHECK_ARG(a->n_y_peers >= 0 && a->n_y_peers <= MOE_MAX_PEERS, "moe_grouped_gemm: n_y_peers must be 0..%d", MOE_MAX_PEERS);
+  p.n_y_peers = a->n_y_peers; p.y_rows_per_peer = a->y_rows_per_peer;
+  for (int i = 0; i < MOE_MAX_PEERS; ++i) p.y_peers[i] = i < a->n_y_peers ? a->y_peers[i] : nullptr;
+  if (a->n_y_peers > 0) {
+    MOE_CHECK_ARG(a->y_rows_per_peer > 0, "moe_grouped_gemm: y_rows_per_peer must be positive with y_peers");
+    for (int i = 0; i < a->n_y_peers; ++i)
+      MOE_CHECK_ARG(a->y_peers[i] != nullptr && (uintptr_t)a->y_peers[i] % 16 == 0,
+                    "moe_grouped_gemm: y_peers[%d] is NULL or not 16-byte aligned", i);
+    p.y = a->y_peers[0];
+  }
 
   const char* why = "";
   bool tc = moe_gemm_tc_supported(*a, &why);

@@ -20,7 +20,15 @@ struct GemmParams {
   int activation; float act_alpha, act_limit; int act_has_limit;
   void* y; int64_t ld_y;
   int32_t* status;
+  void* y_peers[MOE_MAX_PEERS]; int n_y_peers; int64_t y_rows_per_peer;   // output rows spread over peer buffers
 };
+
+// first element of output row `dst`: in y, or in the peer buffer that holds that row
+template <typename TY> __device__ __forceinline__ TY* gemm_out_row(const GemmParams& p, int64_t dst) {
+  if (p.n_y_peers == 0) return (TY*)p.y + dst * p.ld_y;
+  const int64_t peer = dst / p.y_rows_per_peer;
+  return (TY*)p.y_peers[peer] + (dst - peer * p.y_rows_per_peer) * p.ld_y;
+}
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int64_t off) {
   switch (dtype) {

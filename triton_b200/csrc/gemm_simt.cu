@@ -111,7 +111,6 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmParams p) {
   }
 
   // epilogue
-  TY* Y = (TY*)p.y;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = ty * 4 + i;
@@ -122,6 +121,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmParams p) {
       dst = p.scatter_indx[m];
       if (dst < 0) continue;
     }
+    TY* yrow = gemm_out_row<TY>(p, dst);
     const float beta = p.betas ? p.betas[m] : 1.0f;
     const float gamma = p.gammas ? p.gammas[m] : 1.0f;
     float v[4];
@@ -138,14 +138,14 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmParams p) {
       for (int j = 0; j < 2; ++j) {
         const int gn = n0 + tx * 4 + 2 * j;
         if (gn + 1 < p.N)
-          Y[dst * p.ld_y + (gn >> 1)] =
+          yrow[gn >> 1] =
               from_f32<TY>(gemm_swiglu(v[2 * j], v[2 * j + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma);
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int gn = n0 + tx * 4 + j;
-        if (gn < p.N) Y[dst * p.ld_y + gn] = from_f32<TY>(v[j] * gamma);
+        if (gn < p.N) yrow[gn] = from_f32<TY>(v[j] * gamma);
       }
     }
   }

@@ -563,7 +563,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
     constexpr int TILE_N = NH * HALF_N;
     float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + q * TILE_N;    // private to this warp
-    TY* Y = (TY*)p.y;
     const bool swiglu = p.activation == MOE_ACT_SWIGLU;
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
     uint32_t tc = 0;
@@ -603,11 +602,12 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
           tmem_ld_wait();
           // parameters of token c0 + lane
           const int tj = c0 + lane;
-          int64_t dst_l = -1;
+          TY* dst_l = nullptr;                              // output row of this lane's token (none: not stored)
           float beta_l = 1.0f, gamma_l = 1.0f;
           if (tj < rows) {
             const int64_t m = row0 + tj;
-            dst_l = p.scatter_indx ? (int64_t)p.scatter_indx[m] : m;
+            const int64_t d = p.scatter_indx ? (int64_t)p.scatter_indx[m] : m;
+            if (d >= 0) dst_l = gemm_out_row<TY>(p, d);
             if (p.betas) beta_l = p.betas[m];
             if (p.gammas) gamma_l = p.gammas[m];
           }
@@ -615,18 +615,18 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (j < jmax) {                                   // warp-uniform
-              const int64_t dst = __shfl_sync(0xFFFFFFFFu, dst_l, j);
+              TY* yrow = (TY*)__shfl_sync(0xFFFFFFFFu, (unsigned long long)dst_l, j);
               const float beta = __shfl_sync(0xFFFFFFFFu, beta_l, j);
               const float gamma = __shfl_sync(0xFFFFFFFFu, gamma_l, j);
               float a = __uint_as_float(raw[j]) + bias_n * beta;
               if (p.has_out_alpha) a *= p.out_alpha;
               if (swiglu) {
                 const float other = __shfl_xor_sync(0xFFFFFFFFu, a, 1);
-                if (!(lane & 1) && dst >= 0 && n + 1 < p.N)
-                  Y[dst * p.ld_y + (n >> 1)] =
+                if (!(lane & 1) && yrow != nullptr && n + 1 < p.N)
+                  yrow[n >> 1] =
                       from_f32<TY>(gemm_swiglu(a, other, p.act_alpha, p.act_limit, p.act_has_limit) * gamma);
-              } else if (dst >= 0 && n < p.N) {
-                Y[dst * p.ld_y + n] = from_f32<TY>(a * gamma);
+              } else if (yrow != nullptr && n < p.N) {
+                yrow[n] = from_f32<TY>(a * gamma);
               }
             }
           }
@@ -648,6 +648,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
           if (p.gammas) gamma = p.gammas[m];
         }
         const bool store_row = row_live && dst >= 0;
+        TY* yrow = store_row ? gemm_out_row<TY>(p, dst) : nullptr;
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * C::ACC_COLS + h * TILE_N;
         // two register buffers: the tensor-memory load of the next 16 columns is in flight while this one is
         // turned into output
@@ -672,13 +673,13 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
               float acc = 0.f;
 #pragma unroll
               for (int jx = 0; jx < 8; ++jx) acc += o[jx];
-              if (acc == 12345.678f) Y[0] = from_f32<TY>(acc);
+              if (acc == 12345.678f) yrow[0] = from_f32<TY>(acc);
             } else
-            store_out<TY, 8>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 16, ncols >> 1);
+            store_out<TY, 8>(yrow + ((n0 + c0) >> 1), o, y_vec && ncols == 16, ncols >> 1);
           } else {
 #pragma unroll
             for (int jx = 0; jx < 16; ++jx) v[jx] *= gamma;
-            store_out<TY, 16>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 16, ncols);
+            store_out<TY, 16>(yrow + (n0 + c0), v, y_vec && ncols == 16, ncols);
           }
         };
         uint32_t raw0[16], raw1[16];

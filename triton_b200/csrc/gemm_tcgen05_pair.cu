@@ -487,7 +487,6 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
     // ================================= epilogue =========================================================
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
     float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + q * P_TILE_N;    // private to this warp
-    TY* Y = (TY*)p.y;
     const bool swiglu = p.activation == MOE_ACT_SWIGLU;
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
     uint32_t tc = 0;
@@ -517,6 +516,7 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
         if (p.gammas) gamma = p.gammas[m];
       }
       const bool store_row = row_live && dst >= 0;
+      TY* yrow = store_row ? gemm_out_row<TY>(p, dst) : nullptr;
       STAT_ADD(0);
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc >> 1) & 1u, ctl, 501));
       if (!ok) break;
@@ -540,11 +540,11 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
 #pragma unroll
           for (int jx = 0; jx < 8; ++jx)
             o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
-          store_out<TY, 8>(Y + dst * p.ld_y + ((n0 + c0) >> 1), o, y_vec && ncols == 16, ncols >> 1);
+          store_out<TY, 8>(yrow + ((n0 + c0) >> 1), o, y_vec && ncols == 16, ncols >> 1);
         } else {
 #pragma unroll
           for (int jx = 0; jx < 16; ++jx) v[jx] *= gamma;
-          store_out<TY, 16>(Y + dst * p.ld_y + (n0 + c0), v, y_vec && ncols == 16, ncols);
+          store_out<TY, 16>(yrow + (n0 + c0), v, y_vec && ncols == 16, ncols);
         }
       };
       uint32_t raw0[16], raw1[16];

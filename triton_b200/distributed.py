@@ -85,14 +85,50 @@ class Mesh:
 
 
 class SymmetricMemoryPool:
-    """Holds the process group of the EP exchange.  The name is the reference's (its pool carves one
-    symmetric-memory arena); with NCCL all-to-all there is no peer-mapped memory to manage, so this object
-    only carries the mesh and the sizes given to `initialize_matmul`."""
+    """Process group and exchange buffers of the EP layer (the reference's pool carves one symmetric-memory arena,
+    distributed.py:30-120).  `enable_peer_buffers` allocates the two exchange buffers in symmetric memory and
+    learns every rank's address of them, which the pull-dispatch / push-combine kernels need; without it (or when
+    the rendezvous is not available) the exchanges run as NCCL all-to-alls."""
 
     def __init__(self, mesh: Mesh):
         self.mesh = mesh
         self._is_initialized = False
         self.sizes = {}
+        self.peer_ok = False
+        self.peer_error = "enable_peer_buffers was not called"
+
+    def enable_peer_buffers(self, n_tokens_local, d_in, d_out, k, dtype, device) -> bool:
+        """x buffer [T_local, d_in] and y buffer [T_local * k, d_out] in symmetric memory; True when every rank of
+        the mesh mapped every other rank's buffers."""
+        ok = 1
+        try:
+            import torch.distributed._symmetric_memory as symm
+            group = self.mesh.process_group if self.mesh.process_group is not None else dist.group.WORLD
+            self.xbuf = symm.empty((n_tokens_local, d_in), dtype=dtype, device=device)
+            self.ybuf = symm.empty((n_tokens_local * k, d_out), dtype=dtype, device=device)
+            self._hx = symm.rendezvous(self.xbuf, group.group_name)
+            self._hy = symm.rendezvous(self.ybuf, group.group_name)
+            self.x_ptrs = [int(p) for p in self._hx.buffer_ptrs]
+            self.y_ptrs = [int(p) for p in self._hy.buffer_ptrs]
+            assert len(self.x_ptrs) == self.mesh.world_size and all(self.x_ptrs) and all(self.y_ptrs)
+        except Exception as ex:           # no symmetric memory on this system: stay on NCCL
+            ok, self.peer_error = 0, f"{type(ex).__name__}: {ex}"
+        flag = torch.tensor([ok], dtype=torch.int32, device=device)
+        if self.mesh.world_size > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.mesh.process_group)
+        self.peer_ok = bool(int(flag.item()))
+        if self.peer_ok:
+            self.peer_shape = (n_tokens_local, d_in, d_out, k, dtype)
+            self._barrier_word = torch.zeros(1, dtype=torch.int32, device=device)
+        elif ok:
+            self.peer_error = "another rank could not map the buffers"
+        return self.peer_ok
+
+    def barrier(self):
+        """Stream-ordered barrier over the mesh: every rank's earlier work on its current stream (peer stores
+        included) is complete before any rank's later work starts."""
+        if self.mesh.world_size > 1:
+            dist.all_reduce(self._barrier_word, group=self.mesh.process_group)
 
     def initialize_matmul(self, n_tokens_global, d_input, d_model, n_expts_act, n_expts_tot, dtype, device):
         self.sizes = dict(n_tokens_global=n_tokens_global, d_input=d_input, d_model=d_model, n_expts_act=n_expts_act,

@@ -7,7 +7,7 @@ output through torch and makes one call into libmoe_b200 (`moe_grouped_gemm`), w
 kernel for bf16 activations x MXFP4 weights in the B200 tiled layouts and the SIMT kernel otherwise."""
 from dataclasses import dataclass
 from enum import Enum, auto
-from typing import Callable
+from typing import Callable, Sequence
 
 import torch
 
@@ -27,6 +27,23 @@ from .tensor_details.layout import (B200MXScaleLayout, B200MXValueLayout, Blackw
 class FusedActivation:
     specs: FnSpecs = FnSpecs.default()
     fn_args: tuple = tuple()
+
+
+@dataclass
+class FusedComm:
+    """Output rows stored straight into buffers of several devices (matmul.py:60-79 of the reference).
+
+    out_handles: device addresses (ints) of one [rows_per_shard, N_out] buffer per shard, this rank's own included,
+    peer-mapped memory for the others.  The reference takes a JIT closure `map_dst_coord`; the only map built here is
+    the block map the expert-parallel combine needs: output row r (after scatter_indx) is row r % rows_per_shard of
+    shard r // rows_per_shard.  `local` is this rank's buffer as a tensor: it carries dtype and row pitch and is
+    what `matmul` returns."""
+    out_handles: Sequence[int]
+    rows_per_shard: int
+    local: torch.Tensor
+    map_dst_coord: object = "block_rows"
+    reduce_rank: int = 0
+    n_reduce_shards: int = 1
 
 
 @dataclass(frozen=True)
@@ -139,7 +156,12 @@ def matmul(a, b, bias,
     if b_ragged_metadata is not None:
         raise NotImplementedError("ragged-K (weight-gradient) matmul is outside the MoE path")
     if fused_comm is not None:
-        raise NotImplementedError("fused_comm is not implemented")
+        if fused_comm.map_dst_coord != "block_rows" or fused_comm.n_reduce_shards != 1:
+            raise NotImplementedError("fused_comm: only the block-of-rows destination map is implemented")
+        if c is not None:
+            raise ValueError("fused_comm writes into its own buffers: do not pass c")
+        if len(fused_comm.out_handles) > _lib.MOE_MAX_PEERS:
+            raise NotImplementedError(f"fused_comm: at most {_lib.MOE_MAX_PEERS} shards")
     if c_acc_in is not None:
         raise NotImplementedError("c_acc_in is not implemented")
     if precision_config is None:
@@ -233,7 +255,11 @@ def matmul(a, b, bias,
     out_rows = M if scatter_indx is None else scatter_indx.shape[0]
     out_dtype = pc.out_dtype or a.dtype
     out_shape = (out_rows, N // red_n)
-    if c is None:
+    if fused_comm is not None:
+        c = fused_comm.local
+        assert c.ndim == 2 and c.shape[1] == N // red_n and c.stride(-1) == 1 and c.dtype == out_dtype
+        assert c.shape[0] == fused_comm.rows_per_shard
+    elif c is None:
         c = torch.empty(out_shape, dtype=out_dtype, device=dev)
     else:
         if c.ndim == 3 and c.shape[0] == 1:
@@ -282,6 +308,10 @@ def matmul(a, b, bias,
         args.activation, args.act_alpha = _lib.MOE_ACT_SWIGLU, float(alpha)
         args.act_limit, args.act_has_limit = (float(limit), 1) if limit is not None else (0.0, 0)
     args.y, args.y_dtype, args.ld_y = c.data_ptr(), _lib.dtype_code(c.dtype), c.stride(0)
+    if fused_comm is not None:
+        args.n_y_peers, args.y_rows_per_peer = len(fused_comm.out_handles), int(fused_comm.rows_per_shard)
+        for i, h in enumerate(fused_comm.out_handles):
+            args.y_peers[i] = int(h)
     args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05,
                    "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR}[kernel_choice]
     args.tile_m, args.tile_n = resolve_tile_m(), resolve_tile_n()

@@ -5,6 +5,7 @@
             -> k-way reduce
 
 `MoeLayerWeights` holds MXFP4 expert weights already in the B200 tiled layouts."""
+import ctypes
 from dataclasses import dataclass
 
 import torch
@@ -89,13 +90,58 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     return z
 
 
+def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer):
+    """Expert-parallel layer over peer-mapped buffers: the dispatch is one gather kernel that pulls every routed token
+    row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want), and the combine is
+    fc2's epilogue storing every output row into its home rank's buffer; two stream-ordered barriers replace the two
+    all-to-alls."""
+    from . import _lib
+    from .matmul import FusedComm
+    lib = _lib.load()
+    mesh = pool.mesh
+    W, rank = mesh.world_size, mesh.local_rank
+    T_local, d = x_local.shape
+    md = sparse.mask_metadata
+    n = md.row_sorted_indx.shape[0]
+    dev = x_local.device
+    meta_global = make_ragged_tensor_metadata(md.col_sum, n)
+    meta_local = remap_ragged_tensor_metadata(meta_global, expt_assignment.expt_map[rank, :])
+    col = md.col_sorted_indx.reshape(-1)                               # flat (token * k + slot) of every position
+    colc = col.long().clamp_min(0)
+    gammas = sparse.vals.reshape(-1)[colc]
+    # positions whose expert lives here pull their token's row; all others are skipped (and never read by the GEMMs)
+    e_pos = sparse.indx.reshape(-1)[colc].long()
+    mine = (expt_assignment.expt_map[rank, :][e_pos] >= 0) & (col >= 0)
+    src_row = torch.where(mine, torch.div(col, k, rounding_mode="floor"), torch.full_like(col, -2)).to(torch.int32)
+    pool.xbuf.copy_(x_local)
+    pool.barrier()                                                     # every rank's tokens are in its buffer
+    x_sorted = torch.empty((n, d), dtype=x_local.dtype, device=dev)
+    ptrs = (ctypes.c_void_p * W)(*pool.x_ptrs)
+    _lib.check(lib.moe_gather_rows_peers(ptrs, W, T_local, d * x_local.element_size(), _lib.ptr(src_row), n,
+                                         d * x_local.element_size(), _lib.ptr(x_sorted),
+                                         d * x_local.element_size(), _lib.stream()), "moe_gather_rows_peers")
+    pc1 = PrecisionConfig(b_mx_scale=lw_local.w1_scale, b_microblock_size=32)
+    pc2 = PrecisionConfig(b_mx_scale=lw_local.w2_scale, b_microblock_size=32)
+    with _span(gemm_timer):
+        h = matmul(x_sorted, lw_local.w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
+                   fused_activation=_activation(lw_local))
+    with _span(gemm_timer):
+        y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, scatter_indx=col, precision_config=pc2,
+                   gammas=gammas, fused_comm=FusedComm(pool.y_ptrs, T_local * k, pool.ybuf))
+    pool.barrier()                                                     # every rank's outputs have landed
+    z, _ = reduce(y.view(T_local, k, -1), dim=1)
+    return z
+
+
 def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: int, expt_assignment, pool,
-                         gemm_timer=None, fused_exchange=True):
+                         gemm_timer=None, fused_exchange=True, exchange="auto"):
     """Expert-parallel layer: tokens are sharded over ranks (x_local [T_local, d_model]), experts over ranks
     (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered, token
     rows travel to the expert owners and back by one NCCL all-to-all each way.
 
-    With `fused_exchange` the two GEMMs read and write the exchange buffers through index maps (fc1 gathers from
+    `exchange`: "peer" (pull-dispatch / push-combine kernels over the pool's peer-mapped buffers, see
+    `SymmetricMemoryPool.enable_peer_buffers`), "nccl" (all-to-all), "auto" (peer when the pool has the buffers).
+    With `fused_exchange` (NCCL form) the two GEMMs read and write the exchange buffers through index maps (fc1 gathers from
     the receive buffer, fc2 scatters into the send buffer) and the k-way combine reads the returned rows in
     place; without it the layer is the reference's composition convert_dp_to_ep -> matmul -> matmul ->
     convert_ep_to_dp -> reduce (python/triton_kernels/tests/test_distributed.py:223-247)."""
@@ -104,6 +150,11 @@ def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: in
     rank = pool.mesh.local_rank
     T_local = x_local.shape[0]
     sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
+    peer_fit = pool.peer_ok and pool.peer_shape == (T_local, x_local.shape[1], lw_local.w2.shape[-1], k, x_local.dtype)
+    if exchange == "peer" and not peer_fit:
+        raise RuntimeError(f"peer exchange is not available: {pool.peer_error}")
+    if exchange in ("auto", "peer") and peer_fit:
+        return _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer)
     md = sparse.mask_metadata
     n_entries = md.row_sorted_indx.shape[0]
     meta_global = make_ragged_tensor_metadata(md.col_sum, n_entries)
