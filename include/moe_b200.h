@@ -197,6 +197,11 @@ int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
  * this key (moe_bitmatrix_metadata with E = world^2, k = 1) yields the order rows travel in.           */
 int moe_ep_keys(const int32_t* col_sorted, const int16_t* expt_indx, const int32_t* owner, int64_t n,
                 int entries_per_rank, int world, int16_t* keys, void* stream);
+/* Index of the pull dispatch: for every expert-sorted position p, src_row[p] = col_sorted[p] / k (the global token row)
+ * when the position's expert is local (local_expt[e] >= 0, one row of expt_map), else -2; gammas[p] = vals[col_sorted[p]]
+ * (0 for padding).  vals / expt_indx are the flat [T_global * k] routing outputs.                          */
+int moe_ep_pull_index(const int32_t* col_sorted, const int16_t* expt_indx, const float* vals, const int32_t* local_expt,
+                      int64_t n, int k, int32_t* src_row, float* gammas, void* stream);
 int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
                     void* dst, int64_t ld_dst, void* stream);
 /* moe_gather_rows over rows that live on several devices: global row g = row_indx[r] is row g % rows_per_peer of

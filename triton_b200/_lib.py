@@ -73,6 +73,7 @@ PROTOTYPES = {
     "moe_weight_layout_from_b200": (i32, [vp, vp, i32, i32, i32, vp, vp, vp]),
     "moe_grouped_gemm": (i32, [C.POINTER(MoeGemmArgs), vp]),
     "moe_ep_keys": (i32, [vp, vp, vp, i64, i32, i32, vp, vp]),
+    "moe_ep_pull_index": (i32, [vp, vp, vp, vp, i64, i32, vp, vp, vp]),
     "moe_gather_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
     "moe_gather_rows_peers": (i32, [vp, i32, i64, i64, vp, i64, i64, vp, i64, vp]),
     "moe_gather_reduce_rows": (i32, [vp, i64, vp, i64, i32, i64, vp, i64, vp]),

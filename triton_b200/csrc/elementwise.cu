@@ -322,6 +322,41 @@ extern "C" __attribute__((visibility("default"))) int moe_ep_keys(const int32_t*
   return MOE_OK;
 }
 
+// Per expert-sorted position p of the replicated routing metadata: the global token row this rank pulls for it
+// (flat / k when the position's expert is local, -2 = not ours or padding) and the routing weight of that position.
+namespace {
+__global__ void __launch_bounds__(256) ep_pull_index_kernel(const int32_t* __restrict__ col_sorted,
+                                                            const int16_t* __restrict__ expt_indx,
+                                                            const float* __restrict__ vals,
+                                                            const int32_t* __restrict__ local_expt, int64_t n, int k,
+                                                            int32_t* __restrict__ src_row, float* __restrict__ gammas) {
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t flat = col_sorted[p];
+    int32_t row = -2;
+    float g = 0.0f;
+    if (flat >= 0) {
+      g = vals[flat];
+      if (local_expt[expt_indx[flat]] >= 0) row = flat / k;
+    }
+    src_row[p] = row;
+    gammas[p] = g;
+  }
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_ep_pull_index(const int32_t* col_sorted, const int16_t* expt_indx,
+                                                                        const float* vals, const int32_t* local_expt,
+                                                                        int64_t n, int k, int32_t* src_row, float* gammas,
+                                                                        void* stream) {
+  MOE_CHECK_ARG(n >= 0 && k > 0, "moe_ep_pull_index: bad extents");
+  if (n == 0) return MOE_OK;
+  MOE_CHECK_ARG(col_sorted && expt_indx && vals && local_expt && src_row && gammas, "moe_ep_pull_index: NULL pointer");
+  ep_pull_index_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(col_sorted, expt_indx, vals, local_expt, n, k,
+                                                                            src_row, gammas);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // y[t, :] = sum_{j < k} src[row_indx[t * k + j], :]   (row_indx < 0: skipped), fp32 accumulation, bf16 rows.
 // The k-way combine of an expert-parallel layer read straight out of the receive buffer of the combine

@@ -107,12 +107,14 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
     meta_global = make_ragged_tensor_metadata(md.col_sum, n)
     meta_local = remap_ragged_tensor_metadata(meta_global, expt_assignment.expt_map[rank, :])
     col = md.col_sorted_indx.reshape(-1)                               # flat (token * k + slot) of every position
-    colc = col.long().clamp_min(0)
-    gammas = sparse.vals.reshape(-1)[colc]
     # positions whose expert lives here pull their token's row; all others are skipped (and never read by the GEMMs)
-    e_pos = sparse.indx.reshape(-1)[colc].long()
-    mine = (expt_assignment.expt_map[rank, :][e_pos] >= 0) & (col >= 0)
-    src_row = torch.where(mine, torch.div(col, k, rounding_mode="floor"), torch.full_like(col, -2)).to(torch.int32)
+    src_row = torch.empty(n, dtype=torch.int32, device=dev)
+    gammas = torch.empty(n, dtype=torch.float32, device=dev)
+    indx16 = sparse.indx if sparse.indx.dtype == torch.int16 else sparse.indx.to(torch.int16)
+    local_expt = expt_assignment.expt_map[rank, :].to(torch.int32).contiguous()
+    _lib.check(lib.moe_ep_pull_index(_lib.ptr(col), _lib.ptr(indx16.contiguous()), _lib.ptr(sparse.vals.contiguous()),
+                                     _lib.ptr(local_expt), n, k, _lib.ptr(src_row), _lib.ptr(gammas), _lib.stream()),
+               "moe_ep_pull_index")
     pool.xbuf.copy_(x_local)
     pool.barrier()                                                     # every rank's tokens are in its buffer
     x_sorted = torch.empty((n, d), dtype=x_local.dtype, device=dev)
