@@ -30,7 +30,7 @@ enum { MOE_W_DENSE = 0,          /* w[e,k,n] in the activation dtype, arbitrary 
        MOE_W_MX4_CANONICAL = 1,  /* e2m1x2 bytes packed along K (K contiguous) + e8m0 scales, byte strides */
        MOE_W_MX4_B200 = 2        /* tile-contiguous values + scales made by moe_weight_layout_to_b200 */ };
 #define MOE_MAX_PEERS 16
-enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3 };
+enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3, MOE_GEMM_STREAM = 4 };
 
 const char* moe_last_error(void);
 int moe_abi_version(void);

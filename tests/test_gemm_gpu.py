@@ -99,7 +99,7 @@ SMALL = [
 
 @pytest.mark.parametrize("case", SMALL)
 @pytest.mark.parametrize("mode", ["plain", "gather", "scatter_w", "swiglu", "all"])
-@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256", "tcgen05-256x256", "tcgen05-pair"])
+@pytest.mark.parametrize("path", ["simt-canonical", "simt-blackwell", "tcgen05", "tcgen05-256", "tcgen05-256x256", "tcgen05-pair", "stream"])
 def test_grouped_gemm(case, mode, path, device):
     E, K, N, sizes, T = case
     opts = dict(plain=dict(gather=False), gather=dict(gather=True),
@@ -109,7 +109,7 @@ def test_grouped_gemm(case, mode, path, device):
     layout, kernel, block_m, block_n = {
         "simt-canonical": ("canonical", "simt", None, None), "simt-blackwell": ("blackwell", "simt", None, None),
         "tcgen05": ("b200", "tcgen05", 128, 128), "tcgen05-256": ("b200", "tcgen05", 256, 128),
-        "tcgen05-256x256": ("b200", "tcgen05", 256, 256), "tcgen05-pair": ("b200", "tcgen05-pair", 0, 0)}[path]
+        "tcgen05-256x256": ("b200", "tcgen05", 256, 256), "tcgen05-pair": ("b200", "tcgen05-pair", 0, 0), "stream": ("b200", "stream", 0, 0)}[path]
     y = run(p, device, layout, kernel, block_m, block_n)
     check(p, y)
 

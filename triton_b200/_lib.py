@@ -18,7 +18,7 @@ MOE_F32, MOE_F16, MOE_BF16 = 0, 1, 2
 MOE_ROUND_UP, MOE_ROUND_DOWN = 0, 1
 MOE_ACT_NONE, MOE_ACT_SWIGLU = 0, 1
 MOE_W_DENSE, MOE_W_MX4_CANONICAL, MOE_W_MX4_B200 = 0, 1, 2
-MOE_GEMM_AUTO, MOE_GEMM_SIMT, MOE_GEMM_TCGEN05, MOE_GEMM_TCGEN05_PAIR = 0, 1, 2, 3
+MOE_GEMM_AUTO, MOE_GEMM_SIMT, MOE_GEMM_TCGEN05, MOE_GEMM_TCGEN05_PAIR, MOE_GEMM_STREAM = 0, 1, 2, 3, 4
 MOE_MAX_PEERS = 16
 
 _DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: MOE_BF16}

@@ -6,6 +6,8 @@ int moe_gemm_tc_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t s
 bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why);
 int moe_gemm_tc_pair_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st);
 bool moe_gemm_tc_pair_supported(const MoeGemmArgs& a, const char** why);
+int moe_gemm_stream_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st);
+bool moe_gemm_stream_supported(const MoeGemmArgs& a, const char** why);
 
 // upper bound on the number of row blocks (triton_kernels tensor_details/ragged_tensor.py:73-77)
 static int64_t n_blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
@@ -60,12 +62,23 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
 
   const char* why = "";
   bool tc = moe_gemm_tc_supported(*a, &why);
-  if ((a->kernel == MOE_GEMM_TCGEN05 || a->kernel == MOE_GEMM_TCGEN05_PAIR) && !tc) {
+  if ((a->kernel == MOE_GEMM_TCGEN05 || a->kernel == MOE_GEMM_TCGEN05_PAIR || a->kernel == MOE_GEMM_STREAM) && !tc) {
     moe_set_error("moe_grouped_gemm: tcgen05 kernel not applicable: %s", why);
     return MOE_ERR_UNSUPPORTED;
   }
   if (a->kernel == MOE_GEMM_SIMT) tc = false;
   if (tc) {
+    // A few rows per expert (decode): the weight-streaming kernel, bound by HBM rather than by pipeline hand-offs.
+    bool streaming = moe_gemm_stream_supported(*a, &why);
+    if (a->kernel == MOE_GEMM_STREAM && !streaming) {
+      moe_set_error("moe_grouped_gemm: streaming kernel not applicable: %s", why);
+      return MOE_ERR_UNSUPPORTED;
+    }
+    if (a->kernel == MOE_GEMM_AUTO)
+      streaming = streaming && a->tile_m == 0 && a->tile_n == 0 && a->M <= 6 * (int64_t)(a->E > 0 ? a->E : 1);
+    else if (a->kernel != MOE_GEMM_STREAM)
+      streaming = false;
+    if (streaming) return moe_gemm_stream_launch(p, *a, st);
     // Large problems run on pairs of SMs (256 x 256 tiles, cta_group::2); small ones and explicit tile requests on
     // the single-SM kernel.
     bool pair = moe_gemm_tc_pair_supported(*a, &why);

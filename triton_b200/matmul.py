@@ -313,7 +313,7 @@ def matmul(a, b, bias,
         for i, h in enumerate(fused_comm.out_handles):
             args.y_peers[i] = int(h)
     args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05,
-                   "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR}[kernel_choice]
+                   "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR, "stream": _lib.MOE_GEMM_STREAM}[kernel_choice]
     args.tile_m, args.tile_n = resolve_tile_m(), resolve_tile_n()
     args.status = _status_word(dev).data_ptr()
     if gather_indx is not None and args.w_kind == _lib.MOE_W_MX4_B200 and a.dtype == torch.bfloat16 and M >= 2048:

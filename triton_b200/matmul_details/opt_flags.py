@@ -1,6 +1,6 @@
 """User-visible tuning overrides for `matmul` (triton_kernels/matmul_details/opt_flags.py:482-532).
 
-The constraint dictionary is context-local.  Keys understood here: ``kernel`` ("auto", "simt", "tcgen05-pair",
+The constraint dictionary is context-local.  Keys understood here: ``kernel`` ("auto", "simt", "tcgen05-pair", "stream",
 "tcgen05").  The reference's tile-shape keys (block_m, block_n, block_k, num_stages, split_k,
 is_persistent, epilogue_subtile, ...) are accepted and ignored when they cannot matter, and raise
 InapplicableConstraint when they ask for something the CUDA kernels do not implement (split_k > 1)."""
@@ -65,7 +65,7 @@ def resolve_kernel_choice() -> str:
     c = get_opt_flags_constraints()
     for k, v in c.items():
         if k == "kernel":
-            if v not in ("auto", "simt", "tcgen05", "tcgen05-pair"):
+            if v not in ("auto", "simt", "tcgen05", "tcgen05-pair", "stream"):
                 raise InapplicableConstraint(f"unknown kernel {v!r}")
         elif k == "split_k":
             if v not in (None, 1):
