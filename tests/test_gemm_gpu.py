@@ -247,3 +247,19 @@ def test_gpt_oss_20b_layer_full_size_properties(tokens, layer_20b, device):
     oracle.assert_close_oracle(z_sub.cpu(), z[sub].cpu(), maxtol=MAXTOL_MX4, rmstol=None, what="tcgen05 vs simt")
     assert oracle.rel_l2(z_sub.cpu(), z[sub].cpu()) < 1e-2
     assert torch.isfinite(z.float()).all()
+
+
+@pytest.mark.parametrize("tokens", [4, 64])
+def test_graphed_layer_equals_eager_layer(tokens, layer_20b, device):
+    """The layer replayed from a CUDA graph returns exactly what the eager layer returns, for new inputs too."""
+    from triton_b200.moe import GraphedMoeLayer, moe_layer_forward
+    lw, _, _ = layer_20b
+    graphed = GraphedMoeLayer(lw, 4, tokens, 2880, 32, device)
+    for seed in (1, 2):
+        g = torch.Generator(device=device).manual_seed(seed)
+        x = torch.randn(tokens, 2880, device=device, generator=g).bfloat16()
+        logits = torch.randn(tokens, 32, device=device, generator=g)
+        want = moe_layer_forward(x, logits, lw, 4)
+        got = graphed(x, logits).clone()
+        tb.matmul_check_status()
+        assert torch.equal(want, got)

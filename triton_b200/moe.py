@@ -90,6 +90,32 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     return z
 
 
+class GraphedMoeLayer:
+    """The single-GPU layer for a fixed token count, captured once in a CUDA graph and replayed: at decode sizes the
+    dozen launches of a step cost more host time than they run on the GPU.  `__call__` copies the inputs into the
+    graph's static buffers and returns the graph's static output tensor (overwritten by the next call)."""
+
+    def __init__(self, lw: MoeLayerWeights, k: int, n_tokens: int, d_model: int, n_expts: int, device, warmup: int = 3):
+        self.x = torch.zeros((n_tokens, d_model), dtype=torch.bfloat16, device=device)
+        self.logits = torch.zeros((n_tokens, n_expts), dtype=torch.float32, device=device)
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):                  # lazy initialisation (kernel attributes, caches) happens here
+            for _ in range(warmup):
+                moe_layer_forward(self.x, self.logits, lw, k)
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.z = moe_layer_forward(self.x, self.logits, lw, k)
+
+    def __call__(self, x, logits):
+        self.x.copy_(x, non_blocking=True)
+        self.logits.copy_(logits, non_blocking=True)
+        self.graph.replay()
+        return self.z
+
+
 def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer):
     """Expert-parallel layer over peer-mapped buffers: the dispatch is one gather kernel that pulls every routed token
     row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want), and the combine is
