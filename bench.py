@@ -246,6 +246,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="expert-parallel exchange: kernels over peer-mapped buffers, or NCCL all-to-all")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "uniform"],
+                    help="expert placement over ranks: equal counts balanced by measured load, or contiguous blocks")
     ap.add_argument("--micro", default=None, choices=["routing", "mxfp"],
                     help="time the memory-bound kernels on their standalone configuration instead of the layer")
     args = ap.parse_args()
@@ -289,7 +291,15 @@ def main():
     logits = torch.randn(T, N_EXPTS, device=dev, generator=g) + expert_bias
     pool = assignment = None
     if world > 1:
-        assignment = tb.make_expt_assignment(world, N_EXPTS, tb.make_expt_dict_uniform(world, N_EXPTS), dev)
+        if args.placement == "balanced":
+            # one calibration batch: rows per expert over all ranks' tokens, then equal-count placement by load (the
+            # weights are synthetic per rank, so placing an expert only decides which logits column it answers to)
+            load = tb.topk(logits, TOP_K).mask_metadata.col_sum.to(torch.float32)
+            dist.all_reduce(load)
+            expt_dict = tb.make_expt_dict_balanced(world, N_EXPTS, load.cpu().tolist())
+        else:
+            expt_dict = tb.make_expt_dict_uniform(world, N_EXPTS)
+        assignment = tb.make_expt_assignment(world, N_EXPTS, expt_dict, dev)
         pool = tb.SymmetricMemoryPool(tb.Mesh(dist.group.WORLD))
         pool.initialize_matmul(T * world, D_MODEL, D_MODEL, TOP_K, N_EXPTS, torch.bfloat16, dev)
         if args.exchange != "nccl":
@@ -446,6 +456,8 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(T, world),
                        "cuda_graph": graphed is not None,
+                       "expert_placement": None if world == 1 else
+                       (f"{E_local} per rank, balanced by measured load" if args.placement == "balanced" else "contiguous blocks"),
                        "exchange": None if world == 1 else ("peer-mapped buffers" if pool.peer_ok else
                                                             f"NCCL all-to-all ({pool.peer_error})"),
                        "l2": "inputs larger than L2 (weights streamed once per step)",

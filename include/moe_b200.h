@@ -215,6 +215,11 @@ int moe_gather_rows_peers(const void* const* src_peers, int n_peers, int64_t row
  * k-way combine (reduce.py:1143-1165 with dim = 1) read through an index, used after the combine exchange.   */
 int moe_gather_reduce_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t T, int k, int64_t d,
                            void* y, int64_t ld_y, void* stream);
+/* moe_gather_reduce_rows over rows that live on several devices (global row g = row g % rows_per_peer of
+ * src_peers[g / rows_per_peer], pitch ld_src elements): the pull half of the expert-parallel combine fused with the
+ * k-way sum (distributed.py:256-283 followed by reduce.py:1143-1165 in the reference).                          */
+int moe_gather_reduce_rows_peers(const void* const* src_peers, int n_peers, int64_t rows_per_peer, int64_t ld_src,
+                                 const int32_t* row_indx, int64_t T, int k, int64_t d, void* y, int64_t ld_y, void* stream);
 int moe_scatter_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_in, int64_t row_bytes,
                      void* dst, int64_t ld_dst, void* stream);
 

@@ -148,3 +148,18 @@ def test_opt_flags_constraints_are_scoped():
     with triton_b200.scoped_opt_flags_constraints({"split_k": 4}):
         with pytest.raises(triton_b200.InapplicableConstraint):
             opt_flags.resolve_kernel_choice()
+
+
+def test_balanced_expert_placement():
+    """Equal counts per shard, every expert placed once, and a far better balance than contiguous blocks on a skewed load."""
+    import random
+    from triton_b200.distributed import make_expt_dict_balanced, make_expt_dict_uniform
+    rng = random.Random(0)
+    load = [2.718 ** rng.gauss(0, 1) for _ in range(128)]
+    for shards in (2, 4, 8):
+        d = make_expt_dict_balanced(shards, 128, load)
+        assert sorted(e for v in d.values() for e in v) == list(range(128))
+        assert all(len(v) == 128 // shards for v in d.values())
+        spread = lambda dd: max(sum(load[e] for e in v) for v in dd.values()) / (sum(load) / shards)
+        assert spread(d) < 1.02 <= spread(make_expt_dict_uniform(shards, 128)) + 1e-9 or spread(d) < 1.02
+        assert spread(d) <= spread(make_expt_dict_uniform(shards, 128))

@@ -44,6 +44,23 @@ def make_expt_dict_random(n_expt_shard, n_expt_tot):
     return {i: perm[cuts[i]:cuts[i + 1]] for i in range(n_expt_shard)}
 
 
+def make_expt_dict_balanced(n_expt_shard, n_expt_tot, load):
+    """Equal expert counts per shard, chosen so that the measured loads (rows per expert, any sequence of numbers)
+    add up as evenly as possible: heaviest expert first, each to the least loaded shard that still has room.
+    (No counterpart in the reference, whose helpers place experts without looking at the router.)"""
+    per = n_expt_tot // n_expt_shard
+    assert per * n_expt_shard == n_expt_tot, "experts must divide evenly over the shards"
+    load = [float(v) for v in load]
+    assert len(load) == n_expt_tot
+    owned = {i: [] for i in range(n_expt_shard)}
+    total = [0.0] * n_expt_shard
+    for e in sorted(range(n_expt_tot), key=lambda j: (-load[j], j)):
+        shard = min((i for i in range(n_expt_shard) if len(owned[i]) < per), key=lambda i: (total[i], i))
+        owned[shard].append(e)
+        total[shard] += load[e]
+    return {i: sorted(v) for i, v in owned.items()}
+
+
 def make_expt_assignment(n_expt_shard, n_expt_tot, expt_dict, device) -> ExptAssignment:
     words = (n_expt_tot + 31) // 32
     bitmask = torch.zeros((n_expt_shard, words), dtype=torch.int64)
@@ -98,14 +115,15 @@ class SymmetricMemoryPool:
         self.peer_error = "enable_peer_buffers was not called"
 
     def enable_peer_buffers(self, n_tokens_local, d_in, d_out, k, dtype, device) -> bool:
-        """x buffer [T_local, d_in] and y buffer [T_local * k, d_out] in symmetric memory; True when every rank of
+        """x buffer [T_local, d_in] (this rank's tokens) and y buffer [T_global * k, d_out] (expert outputs in
+        expert-sorted order; a rank fills the rows of its own experts) in symmetric memory; True when every rank of
         the mesh mapped every other rank's buffers."""
         ok = 1
         try:
             import torch.distributed._symmetric_memory as symm
             group = self.mesh.process_group if self.mesh.process_group is not None else dist.group.WORLD
             self.xbuf = symm.empty((n_tokens_local, d_in), dtype=dtype, device=device)
-            self.ybuf = symm.empty((n_tokens_local * k, d_out), dtype=dtype, device=device)
+            self.ybuf = symm.empty((n_tokens_local * self.mesh.world_size * k, d_out), dtype=dtype, device=device)
             self._hx = symm.rendezvous(self.xbuf, group.group_name)
             self._hy = symm.rendezvous(self.ybuf, group.group_name)
             self.x_ptrs = [int(p) for p in self._hx.buffer_ptrs]

@@ -118,11 +118,12 @@ class GraphedMoeLayer:
 
 def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer):
     """Expert-parallel layer over peer-mapped buffers: the dispatch is one gather kernel that pulls every routed token
-    row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want), and the combine is
-    fc2's epilogue storing every output row into its home rank's buffer; two stream-ordered barriers replace the two
-    all-to-alls."""
+    row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want); fc2 writes its rows
+    into this rank's symmetric output buffer, and the combine is one kernel in which every token reads its k rows from
+    the owners' buffers and sums them.  Both transfers are row-wise (512-byte warp accesses over NVLink; stores of
+    16 bytes from the GEMM epilogue into peer memory ran at a seventh of that) and two stream-ordered barriers
+    replace the two all-to-alls."""
     from . import _lib
-    from .matmul import FusedComm
     lib = _lib.load()
     mesh = pool.mesh
     W, rank = mesh.world_size, mesh.local_rank
@@ -154,10 +155,20 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
         h = matmul(x_sorted, lw_local.w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
                    fused_activation=_activation(lw_local))
     with _span(gemm_timer):
-        y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, scatter_indx=col, precision_config=pc2,
-                   gammas=gammas, fused_comm=FusedComm(pool.y_ptrs, T_local * k, pool.ybuf))
-    pool.barrier()                                                     # every rank's outputs have landed
-    z, _ = reduce(y.view(T_local, k, -1), dim=1)
+        y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas,
+                   c=pool.ybuf)
+    pool.barrier()                                                     # every rank's expert outputs are written
+    # combine: each (local token, slot) reads its row from the buffer of the rank that owns the slot's expert and
+    # the k rows are summed on the fly
+    from .distributed import expert_owner
+    lo = rank * T_local * k
+    pos = md.row_sorted_indx.reshape(-1)[lo:lo + T_local * k]
+    own = expert_owner(expt_assignment).to(torch.int32)[indx16.reshape(-1)[lo:lo + T_local * k].long()]
+    comb = (own * n + pos).to(torch.int32)
+    z = torch.empty((T_local, y.shape[1]), dtype=y.dtype, device=dev)
+    yptrs = (ctypes.c_void_p * W)(*pool.y_ptrs)
+    _lib.check(lib.moe_gather_reduce_rows_peers(yptrs, W, n, y.stride(0), _lib.ptr(comb), T_local, k, y.shape[1],
+                                                _lib.ptr(z), z.stride(0), _lib.stream()), "moe_gather_reduce_rows_peers")
     return z
 
 
