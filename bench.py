@@ -246,6 +246,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="expert-parallel exchange: kernels over peer-mapped buffers, or NCCL all-to-all")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "tcgen05-pair", "stream"],
+                    help="pin the grouped-GEMM kernel (default: the library's choice)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "uniform"],
                     help="expert placement over ranks: equal counts balanced by measured load, or contiguous blocks")
     ap.add_argument("--micro", default=None, choices=["routing", "mxfp"],
@@ -274,6 +276,8 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    if args.kernel != "auto":
+        tb.update_opt_flags_constraints({"kernel": args.kernel})
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -414,33 +418,33 @@ def main():
     # ---- end to end: host buffers in, host result out, through the public API ---------------------------
     e2e = None
     if not args.no_e2e:
+        from triton_b200.moe import HostStreamingLayer
         xh = x.cpu().pin_memory()
         lh = logits.cpu().pin_memory()
-        zh = torch.empty((T, D_MODEL), dtype=torch.bfloat16).pin_memory()
-        xd, ld = torch.empty_like(x), torch.empty_like(logits)
+        zh = [torch.empty((T, D_MODEL), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        # host buffers in, host buffers out, through the package's streaming front end: every step uploads its inputs
+        # and downloads its result; uploads / downloads of neighbouring steps overlap the compute of this one
+        pipe = HostStreamingLayer(lambda xd, ld: step(xd, ld), T, D_MODEL, N_EXPTS, dev, static_output=graphed is not None)
 
-        def e2e_step():
-            xd.copy_(xh, non_blocking=True)
-            ld.copy_(lh, non_blocking=True)
-            zz = step(xd, ld)
-            zh.copy_(zz, non_blocking=True)
+        def e2e_run(n):
+            for i in range(n):
+                pipe.submit(xh, lh, zh[i & 1])
+            pipe.drain()
 
-        for _ in range(3):
-            e2e_step()
+        e2e_run(3)
         barrier()
-        n_e2e = max(3, args.steps // 2)
+        n_e2e = max(4, args.steps // 2)
         ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         ev2[0].record()
-        for _ in range(n_e2e):
-            e2e_step()
+        e2e_run(n_e2e)
         ev2[1].record()
         barrier()
         t2 = torch.tensor([ev2[0].elapsed_time(ev2[1])], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t2, op=dist.ReduceOp.MAX)
         e2e = {"value": T * world / (float(t2.item()) / n_e2e * 1e-3), "unit": UNIT,
-               "h2d_bytes_per_step": xh.numel() * 2 + lh.numel() * 4, "d2h_bytes_per_step": zh.numel() * 2,
-               "steps": n_e2e}
+               "h2d_bytes_per_step": xh.numel() * 2 + lh.numel() * 4, "d2h_bytes_per_step": zh[0].numel() * 2,
+               "steps": n_e2e, "pipelined": "upload, compute and download of consecutive steps overlap (3 streams)"}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -263,3 +263,25 @@ def test_graphed_layer_equals_eager_layer(tokens, layer_20b, device):
         got = graphed(x, logits).clone()
         tb.matmul_check_status()
         assert torch.equal(want, got)
+
+
+def test_host_streaming_layer(layer_20b, device):
+    """Steps fed from and returned to pinned host memory through the three-stream pipeline equal the eager layer."""
+    from triton_b200.moe import HostStreamingLayer, moe_layer_forward
+    lw, _, _ = layer_20b
+    T = 300
+    pipe = HostStreamingLayer(lambda x, l: moe_layer_forward(x, l, lw, 4), T, 2880, 32, device)
+    xs, ls, zs, want = [], [], [], []
+    for seed in range(5):
+        g = torch.Generator().manual_seed(seed)
+        xs.append(torch.randn(T, 2880, generator=g).bfloat16().pin_memory())
+        ls.append(torch.randn(T, 32, generator=g).pin_memory())
+        zs.append(torch.empty(T, 2880, dtype=torch.bfloat16).pin_memory())
+        want.append(moe_layer_forward(xs[-1].to(device), ls[-1].to(device), lw, 4).cpu())
+    for i in range(5):
+        pipe.submit(xs[i], ls[i], zs[i])
+    pipe.drain()
+    torch.cuda.synchronize()
+    tb.matmul_check_status()
+    for i in range(5):
+        assert torch.equal(zs[i], want[i]), i

@@ -116,6 +116,55 @@ class GraphedMoeLayer:
         return self.z
 
 
+class HostStreamingLayer:
+    """Layer steps fed from pinned host buffers and returning into pinned host buffers, pipelined over three streams:
+    while step i computes, the inputs of step i + 1 are uploading and the result of step i - 1 is downloading (two
+    device input slots).  `forward(x_dev, logits_dev) -> z_dev` is the layer (any of the forward functions above,
+    bound to its weights).  Every `submit` copies that step's inputs in and its result out; `drain` waits for all of
+    them."""
+
+    def __init__(self, forward, n_tokens, d_model, n_expts, device, static_output=False):
+        # static_output: `forward` returns the same tensor every call (a replayed CUDA graph): the next step then
+        # waits until the previous result has left the device
+        self.forward = forward
+        self.static_output = static_output
+        self.ev_out = torch.cuda.Event()
+        self.dev = torch.device(device)
+        self.s_in, self.s_out = torch.cuda.Stream(device=self.dev), torch.cuda.Stream(device=self.dev)
+        self.x = [torch.empty((n_tokens, d_model), dtype=torch.bfloat16, device=self.dev) for _ in range(2)]
+        self.logits = [torch.empty((n_tokens, n_expts), dtype=torch.float32, device=self.dev) for _ in range(2)]
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]
+        self.ev_done = [torch.cuda.Event() for _ in range(2)]
+        self.n = 0
+
+    def submit(self, x_host, logits_host, z_host):
+        b = self.n & 1
+        main = torch.cuda.current_stream(self.dev)
+        with torch.cuda.stream(self.s_in):
+            if self.n >= 2:
+                self.s_in.wait_event(self.ev_done[b])          # the step that last read this slot has finished
+            else:
+                self.s_in.wait_stream(main)
+            self.x[b].copy_(x_host, non_blocking=True)
+            self.logits[b].copy_(logits_host, non_blocking=True)
+            self.ev_in[b].record(self.s_in)
+        main.wait_event(self.ev_in[b])
+        if self.static_output and self.n > 0:
+            main.wait_event(self.ev_out)
+        z = self.forward(self.x[b], self.logits[b])
+        self.ev_done[b].record(main)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_done[b])
+            z_host.copy_(z, non_blocking=True)
+            z.record_stream(self.s_out)
+            self.ev_out.record(self.s_out)
+        self.n += 1
+
+    def drain(self):
+        torch.cuda.current_stream(self.dev).wait_stream(self.s_out)
+        torch.cuda.current_stream(self.dev).wait_stream(self.s_in)
+
+
 def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer):
     """Expert-parallel layer over peer-mapped buffers: the dispatch is one gather kernel that pulls every routed token
     row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want); fc2 writes its rows
