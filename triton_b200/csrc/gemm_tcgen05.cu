@@ -10,14 +10,15 @@
 // One persistent CTA per SM, 18 warps, specialised:
 //   warp 0       tensor-memory allocation, MMA issue (one elected lane)
 //   warp 1       weight producer: one bulk copy per value tile (8 KB) and scale tile (512 B) and k step
-//   warps 2-5    activation loader: 16-byte cp.async of (gathered) token rows into the 128B-swizzled
-//                K-major operand tile, zero fill for missing rows and the K tail; the source offsets of a
-//                thread's 16 rows stay in registers for the whole tile
+//   warps 2-5    activation loader.  256-row tiles of consecutive token rows: one thread, one TMA tile copy
+//                (128 rows x 64 k, 128-byte swizzle) per half stage.  Otherwise 16-byte cp.async of (gathered)
+//                token rows into the 128B-swizzled K-major operand tile, zero fill for missing rows and the
+//                K tail; the source offsets of a thread's rows stay in registers for the whole tile
 //   warps 6-13   dequantiser: packed e2m1 + e8m0 -> bf16, written into the swizzled K-major B tile; a thread
 //                takes the 32 k values of one (row, scale group) at a time: one 16-byte load, one scale byte
 //   warps 14-17  epilogue: tcgen05.ld of the accumulator, bias*beta, out_alpha, SwiGLU, gamma, cast, store
-// Tile (128 or 256 token rows) x 128 weight rows, 64 k per stage, 6 or 4 stages.
-// Rings: raw weights (producer -> dequantiser), A and B operand stages (-> MMA), two accumulator
+// Tile (128 or 256 token rows) x (128 or 256 weight rows), 64 k per stage, 5, 4 or 3 stages (see Cfg).
+// Rings: raw weights (producer -> dequantiser), A and B operand stages (-> MMA), one or two accumulator
 // buffers (MMA -> epilogue).  Every mbarrier wait is bounded: when a wait expires the CTA raises a
 // shared abort flag, writes the caller's status word, drains its copies, frees tensor memory and
 // returns, so a protocol error can not hang the device.

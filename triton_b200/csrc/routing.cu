@@ -185,11 +185,17 @@ __global__ void __launch_bounds__(1024) bm_scan_kernel(int32_t* __restrict__ par
   // remaining blocks: one thread per expert walks the blocks of tokens
   const int e = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
   if (e >= E) return;
+  // sixteen loads in flight per thread: the walk is a chain of L2 round trips otherwise
   int run = 0;
-  for (int64_t b = 0; b < n_blocks; ++b) {
-    int v = partial[b * E + e];
-    partial[b * E + e] = run;
-    run += v;
+  for (int64_t b0 = 0; b0 < n_blocks; b0 += 16) {
+    int v[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) v[u] = b0 + u < n_blocks ? partial[(b0 + u) * E + e] : 0;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      if (b0 + u < n_blocks) partial[(b0 + u) * E + e] = run;
+      run += v[u];
+    }
   }
 }
 
