@@ -55,12 +55,29 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) topk_kernel(
       s_val[warp][j] = to_f32<T>(x[e]);
     }
   } else {
+    // rows of up to 256 experts are read once and kept as packed keys in registers
+    constexpr int kRegKeys = 8;
+    unsigned long long keys[kRegKeys];
+    const bool in_regs = E <= 32 * kRegKeys;
+    if (in_regs) {
+#pragma unroll
+      for (int u = 0; u < kRegKeys; ++u) {
+        const int e = lane + 32 * u;
+        keys[u] = e < E ? (((unsigned long long)float_key(to_f32<T>(x[e])) << 32) | (uint32_t)(~(uint32_t)e)) : 0ull;
+      }
+    }
     unsigned long long prev = ~0ull;
     for (int j = 0; j < k; ++j) {
       unsigned long long best = 0ull;
-      for (int e = lane; e < E; e += 32) {
-        unsigned long long key = ((unsigned long long)float_key(to_f32<T>(x[e])) << 32) | (uint32_t)(~(uint32_t)e);
-        if (key < prev && key > best) best = key;
+      if (in_regs) {
+#pragma unroll
+        for (int u = 0; u < kRegKeys; ++u)
+          if (keys[u] < prev && keys[u] > best) best = keys[u];
+      } else {
+        for (int e = lane; e < E; e += 32) {
+          unsigned long long key = ((unsigned long long)float_key(to_f32<T>(x[e])) << 32) | (uint32_t)(~(uint32_t)e);
+          if (key < prev && key > best) best = key;
+        }
       }
       best = warp_max_u64(best);
       prev = best;
