@@ -113,6 +113,9 @@ class SymmetricMemoryPool:
         self.sizes = {}
         self.peer_ok = False
         self.peer_error = "enable_peer_buffers was not called"
+        # the expert sort reads the gathered expert indices, not the bitmatrix: a caller that only needs the routing
+        # metadata may switch the bitmatrix exchange off (the other ranks' rows of the mask are then undefined)
+        self.gather_bitmatrix = True
 
     def enable_peer_buffers(self, n_tokens_local, d_in, d_out, k, dtype, device) -> bool:
         """x buffer [T_local, d_in] (this rank's tokens) and y buffer [T_global * k, d_out] (expert outputs in
@@ -167,6 +170,8 @@ class SymmetricMemoryPool:
         gather_rows(y_vals)
         if y_indx is not None:
             gather_rows(y_indx)
+        if not self.gather_bitmatrix:
+            return
         words = bm_store.shape[0]
         loc = bm_store[:, rank * T_local:(rank + 1) * T_local].t().contiguous()      # [T_local, words]
         allr = torch.empty((W * T_local, words), dtype=bm_store.dtype, device=bm_store.device)

@@ -237,7 +237,11 @@ def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: in
                               make_exchange_plan_cuda)
     rank = pool.mesh.local_rank
     T_local = x_local.shape[0]
-    sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
+    keep_bm, pool.gather_bitmatrix = pool.gather_bitmatrix, False     # the layer never reads the mask bits themselves
+    try:
+        sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
+    finally:
+        pool.gather_bitmatrix = keep_bm
     peer_fit = pool.peer_ok and pool.peer_shape == (T_local, x_local.shape[1], lw_local.w2.shape[-1], k, x_local.dtype)
     if exchange == "peer" and not peer_fit:
         raise RuntimeError(f"peer exchange is not available: {pool.peer_error}")
