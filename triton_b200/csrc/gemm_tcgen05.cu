@@ -70,7 +70,7 @@ extern "C" __attribute__((visibility("default"))) int moe_tc_stats_read(long lon
 
 namespace {
 
-constexpr int NUM_THREADS = 576;
+constexpr int NUM_THREADS = 608;          // 19 warps (the register file still allows 96 registers per thread)
 constexpr int LOADER_WARPS = 4, DEQUANT_WARPS = 8;
 constexpr int WARP_LOADER0 = 2, WARP_DEQ0 = 6, WARP_EPI0 = 14;
 // Shared-memory map for a CTA tile of (MH x 128 token rows) x (NH x 128 weight rows), 64 k per stage.
@@ -125,6 +125,9 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // 256-row tiles of consecutive token rows are fetched by TMA tile copies (x_map), everything else by cp.async
   const bool use_tma = MH == 2 && p.gather_indx == nullptr;
+  // second epilogue group (see the epilogue role): only where the loader warps are free and the epilogue is heavy
+  const int epi_groups = (use_tma && p.activation == MOE_ACT_SWIGLU) ? 2 : 1;
+  const bool epi_extra = epi_groups == 2 && ((warp > WARP_LOADER0 && warp < WARP_DEQ0) || warp == WARP_EPI0 + 4);
 
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR_RAW_FULL = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -153,7 +156,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(BAR_ACC_FULL(a), 1);
-      mbar_init(BAR_ACC_EMPTY(a), 4);
+      mbar_init(BAR_ACC_EMPTY(a), epi_groups * 4);
     }
     mbar_init(BAR_DRAIN, 1);
     *s_abort = 0;
@@ -305,7 +308,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
       }
     }
     __syncwarp();
-  } else if (warp < WARP_DEQ0) {
+  } else if (warp < WARP_DEQ0 && !epi_extra) {
     // ================================= activation loader ==============================================
     if constexpr (MH == 1) {
       // Small-tile variant: each of the four loader warps takes every fourth pipeline step and moves that whole
@@ -464,7 +467,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     }
     cp_async_wait_all();
     }
-  } else if (warp < WARP_EPI0) {
+  } else if (warp >= WARP_DEQ0 && warp < WARP_EPI0) {
     // ================================= dequantiser ======================================================
     // A unit is one (weight row, 32-k scale group): one 16-byte load, one scale byte, four 16-byte swizzled stores;
     // a stage holds 256 units per weight tile.  The eight warps work in G groups and group (step mod G) converts
@@ -559,11 +562,16 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
       }
     }
     if (dw == 0 && lane == 0) STAT_FLUSH(8);
-  } else {
+  } else if (warp < WARP_EPI0 + 4 || epi_extra) {
     // ================================= epilogue =========================================================
+    // Four warps, one per tensor-memory lane quarter.  With the single-thread TMA loader and a SwiGLU epilogue (the
+    // arithmetic-heavy one), the three warps the loader leaves idle and warp 18 form a second group and each group
+    // drains half of the tile's columns.
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
     constexpr int TILE_N = NH * HALF_N;
-    float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + q * TILE_N;    // private to this warp
+    const int grp = epi_extra ? 1 : 0;
+    const int cols = TILE_N / epi_groups, c_begin = grp * cols, c_end = c_begin + cols;
+    float* s_bias = reinterpret_cast<float*>(smem + C::OFF_BIAS) + (grp * 4 + q) * cols;   // private to this warp
     const bool swiglu = p.activation == MOE_ACT_SWIGLU;
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
     uint32_t tc = 0;
@@ -578,9 +586,8 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
       const uint32_t ab = tc % ACC_BUFS;
       // stage this tile's bias columns (each warp keeps its own copy: no CTA-level barrier in this role)
       __syncwarp();
-#pragma unroll
-      for (int jb = 0; jb < TILE_N / 32; ++jb) {
-        const int gn = n0 + jb * 32 + lane;
+      for (int jb = 0; jb < cols / 32; ++jb) {
+        const int gn = n0 + c_begin + jb * 32 + lane;
         s_bias[jb * 32 + lane] = (p.bias && gn < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + gn) : 0.0f;
       }
       __syncwarp();
@@ -658,7 +665,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
           float v[16];
 #pragma unroll
           for (int jx = 0; jx < 16; ++jx) {
-            float a = __uint_as_float(raw[jx]) + s_bias[c0 + jx] * beta;
+            float a = __uint_as_float(raw[jx]) + s_bias[c0 - c_begin + jx] * beta;
             if (p.has_out_alpha) a *= p.out_alpha;
             v[jx] = a;
           }
@@ -684,14 +691,14 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
           }
         };
         uint32_t raw0[16], raw1[16];
-        tmem_ld16(taddr, raw0);
+        tmem_ld16(taddr + (uint32_t)c_begin, raw0);
 #pragma unroll 1
-        for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
           tmem_ld_wait();
           tmem_ld16(taddr + (uint32_t)(c0 + 16), raw1);
           emit(raw0, c0);
           tmem_ld_wait();
-          if (c0 + 32 < TILE_N) tmem_ld16(taddr + (uint32_t)(c0 + 32), raw0);
+          if (c0 + 32 < c_end) tmem_ld16(taddr + (uint32_t)(c0 + 32), raw0);
           emit(raw1, c0 + 16);
         }
       }
@@ -701,7 +708,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
       if (lane == 0) mbar_arrive(BAR_ACC_EMPTY(ab));
       STAT_ADD(2);
     }
-    if (q == 0 && lane == 0) STAT_FLUSH(12);
+    if (q == 0 && lane == 0 && grp == 0) STAT_FLUSH(12);
   }
 
   // ---- teardown ----------------------------------------------------------------------------------------
