@@ -246,6 +246,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="expert-parallel exchange: kernels over peer-mapped buffers, or NCCL all-to-all")
+    ap.add_argument("--no-graph", action="store_true", help="never replay the step from a CUDA graph")
     ap.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "tcgen05-pair", "stream"],
                     help="pin the grouped-GEMM kernel (default: the library's choice)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "uniform"],
@@ -311,10 +312,22 @@ def main():
 
     # decode sizes on one GPU: the step is replayed from a CUDA graph (a dozen short launches per step cost more host
     # time than GPU time); the roofline pass below times the GEMM launches of the eager step
-    graphed = None
-    if world == 1 and T <= 1024:
+    graphed, graph_note = None, None
+    if world == 1 and T <= 1024 and not args.no_graph:
         from triton_b200.moe import GraphedMoeLayer
         graphed = GraphedMoeLayer(lw, TOP_K, T, D_MODEL, N_EXPTS, dev)
+
+    if world > 1 and pool.peer_ok and args.exchange != "nccl" and not args.no_graph:
+        # the expert-parallel step over peer buffers has no host synchronisation either: replay it from a graph, too
+        # (every rank takes the same branch; if capture is not possible here, all ranks fall back to eager launches)
+        from triton_b200.moe import GraphedMoeLayer
+        try:
+            graphed = GraphedMoeLayer(lw, TOP_K, T, D_MODEL, N_EXPTS, dev, forward=lambda xi, li: moe_layer_forward_ep(
+                xi, li, lw, TOP_K, assignment, pool, exchange=args.exchange))
+        except Exception as ex:
+            graphed = None
+            graph_note = f"eager ({type(ex).__name__}: {str(ex)[:80]})"
+            torch.cuda.synchronize()
 
     def step(xi, li, timer=None):
         if graphed is not None and timer is None:
@@ -476,7 +489,7 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(T, world),
-                       "cuda_graph": graphed is not None,
+                       "cuda_graph": graphed is not None if graph_note is None else graph_note,
                        "expert_placement": None if world == 1 else
                        (f"{E_local} per rank, balanced by measured load" if args.placement == "balanced" else "contiguous blocks"),
                        "exchange": None if world == 1 else ("peer-mapped buffers" if pool.peer_ok else

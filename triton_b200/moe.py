@@ -91,23 +91,28 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
 
 
 class GraphedMoeLayer:
-    """The single-GPU layer for a fixed token count, captured once in a CUDA graph and replayed: at decode sizes the
-    dozen launches of a step cost more host time than they run on the GPU.  `__call__` copies the inputs into the
-    graph's static buffers and returns the graph's static output tensor (overwritten by the next call)."""
+    """A layer forward for a fixed token count, captured once in a CUDA graph and replayed: at decode sizes the dozen
+    launches of a step cost more host time than they run on the GPU, and in the expert-parallel layer the routing
+    phase before the first GEMM is a chain of short launches and collectives.  `forward(x, logits) -> z` defaults to the
+    single-GPU layer on `lw`; pass the expert-parallel forward (peer-buffer exchange only: the NCCL all-to-all form
+    reads split sizes on the host) to capture that instead.  `__call__` copies the inputs into the graph's static
+    buffers and returns the graph's static output tensor (overwritten by the next call)."""
 
-    def __init__(self, lw: MoeLayerWeights, k: int, n_tokens: int, d_model: int, n_expts: int, device, warmup: int = 3):
+    def __init__(self, lw: MoeLayerWeights, k: int, n_tokens: int, d_model: int, n_expts: int, device, warmup: int = 3,
+                 forward=None):
+        self.forward = forward if forward is not None else (lambda x, logits: moe_layer_forward(x, logits, lw, k))
         self.x = torch.zeros((n_tokens, d_model), dtype=torch.bfloat16, device=device)
         self.logits = torch.zeros((n_tokens, n_expts), dtype=torch.float32, device=device)
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):                  # lazy initialisation (kernel attributes, caches) happens here
             for _ in range(warmup):
-                moe_layer_forward(self.x, self.logits, lw, k)
+                self.forward(self.x, self.logits)
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.z = moe_layer_forward(self.x, self.logits, lw, k)
+            self.z = self.forward(self.x, self.logits)
 
     def __call__(self, x, logits):
         self.x.copy_(x, non_blocking=True)
