@@ -317,18 +317,6 @@ def main():
         from triton_b200.moe import GraphedMoeLayer
         graphed = GraphedMoeLayer(lw, TOP_K, T, D_MODEL, N_EXPTS, dev)
 
-    if world > 1 and pool.peer_ok and args.exchange != "nccl" and not args.no_graph:
-        # the expert-parallel step over peer buffers has no host synchronisation either: replay it from a graph, too
-        # (every rank takes the same branch; if capture is not possible here, all ranks fall back to eager launches)
-        from triton_b200.moe import GraphedMoeLayer
-        try:
-            graphed = GraphedMoeLayer(lw, TOP_K, T, D_MODEL, N_EXPTS, dev, forward=lambda xi, li: moe_layer_forward_ep(
-                xi, li, lw, TOP_K, assignment, pool, exchange=args.exchange))
-        except Exception as ex:
-            graphed = None
-            graph_note = f"eager ({type(ex).__name__}: {str(ex)[:80]})"
-            torch.cuda.synchronize()
-
     def step(xi, li, timer=None):
         if graphed is not None and timer is None:
             return graphed(xi, li)

@@ -93,10 +93,11 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
 class GraphedMoeLayer:
     """A layer forward for a fixed token count, captured once in a CUDA graph and replayed: at decode sizes the dozen
     launches of a step cost more host time than they run on the GPU, and in the expert-parallel layer the routing
-    phase before the first GEMM is a chain of short launches and collectives.  `forward(x, logits) -> z` defaults to the
-    single-GPU layer on `lw`; pass the expert-parallel forward (peer-buffer exchange only: the NCCL all-to-all form
-    reads split sizes on the host) to capture that instead.  `__call__` copies the inputs into the graph's static
-    buffers and returns the graph's static output tensor (overwritten by the next call)."""
+    phase before the first GEMM is a chain of short launches.  `forward(x, logits) -> z` defaults to the single-GPU
+    layer on `lw`; any forward without host synchronisation and without collectives can be passed instead (a capture
+    of the expert-parallel step, whose NCCL barriers and all-gathers sit inside the graph, stopped making progress
+    on 2 GPUs and is not used).  `__call__` copies the inputs into the graph's static buffers and returns the graph's
+    static output tensor (overwritten by the next call)."""
 
     def __init__(self, lw: MoeLayerWeights, k: int, n_tokens: int, d_model: int, n_expts: int, device, warmup: int = 3,
                  forward=None):
