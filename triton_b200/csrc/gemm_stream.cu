@@ -243,27 +243,27 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const GemmPar
         const int s = it % S_STAGES;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_FULL(s), (it / S_STAGES) & 1u, ctl, 702));
         if (!ok) break;
-        const uint8_t* stage = smem + C::OFF_RING + s * S_STAGE_BYTES;
-        const uint32_t sc_lo = *reinterpret_cast<const uint32_t*>(stage + 2 * RAWV_BYTES + r_lo * 4);
-        const uint32_t sc_hi = *reinterpret_cast<const uint32_t*>(stage + 2 * RAWV_BYTES + r_hi * 4);
+        const uint32_t stage = sbase + C::OFF_RING + s * S_STAGE_BYTES;
+        const uint32_t sc_lo = lds32(stage + 2 * RAWV_BYTES + r_lo * 4);
+        const uint32_t sc_hi = lds32(stage + 2 * RAWV_BYTES + r_hi * 4);
         // all four 32-k groups of the tile, unconditionally: past K the packed weights and their scales are zero
         // padding and the staged token rows are zeros
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           {
-            const uint32_t wl = *reinterpret_cast<const uint32_t*>(stage + g * 2048 + r_lo * 16 + c4 * 4);
-            const uint32_t wh = *reinterpret_cast<const uint32_t*>(stage + g * 2048 + r_hi * 16 + c4 * 4);
+            const uint32_t wl = lds32(stage + g * 2048 + r_lo * 16 + c4 * 4);
+            const uint32_t wh = lds32(stage + g * 2048 + r_hi * 16 + c4 * 4);
             const float fl = g == 0 ? scale_f32<0>(sc_lo) : g == 1 ? scale_f32<1>(sc_lo) : g == 2 ? scale_f32<2>(sc_lo) : scale_f32<3>(sc_lo);
             const float fh = g == 0 ? scale_f32<0>(sc_hi) : g == 1 ? scale_f32<1>(sc_hi) : g == 2 ? scale_f32<2>(sc_hi) : scale_f32<3>(sc_hi);
             const uint32_t p0 = e2m1_pair_f16<0>(wl), p1 = e2m1_pair_f16<1>(wl), p2 = e2m1_pair_f16<2>(wl),
                            p3 = e2m1_pair_f16<3>(wl);
             const uint32_t q0 = e2m1_pair_f16<0>(wh), q1 = e2m1_pair_f16<1>(wh), q2 = e2m1_pair_f16<2>(wh),
                            q3 = e2m1_pair_f16<3>(wh);
-            const uint8_t* xg = smem + C::OFF_X + ((kt * 4 + g) * 2) * 512 + qrow * 64 + c4 * 16;
+            const uint32_t xg = sbase + C::OFF_X + ((kt * 4 + g) * 2) * 512 + qrow * 64 + c4 * 16;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
               if (b < nblk) {
-                const uint4 xb = *reinterpret_cast<const uint4*>(xg + b * 512);
+                const uint4 xb = lds128(xg + b * 512);
                 float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 mma_f16_16816(d, p0, q0, p1, q1, xb.x, xb.y);
                 mma_f16_16816(d, p2, q2, p3, q3, xb.z, xb.w);

@@ -164,6 +164,28 @@ __device__ __forceinline__ void tma_tile_2d(uint32_t dst, const CUtensorMap* tma
       : "memory");
 }
 
+// ---- shared-memory accesses by 32-bit shared address: the shared-memory base of these kernels is an aligned-up
+// generic pointer, through which the compiler can only emit generic loads and stores (address-space check on every
+// access, tracked like global loads); these go straight to the shared-memory pipe
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // ---- weight dequantisation ---------------------------------------------------------------------------
 // `w` holds 8 e2m1 codes of one row: nibble p of the low half-word is k = 2p, of the high half-word k = 2p+1.
 // The 3 magnitude bits dropped at bf16 bit 6 give value * 2^-126; one bf16x2 multiply by 2^(s-1)

@@ -509,14 +509,13 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
           if (h < nh_live) {
-            const uint4* rv = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE +
-                                                             h * (RAWK * RAWV_BYTES) + half_off) + g * HALF_N;
-            const uint8_t* rsc = smem + C::OFF_RAWS + rs * C::RAWS_STAGE + h * RAWS_BYTES + (kt & 1) * 2 + g;
+            const uint32_t rv = sbase + C::OFF_RAWV + rs * C::RAWV_STAGE + h * (RAWK * RAWV_BYTES) + half_off + g * HALF_N * 16;
+            const uint32_t rsc = sbase + C::OFF_RAWS + rs * C::RAWS_STAGE + h * RAWS_BYTES + (kt & 1) * 2 + g;
 #pragma unroll
             for (int u = 0; u < U; ++u) {
               const int r = r0 + 16 * WPG * u;
-              raw[h][u] = rv[r];
-              sb[h][u] = rsc[r * 4];
+              raw[h][u] = lds128(rv + r * 16);
+              sb[h][u] = lds8(rsc + r * 4);
             }
           }
         }
@@ -527,7 +526,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
             for (int u = 0; u < U; ++u) {
               const int r = r0 + 16 * WPG * u;
               const int x7 = r & 7;
-              uint8_t* row = smem + C::OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES + r * 128;
+              const uint32_t row = sbase + C::OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES + r * 128;
               const uint32_t w[4] = {raw[h][u].x, raw[h][u].y, raw[h][u].z, raw[h][u].w};
               const uint32_t sbu = sb[h][u];
               if (MOE_PROBE_NO_DEQ) {
@@ -536,11 +535,11 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
                 const uint32_t c2 = c * 0x10001u;
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                  *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
+                  sts128(row + (((g * 4 + q) ^ x7) << 4), dequant8(w[q], c2));
               } else {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                  *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sbu);
+                  sts128(row + (((g * 4 + q) ^ x7) << 4), dequant8_wide(w[q], sbu));
               }
             }
           }
@@ -663,11 +662,17 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         auto emit = [&](const uint32_t (&raw)[16], int c0) {
           if (!store_row || n0 + c0 >= p.N || MOE_PROBE_NO_EPI) return;
           float v[16];
+          const uint32_t bias_addr = smem_u32(s_bias) + (uint32_t)(c0 - c_begin) * 4u;
 #pragma unroll
-          for (int jx = 0; jx < 16; ++jx) {
-            float a = __uint_as_float(raw[jx]) + s_bias[c0 - c_begin + jx] * beta;
-            if (p.has_out_alpha) a *= p.out_alpha;
-            v[jx] = a;
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const uint4 b4 = lds128(bias_addr + j4 * 16);
+            const float bv[4] = {__uint_as_float(b4.x), __uint_as_float(b4.y), __uint_as_float(b4.z), __uint_as_float(b4.w)};
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              float a = __uint_as_float(raw[j4 * 4 + jj]) + bv[jj] * beta;
+              if (p.has_out_alpha) a *= p.out_alpha;
+              v[j4 * 4 + jj] = a;
+            }
           }
           const int ncols = min(16, p.N - (n0 + c0));
           if (swiglu) {

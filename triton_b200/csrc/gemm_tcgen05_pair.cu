@@ -454,22 +454,21 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
         STAT_ADD(1);
         if (!ok) break;
         if (b_live) {
-          const uint4* rv = reinterpret_cast<const uint4*>(smem + C::OFF_RAWV + rs * C::RAWV_STAGE +
-                                                           ((kt & 1) ? RAWV_BYTES : 0)) + g * HALF_N;
-          const uint8_t* rsc = smem + C::OFF_RAWS + rs * C::RAWS_STAGE + (kt & 1) * 2 + g;
-          const uint4 raw = rv[r];
-          const uint32_t sbu = rsc[r * 4];
-          uint8_t* row = smem + C::OFF_B + s * C::B_STAGE + r * 128;
+          const uint32_t rv = sbase + C::OFF_RAWV + rs * C::RAWV_STAGE + ((kt & 1) ? RAWV_BYTES : 0) + g * HALF_N * 16;
+          const uint32_t rsc = sbase + C::OFF_RAWS + rs * C::RAWS_STAGE + (kt & 1) * 2 + g;
+          const uint4 raw = lds128(rv + r * 16);
+          const uint32_t sbu = lds8(rsc + r * 4);
+          const uint32_t row = sbase + C::OFF_B + s * C::B_STAGE + r * 128;
           const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
           if (sbu <= 128u) {
             const uint32_t c = sbu ? ((sbu + 126u) << 7) : 0u;
             const uint32_t c2 = c * 0x10001u;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8(w[q], c2);
+            for (int q = 0; q < 4; ++q) sts128(row + (((g * 4 + q) ^ x7) << 4), dequant8(w[q], c2));
           } else {
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-              *reinterpret_cast<uint4*>(row + (((g * 4 + q) ^ x7) << 4)) = dequant8_wide(w[q], sbu);
+              sts128(row + (((g * 4 + q) ^ x7) << 4), dequant8_wide(w[q], sbu));
           }
           fence_proxy_async();
         }
