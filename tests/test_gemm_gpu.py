@@ -169,6 +169,20 @@ def test_against_reference_fixture(golden, device):
         oracle.assert_close_oracle(g["y"], y.cpu(), maxtol=MAXTOL_MX4, rmstol=None, what=layout)
 
 
+def test_dense_plain_product_library_gemm(device):
+    """x @ W + b without routing (the router's logits) goes to the library GEMM; same answer as the SIMT kernel."""
+    torch.manual_seed(1)
+    x = torch.randn(300, 2880, device=device).bfloat16()
+    w = (torch.randn(2880, 128, device=device) * 0.02).bfloat16()
+    b = torch.randn(128, device=device)
+    y = tb.matmul(x, w, b)
+    with tb.scoped_opt_flags_constraints({"kernel": "simt"}):
+        y_simt = tb.matmul(x, w, b)
+    ref = (x.float().cpu() @ w.float().cpu() + b.cpu()).bfloat16()
+    oracle.assert_close_oracle(ref, y.cpu())
+    oracle.assert_close_oracle(ref, y_simt.cpu())
+
+
 def test_dense_weights_simt(device):
     torch.manual_seed(0)
     x = torch.randn(70, 100, device=device).bfloat16()

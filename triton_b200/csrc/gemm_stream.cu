@@ -46,6 +46,14 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// the same with a zero accumulator input (no registers to clear)
+__device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
 // pair i of word w (nibble i of the low half-word is k = 2i, of the high half-word k = 2i + 1) -> fp16x2 of
 // value * 2^-14: the three magnitude bits at fp16 bits 11:9 (exponent bias 15 against e2m1's 1, subnormal 0.5 included)
 template <int I> __device__ __forceinline__ uint32_t e2m1_pair_f16(uint32_t w) {
@@ -264,8 +272,8 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const GemmPar
             for (int b = 0; b < 2; ++b) {
               if (b < nblk) {
                 const uint4 xb = lds128(xg + b * 512);
-                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                mma_f16_16816(d, p0, q0, p1, q1, xb.x, xb.y);
+                float d[4];
+                mma_f16_16816_zero(d, p0, q0, p1, q1, xb.x, xb.y);
                 mma_f16_16816(d, p2, q2, p3, q3, xb.z, xb.w);
                 acc[b][0] = fmaf(fl, d[0], acc[b][0]);
                 acc[b][1] = fmaf(fl, d[1], acc[b][1]);

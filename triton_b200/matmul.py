@@ -269,6 +269,21 @@ def matmul(a, b, bias,
         return c
     if a_ragged_metadata is None:
         assert E == 1, "several weight matrices need a_ragged_metadata"
+    # A plain dense product (the router's logits = x @ Wg + bg, bench/bench_mlp.py:70 of the reference) is a library
+    # GEMM: cuBLAS through torch, fp32 accumulation, with the epilogue terms that apply to it.
+    if (args.w_kind == _lib.MOE_W_DENSE and kernel_choice == "auto" and a_ragged_metadata is None and gather_indx is None
+            and scatter_indx is None and fused_comm is None and act_name == "dflt" and betas is None and gammas is None
+            and a.dtype in (torch.bfloat16, torch.float16) and a.is_cuda):
+        try:
+            y = torch.mm(a, wd[0], out_dtype=torch.float32)      # fp32 out of the library GEMM: one rounding at the end
+        except (TypeError, RuntimeError):
+            y = torch.mm(a, wd[0]).float()
+        if bias is not None:
+            y = y + bias.reshape(1, -1).float()
+        if out_alpha is not None:
+            y = y * float(out_alpha)
+        c.copy_(y)
+        return c
 
     def i32(t):
         if t is None:
