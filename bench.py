@@ -317,6 +317,13 @@ def main():
         from triton_b200.moe import GraphedMoeLayer
         graphed = GraphedMoeLayer(lw, TOP_K, T, D_MODEL, N_EXPTS, dev)
 
+    if world > 1 and pool.peer_ok and args.exchange != "nccl" and not args.no_graph:
+        # over peer buffers the expert-parallel step holds no collective call and no host synchronisation either:
+        # replay it from a graph, too (every rank takes the same branch)
+        from triton_b200.moe import GraphedMoeLayer
+        graphed = GraphedMoeLayer(lw, TOP_K, T, D_MODEL, N_EXPTS, dev, forward=lambda xi, li: moe_layer_forward_ep(
+            xi, li, lw, TOP_K, assignment, pool, exchange=args.exchange))
+
     def step(xi, li, timer=None):
         if graphed is not None and timer is None:
             return graphed(xi, li)

@@ -215,6 +215,15 @@ int moe_gather_rows_peers(const void* const* src_peers, int n_peers, int64_t row
  * k-way combine (reduce.py:1143-1165 with dim = 1) read through an index, used after the combine exchange.   */
 int moe_gather_reduce_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t T, int k, int64_t d,
                            void* y, int64_t ld_y, void* stream);
+/* Barrier among the ranks of an expert-parallel group without a collective call: sig_peers[r] is rank r's signal
+ * buffer of n_peers 32-bit words (peer-mapped, zero before the first barrier), `epoch` a zeroed 32-bit word of this
+ * rank's own device memory that the kernel increments.  Work enqueued before the call on every rank is complete and
+ * visible before work enqueued after it on any rank starts.  The wait is bounded (2 s); on expiry `status` (optional
+ * device word) is set to 901 and the kernel returns.  Replaces the NCCL barriers around the reference's peer-store
+ * exchanges (distributed.py:118-126 `symm_mem_pool` barriers).                                               */
+int moe_peer_barrier(void* const* sig_peers, int n_peers, int rank, uint32_t* epoch, int32_t* status, void* stream);
+/* All-gather of one small slice per rank by plain loads: dst[r * slice_bytes ...] = src_peers[r][0 .. slice_bytes). */
+int moe_allgather_peers(const void* const* src_peers, int n_peers, int64_t slice_bytes, void* dst, void* stream);
 /* moe_gather_reduce_rows over rows that live on several devices (global row g = row g % rows_per_peer of
  * src_peers[g / rows_per_peer], pitch ld_src elements): the pull half of the expert-parallel combine fused with the
  * k-way sum (distributed.py:256-283 followed by reduce.py:1143-1165 in the reference).                          */

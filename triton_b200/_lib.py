@@ -76,6 +76,8 @@ PROTOTYPES = {
     "moe_ep_pull_index": (i32, [vp, vp, vp, vp, i64, i32, vp, vp, vp]),
     "moe_gather_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
     "moe_gather_rows_peers": (i32, [vp, i32, i64, i64, vp, i64, i64, vp, i64, vp]),
+    "moe_peer_barrier": (i32, [vp, i32, i32, vp, vp, vp]),
+    "moe_allgather_peers": (i32, [vp, i32, i64, vp, vp]),
     "moe_gather_reduce_rows_peers": (i32, [vp, i32, i64, i64, vp, i64, i32, i64, vp, i64, vp]),
     "moe_gather_reduce_rows": (i32, [vp, i64, vp, i64, i32, i64, vp, i64, vp]),
     "moe_scatter_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),

@@ -145,6 +145,58 @@ __global__ void __launch_bounds__(128) gather_rows_peers_kernel(PeerBases peers,
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Barrier among the ranks of an expert-parallel group through peer-mapped signal words, and an all-gather of small
+// per-rank slices by plain loads from the peers' buffers: the routing phase of the expert-parallel layer then holds
+// no collective call, only kernels (which also makes the whole step capturable in a CUDA graph).
+// Rank r owns `sig` words [W]; word s is written by rank s.  Every call bumps this rank's epoch counter (device
+// memory, so that a replayed graph keeps counting), writes the epoch into its word on every peer and waits until all
+// of its own words have reached it.  The wait is bounded (2 s): on expiry the kernel records a status and returns.
+struct PeerSignals { uint32_t* sig[MOE_MAX_PEERS]; };
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(PeerSignals peers, int W, int rank, uint32_t* __restrict__ epoch,
+                                                          int32_t* __restrict__ status) {
+  __shared__ uint32_t s_e;
+  if (threadIdx.x == 0) {
+    s_e = *epoch + 1u;
+    *epoch = s_e;
+  }
+  __syncthreads();
+  const uint32_t e = s_e;
+  __threadfence_system();                              // everything this rank wrote before the barrier is visible first
+  if ((int)threadIdx.x < W) {
+    uint32_t* theirs = peers.sig[threadIdx.x] + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
+    const uint32_t* mine = peers.sig[rank] + threadIdx.x;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - e) >= 0) break;
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) {
+        if (status) atomicExch(status, 901);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  __threadfence_system();
+}
+
+// dst[r * slice_words + w] = src[r][w]: every rank's slice (32-bit words) from its own buffer into one local array
+__global__ void __launch_bounds__(256) allgather_peers_kernel(PeerBases src, int W, int64_t slice_words,
+                                                              uint32_t* __restrict__ dst) {
+  const int64_t total = (int64_t)W * slice_words;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / slice_words;
+    dst[i] = reinterpret_cast<const uint32_t*>(src.base[r])[i - r * slice_words];
+  }
+}
+
 // dst[indx[i], :] = src[i, :]   (indx < 0: dropped)
 __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint8_t* __restrict__ src, int64_t ld_src,
                                                            const int32_t* __restrict__ indx, int64_t n_in,
@@ -270,6 +322,37 @@ extern "C" __attribute__((visibility("default"))) int moe_gather_rows_peers(cons
   const int64_t max_blocks = (int64_t)moe_sm_count() * 16;
   gather_rows_peers_kernel<<<(int)(n_rows_out < max_blocks ? n_rows_out : max_blocks), 128, 0, (cudaStream_t)stream>>>(
       pb, rows_per_peer, ld_src, row_indx, n_rows_out, row_bytes, (uint8_t*)dst, ld_dst);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_peer_barrier(void* const* sig_peers, int n_peers, int rank, uint32_t* epoch,
+                                                                       int32_t* status, void* stream) {
+  MOE_CHECK_ARG(sig_peers && epoch, "moe_peer_barrier: NULL pointer");
+  MOE_CHECK_ARG(n_peers >= 1 && n_peers <= MOE_MAX_PEERS && rank >= 0 && rank < n_peers, "moe_peer_barrier: bad rank / world");
+  PeerSignals ps;
+  for (int i = 0; i < MOE_MAX_PEERS; ++i) {
+    ps.sig[i] = i < n_peers ? (uint32_t*)sig_peers[i] : nullptr;
+    MOE_CHECK_ARG(i >= n_peers || ps.sig[i], "moe_peer_barrier: signal buffer %d is NULL", i);
+  }
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ps, n_peers, rank, epoch, status);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int moe_allgather_peers(const void* const* src_peers, int n_peers, int64_t slice_bytes,
+                                                                          void* dst, void* stream) {
+  MOE_CHECK_ARG(slice_bytes >= 0 && slice_bytes % 4 == 0, "moe_allgather_peers: slices must be multiples of 4 bytes");
+  if (slice_bytes == 0) return MOE_OK;
+  MOE_CHECK_ARG(src_peers && dst, "moe_allgather_peers: NULL pointer");
+  MOE_CHECK_ARG(n_peers >= 1 && n_peers <= MOE_MAX_PEERS, "moe_allgather_peers: need 1..%d peers", MOE_MAX_PEERS);
+  PeerBases pb;
+  for (int i = 0; i < MOE_MAX_PEERS; ++i) {
+    pb.base[i] = i < n_peers ? (const uint8_t*)src_peers[i] : nullptr;
+    MOE_CHECK_ARG(i >= n_peers || (pb.base[i] && (uintptr_t)pb.base[i] % 4 == 0), "moe_allgather_peers: buffer %d is NULL or unaligned", i);
+  }
+  allgather_peers_kernel<<<grid_for((int64_t)n_peers * (slice_bytes / 4), 256), 256, 0, (cudaStream_t)stream>>>(
+      pb, n_peers, slice_bytes / 4, (uint32_t*)dst);
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }

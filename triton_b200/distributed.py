@@ -2,13 +2,16 @@
 (triton_kernels/distributed.py:9-95, 176-211, 256-283; distributed_details/mesh.py).
 
 Design.  One process per GPU over `torch.distributed` (NCCL on GPUs).  Routing metadata is replicated:
-every rank holds the global top-k indices and the global expert-major sort, as in the reference.  The
-reference moves rows with peer stores into symmetric memory; here each exchange is ONE variable-size
-NCCL all-to-all over NVLink: rows are packed per destination (CUDA gather kernel), exchanged, and
-unpacked into the position the reference would have stored them at (CUDA scatter kernel).  The split
-sizes are a W x W count matrix computed on the device from the replicated metadata and read by the host
-once per exchange pair.  No TMA multicast and no loads from peer memory are involved.
+every rank holds the global top-k indices and the global expert-major sort, as in the reference.  Two forms of
+the exchanges:
+* peer-mapped buffers (`SymmetricMemoryPool.enable_peer_buffers`): tokens, expert outputs, routing outputs and
+  barrier words live in symmetric memory; the library's own kernels pull rows from the peers' buffers with plain
+  loads and the barriers are kernels over the signal words, so a layer step holds no collective call;
+* NCCL: each exchange is one variable-size all-to-all between a pack and an unpack kernel, with the W x W split
+  sizes computed on the device from the replicated metadata and read by the host once per layer.
+No TMA multicast anywhere.
 """
+import ctypes
 import random
 from dataclasses import dataclass
 
@@ -90,6 +93,9 @@ def make_expt_assignment(n_expt_shard, n_expt_tot, expt_dict, device) -> ExptAss
                           [len(v) for v in expt_dict.values()])
 
 
+MAX_PEERS = 16
+
+
 class Mesh:
 
     def __init__(self, process_group=None):
@@ -127,11 +133,24 @@ class SymmetricMemoryPool:
             group = self.mesh.process_group if self.mesh.process_group is not None else dist.group.WORLD
             self.xbuf = symm.empty((n_tokens_local, d_in), dtype=dtype, device=device)
             self.ybuf = symm.empty((n_tokens_local * self.mesh.world_size * k, d_out), dtype=dtype, device=device)
+            # routing outputs of this rank's tokens (top-k values fp32 + expert ids int16), and the barrier's signal words
+            self.route_vals = symm.empty((n_tokens_local, k), dtype=torch.float32, device=device)
+            self.route_indx = symm.empty((n_tokens_local, k), dtype=torch.int16, device=device)
+            self.sig = symm.empty((MAX_PEERS,), dtype=torch.int32, device=device)
+            self.sig.zero_()
             self._hx = symm.rendezvous(self.xbuf, group.group_name)
             self._hy = symm.rendezvous(self.ybuf, group.group_name)
+            self._hv = symm.rendezvous(self.route_vals, group.group_name)
+            self._hi = symm.rendezvous(self.route_indx, group.group_name)
+            self._hs = symm.rendezvous(self.sig, group.group_name)
             self.x_ptrs = [int(p) for p in self._hx.buffer_ptrs]
             self.y_ptrs = [int(p) for p in self._hy.buffer_ptrs]
+            self.rv_ptrs = [int(p) for p in self._hv.buffer_ptrs]
+            self.ri_ptrs = [int(p) for p in self._hi.buffer_ptrs]
+            self.sig_ptrs = [int(p) for p in self._hs.buffer_ptrs]
             assert len(self.x_ptrs) == self.mesh.world_size and all(self.x_ptrs) and all(self.y_ptrs)
+            assert all(self.rv_ptrs) and all(self.ri_ptrs) and all(self.sig_ptrs)
+            self._epoch = torch.zeros(1, dtype=torch.int32, device=device)
         except Exception as ex:           # no symmetric memory on this system: stay on NCCL
             ok, self.peer_error = 0, f"{type(ex).__name__}: {ex}"
         flag = torch.tensor([ok], dtype=torch.int32, device=device)
@@ -141,6 +160,9 @@ class SymmetricMemoryPool:
         if self.peer_ok:
             self.peer_shape = (n_tokens_local, d_in, d_out, k, dtype)
             self._barrier_word = torch.zeros(1, dtype=torch.int32, device=device)
+            torch.cuda.synchronize(device)
+            if self.mesh.world_size > 1:
+                dist.barrier(group=self.mesh.process_group)    # every rank's signal words are zero before anyone signals
         elif ok:
             self.peer_error = "another rank could not map the buffers"
         return self.peer_ok
@@ -148,7 +170,16 @@ class SymmetricMemoryPool:
     def barrier(self):
         """Stream-ordered barrier over the mesh: every rank's earlier work on its current stream (peer stores
         included) is complete before any rank's later work starts."""
-        if self.mesh.world_size > 1:
+        if self.mesh.world_size <= 1:
+            return
+        if self.peer_ok:
+            from .matmul import _status_word
+            lib = _lib.load()
+            W = self.mesh.world_size
+            ptrs = (ctypes.c_void_p * W)(*self.sig_ptrs)
+            _lib.check(lib.moe_peer_barrier(ptrs, W, self.mesh.local_rank, _lib.ptr(self._epoch),
+                                            _lib.ptr(_status_word(self._epoch.device)), _lib.stream()), "moe_peer_barrier")
+        else:
             dist.all_reduce(self._barrier_word, group=self.mesh.process_group)
 
     def initialize_matmul(self, n_tokens_global, d_input, d_model, n_expts_act, n_expts_tot, dtype, device):
@@ -160,6 +191,22 @@ class SymmetricMemoryPool:
         """In-place all-gather of the routing outputs: rank r's rows are [r * T_local, (r+1) * T_local)."""
         g = self.mesh.process_group
         W = self.mesh.world_size
+        k = y_vals.shape[1]
+        if (self.peer_ok and y_indx is not None and y_vals.dtype == torch.float32 and y_indx.dtype == torch.int16
+                and self.peer_shape[0] == T_local and self.peer_shape[3] == k and y_vals.shape[0] == W * T_local
+                and y_vals.is_contiguous() and y_indx.is_contiguous()):
+            # no collective: publish this rank's rows in its symmetric buffers, barrier, read every rank's rows
+            lib = _lib.load()
+            self.route_vals.copy_(y_vals[rank * T_local:(rank + 1) * T_local])
+            self.route_indx.copy_(y_indx[rank * T_local:(rank + 1) * T_local])
+            self.barrier()
+            pv = (ctypes.c_void_p * W)(*self.rv_ptrs)
+            pi = (ctypes.c_void_p * W)(*self.ri_ptrs)
+            _lib.check(lib.moe_allgather_peers(pv, W, T_local * k * 4, _lib.ptr(y_vals), _lib.stream()), "moe_allgather_peers")
+            _lib.check(lib.moe_allgather_peers(pi, W, T_local * k * 2, _lib.ptr(y_indx), _lib.stream()), "moe_allgather_peers")
+            peer_done = True
+        else:
+            peer_done = False
 
         def gather_rows(buf):
             # byte views: NCCL has no 16-bit integer type
@@ -167,9 +214,10 @@ class SymmetricMemoryPool:
             mine = buf[rank * T_local:(rank + 1) * T_local].view(torch.uint8).clone()
             dist.all_gather_into_tensor(full.reshape(-1), mine.reshape(-1), group=g)
 
-        gather_rows(y_vals)
-        if y_indx is not None:
-            gather_rows(y_indx)
+        if not peer_done:
+            gather_rows(y_vals)
+            if y_indx is not None:
+                gather_rows(y_indx)
         if not self.gather_bitmatrix:
             return
         words = bm_store.shape[0]
