@@ -71,3 +71,43 @@ def test_gather_rows_over_peer_buffers(device):
     want[idx == -1] = 0
     want[idx == -2] = 7.0
     assert torch.equal(out, want)
+
+
+def test_allgather_over_peer_buffers(device):
+    import ctypes
+    from triton_b200 import _lib
+    torch.manual_seed(0)
+    slices = [torch.randint(-1000, 1000, (37, 4), dtype=torch.int16, device=device) for _ in range(3)]
+    out = torch.zeros((3 * 37, 4), dtype=torch.int16, device=device)
+    lib = _lib.load()
+    ptrs = (ctypes.c_void_p * 3)(*[t.data_ptr() for t in slices])
+    _lib.check(lib.moe_allgather_peers(ptrs, 3, 37 * 4 * 2, _lib.ptr(out), _lib.stream()), "moe_allgather_peers")
+    assert torch.equal(out, torch.cat(slices))
+
+
+def test_peer_barrier_counts_epochs_and_its_wait_is_bounded(device):
+    """One rank alone passes its own barrier and counts epochs; a barrier whose second rank never arrives gives up
+    after its time limit, reports status 901 and leaves the device usable."""
+    import ctypes
+    import time
+    from triton_b200 import _lib
+    lib = _lib.load()
+    sig = torch.zeros(16, dtype=torch.int32, device=device)
+    epoch = torch.zeros(1, dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    one = (ctypes.c_void_p * 1)(sig.data_ptr())
+    for _ in range(3):
+        _lib.check(lib.moe_peer_barrier(one, 1, 0, _lib.ptr(epoch), _lib.ptr(status), _lib.stream()), "moe_peer_barrier")
+    torch.cuda.synchronize()
+    assert int(epoch.item()) == 3 and int(sig[0].item()) == 3 and int(status.item()) == 0
+    # two ranks' signal buffers, but only rank 0 ever calls: its wait for rank 1's word runs out
+    sig0, sig1 = torch.zeros(16, dtype=torch.int32, device=device), torch.zeros(16, dtype=torch.int32, device=device)
+    epoch.zero_()
+    two = (ctypes.c_void_p * 2)(sig0.data_ptr(), sig1.data_ptr())
+    t0 = time.time()
+    _lib.check(lib.moe_peer_barrier(two, 2, 0, _lib.ptr(epoch), _lib.ptr(status), _lib.stream()), "moe_peer_barrier")
+    torch.cuda.synchronize()
+    assert 1.5 < time.time() - t0 < 10.0
+    assert int(status.item()) == 901
+    assert int(sig1[0].item()) == 1 and int(sig0[0].item()) == 1          # rank 0's word arrived on both "ranks"
+    assert float((torch.ones(8, device=device) * 2).sum().item()) == 16.0     # the context is still healthy
