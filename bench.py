@@ -389,7 +389,11 @@ def main():
     for _ in range(args.steps):
         z = step(x, logits, gt)
     barrier()
-    gemm_ms = [sum(e0.elapsed_time(e1) for e0, e1 in gt.spans)]
+    # per-step sum of the spans, median over the steps (a span stretches when the host falls behind the GPU)
+    per_call = [e0.elapsed_time(e1) for e0, e1 in gt.spans]
+    calls_per_step = max(1, len(per_call) // args.steps)
+    per_step = sorted(sum(per_call[i:i + calls_per_step]) for i in range(0, len(per_call), calls_per_step))
+    gemm_ms = [per_step[len(per_step) // 2] * args.steps]
     n_gemm = [len(gt.spans)]
     rows_local = T * TOP_K                        # routed rows this rank multiplies (average under uniform ownership)
     flop_per_step = rows_local * (FLOP_PER_ROW_FC1 + FLOP_PER_ROW_FC2)

@@ -109,17 +109,22 @@ __global__ void __launch_bounds__(256) reduce_kernel(const TX* __restrict__ x, i
 }
 
 // dst[i, :] = src[indx[i], :]   (indx < 0: zero row) -- 16 bytes per thread
-__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src, int64_t ld_src,
+// One block walks whole rows (no division per 16-byte element); every thread keeps two loads in flight.
+__global__ void __launch_bounds__(128) gather_rows_kernel(const uint8_t* __restrict__ src, int64_t ld_src,
                                                           const int32_t* __restrict__ indx, int64_t n_out,
                                                           int64_t row_bytes, uint8_t* __restrict__ dst, int64_t ld_dst) {
-  const int64_t vec_per_row = row_bytes >> 4;
-  const int64_t total = n_out * vec_per_row;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+  const int vec_per_row = (int)(row_bytes >> 4);
+  for (int64_t r = blockIdx.x; r < n_out; r += gridDim.x) {
     const int32_t s = indx ? indx[r] : (int32_t)r;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (s >= 0) v = *reinterpret_cast<const uint4*>(src + (int64_t)s * ld_src + c * 16);
-    *reinterpret_cast<uint4*>(dst + r * ld_dst + c * 16) = v;
+    const uint4* in = s >= 0 ? reinterpret_cast<const uint4*>(src + (int64_t)s * ld_src) : nullptr;
+    uint4* out = reinterpret_cast<uint4*>(dst + r * ld_dst);
+    for (int c = threadIdx.x; c < vec_per_row; c += 256) {
+      const int c2 = c + 128;
+      const uint4 v0 = in ? in[c] : make_uint4(0, 0, 0, 0);
+      const uint4 v1 = (in && c2 < vec_per_row) ? in[c2] : make_uint4(0, 0, 0, 0);
+      out[c] = v0;
+      if (c2 < vec_per_row) out[c2] = v1;
+    }
   }
 }
 
@@ -297,7 +302,8 @@ extern "C" __attribute__((visibility("default"))) int moe_gather_rows(const void
   MOE_CHECK_ARG(row_bytes % 16 == 0 && ld_src % 16 == 0 && ld_dst % 16 == 0 && (uintptr_t)src % 16 == 0 &&
                     (uintptr_t)dst % 16 == 0,
                 "moe_gather_rows: rows must be 16-byte aligned multiples of 16 bytes");
-  gather_rows_kernel<<<grid_for(n_rows_out * (row_bytes / 16), 256), 256, 0, (cudaStream_t)stream>>>(
+  const int64_t gr_max = (int64_t)moe_sm_count() * 16;
+  gather_rows_kernel<<<(int)(n_rows_out < gr_max ? n_rows_out : gr_max), 128, 0, (cudaStream_t)stream>>>(
       (const uint8_t*)src, ld_src, row_indx, n_rows_out, row_bytes, (uint8_t*)dst, ld_dst);
   MOE_CHECK_LAUNCH();
   return MOE_OK;
