@@ -111,3 +111,25 @@ def test_peer_barrier_counts_epochs_and_its_wait_is_bounded(device):
     assert int(status.item()) == 901
     assert int(sig1[0].item()) == 1 and int(sig0[0].item()) == 1          # rank 0's word arrived on both "ranks"
     assert float((torch.ones(8, device=device) * 2).sum().item()) == 16.0     # the context is still healthy
+
+
+def test_gather_reduce_over_peer_buffers(device):
+    """k-way combine whose rows live in three buffers (one device standing in for three ranks); -1 entries are skipped."""
+    import ctypes
+    from triton_b200 import _lib
+    torch.manual_seed(0)
+    rows_per_peer, d, T, k = 50, 2880, 40, 4
+    bufs = [torch.randn(rows_per_peer, d, device=device).bfloat16() for _ in range(3)]
+    allrows = torch.cat(bufs)
+    idx = torch.randint(0, 3 * rows_per_peer, (T, k), device=device, dtype=torch.int32)
+    idx[::5, 1] = -1
+    out = torch.empty((T, d), device=device, dtype=torch.bfloat16)
+    lib = _lib.load()
+    ptrs = (ctypes.c_void_p * 3)(*[b.data_ptr() for b in bufs])
+    _lib.check(lib.moe_gather_reduce_rows_peers(ptrs, 3, rows_per_peer, d, _lib.ptr(idx), T, k, d, _lib.ptr(out), d,
+                                                _lib.stream()), "moe_gather_reduce_rows_peers")
+    picked = allrows[idx.long().clamp_min(0)].float() * (idx >= 0).unsqueeze(-1)
+    want = picked[:, 0]
+    for j in range(1, k):
+        want = want + picked[:, j]                    # same order of fp32 additions as the kernel
+    assert torch.equal(out, want.bfloat16())

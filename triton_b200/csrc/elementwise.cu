@@ -480,38 +480,38 @@ __global__ void __launch_bounds__(256) gather_reduce_kernel(const __nv_bfloat16*
 // The same combine over rows that live on several devices: row_indx holds global rows (buffer = index / rows_per_peer).
 // All k loads of a thread are issued before the first is used, so four NVLink reads are in flight per thread.
 namespace {
-__global__ void __launch_bounds__(256) gather_reduce_peers_kernel(PeerBases peers, int64_t rows_per_peer, int64_t ld_src,
+__global__ void __launch_bounds__(128) gather_reduce_peers_kernel(PeerBases peers, int64_t rows_per_peer, int64_t ld_src,
                                                                   const int32_t* __restrict__ row_indx, int64_t T, int k,
                                                                   int64_t d, __nv_bfloat16* __restrict__ y, int64_t ld_y) {
-  const int64_t vec_per_row = d >> 3;
-  const int64_t total = T * vec_per_row;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t t = i / vec_per_row, c = (i - t * vec_per_row) * 8;
-    float acc[8];
+  const int vec_per_row = (int)(d >> 3);
+  for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {           // one block per token: no division per element
+    for (int c = threadIdx.x; c < vec_per_row; c += 128) {
+      float acc[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-    for (int s0 = 0; s0 < k; s0 += 4) {
-      uint4 raw[4];
+      for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+      for (int s0 = 0; s0 < k; s0 += 4) {
+        uint4 raw[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        raw[u] = make_uint4(0, 0, 0, 0);
-        const int32_t r = s0 + u < k ? row_indx[t * k + s0 + u] : -1;
-        if (r >= 0) {
-          const int64_t peer = r / rows_per_peer;
-          raw[u] = *reinterpret_cast<const uint4*>(peers.base[peer] + ((r - peer * rows_per_peer) * ld_src + c) * 2);
+        for (int u = 0; u < 4; ++u) {
+          raw[u] = make_uint4(0, 0, 0, 0);
+          const int32_t r = s0 + u < k ? row_indx[t * k + s0 + u] : -1;
+          if (r >= 0) {
+            const int64_t peer = r / rows_per_peer;
+            raw[u] = reinterpret_cast<const uint4*>(peers.base[peer] + (r - peer * rows_per_peer) * ld_src * 2)[c];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]);
         }
       }
+      __nv_bfloat16 o[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]);
-      }
+      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
+      reinterpret_cast<uint4*>(y + t * ld_y)[c] = *reinterpret_cast<const uint4*>(o);
     }
-    __nv_bfloat16 o[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
-    *reinterpret_cast<uint4*>(y + t * ld_y + c) = *reinterpret_cast<const uint4*>(o);
   }
 }
 }  // namespace
@@ -534,7 +534,8 @@ extern "C" __attribute__((visibility("default"))) int moe_gather_reduce_rows_pee
     MOE_CHECK_ARG(i >= n_peers || (pb.base[i] && (uintptr_t)pb.base[i] % 16 == 0),
                   "moe_gather_reduce_rows_peers: peer buffer %d is NULL or not 16-byte aligned", i);
   }
-  gather_reduce_peers_kernel<<<grid_for(T * (d / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+  const int64_t grp_max = (int64_t)moe_sm_count() * 16;
+  gather_reduce_peers_kernel<<<(int)(T < grp_max ? T : grp_max), 128, 0, (cudaStream_t)stream>>>(
       pb, rows_per_peer, ld_src, row_indx, T, k, d, (__nv_bfloat16*)y, ld_y);
   MOE_CHECK_LAUNCH();
   return MOE_OK;
