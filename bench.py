@@ -33,7 +33,7 @@ UNIT = "tokens/s"
 
 
 def workload_name(tokens_per_rank, n_gpus):
-    return (f"gpt-oss-120b MoE layer: d_model {D_MODEL}, fused gate+up {2 * D_FF}, E={N_EXPTS} top-{TOP_K}, "
+    return (f"gpt-oss-{'120b' if N_EXPTS == 128 else ('20b' if N_EXPTS == 32 else 'like')} MoE layer: d_model {D_MODEL}, fused gate+up {2 * D_FF}, E={N_EXPTS} top-{TOP_K}, "
             f"{tokens_per_rank} tokens/rank, skewed router, bf16 x MXFP4, EP over {n_gpus} GPU(s)")
 
 
@@ -252,6 +252,7 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="expert-parallel exchange: kernels over peer-mapped buffers, or NCCL all-to-all")
     ap.add_argument("--no-graph", action="store_true", help="never replay the step from a CUDA graph")
+    ap.add_argument("--experts", type=int, default=128, help="experts of the layer (32: the gpt-oss-20b shape)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "tcgen05-pair", "stream"],
                     help="pin the grouped-GEMM kernel (default: the library's choice)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "uniform"],
@@ -261,6 +262,8 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    global N_EXPTS
+    N_EXPTS = args.experts
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
