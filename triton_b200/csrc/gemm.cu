@@ -75,7 +75,7 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
       return MOE_ERR_UNSUPPORTED;
     }
     if (a->kernel == MOE_GEMM_AUTO)
-      streaming = streaming && a->tile_m == 0 && a->tile_n == 0 && a->M <= 6 * (int64_t)(a->E > 0 ? a->E : 1);
+      streaming = streaming && a->tile_m == 0 && a->tile_n == 0 && a->M <= 10 * (int64_t)(a->E > 0 ? a->E : 1);
     else if (a->kernel != MOE_GEMM_STREAM)
       streaming = false;
     if (streaming) return moe_gemm_stream_launch(p, *a, st);
