@@ -88,7 +88,7 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
     }
     if (a->kernel != MOE_GEMM_TCGEN05_PAIR) pair = false;
     // Large gathered problems: copy the gathered rows once into the caller's scratch, then stream them by TMA.
-    const bool big = a->tile_m != 128 && (a->tile_m == 256 || a->M / (a->E > 0 ? a->E : 1) >= 192);
+    const bool big = a->tile_m != 128 && (a->tile_m == 256 || a->M / (a->E > 0 ? a->E : 1) >= 12);
     if (a->gather_indx && a->gather_scratch && big && a->gather_scratch_bytes >= (int64_t)a->M * a->K * 2) {
       const int rc = moe_gather_rows(a->x, a->ld_x * 2, a->gather_indx, a->M, (int64_t)a->K * 2, a->gather_scratch,
                                      (int64_t)a->K * 2, stream);
