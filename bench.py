@@ -319,7 +319,8 @@ def main():
             pool.enable_peer_buffers(T, D_MODEL, D_MODEL, TOP_K, torch.bfloat16, dev)
 
     # decode sizes on one GPU: the step is replayed from a CUDA graph (a dozen short launches per step cost more host
-    # time than GPU time); the roofline pass below times the GEMM launches of the eager step
+    # time than GPU time; at prefill sizes a replayed step was no faster than eager launches and its static output
+    # serialises the host-streaming pipeline); the roofline pass below times the GEMM launches of the eager step
     graphed, graph_note = None, None
     if world == 1 and T <= 1024 and not args.no_graph:
         from triton_b200.moe import GraphedMoeLayer
@@ -390,6 +391,9 @@ def main():
     gt = GemmTimer()
     barrier()
     for _ in range(args.steps):
+        # a spin kernel ahead of every step lets the host enqueue the whole step before the GPU reaches it, so that the
+        # spans hold GPU time only (no launch gaps)
+        torch.cuda._sleep(int(2.0e6 if T > 1024 else 4.0e5))
         z = step(x, logits, gt)
     barrier()
     # per-step sum of the spans, median over the steps (a span stretches when the host falls behind the GPU)
