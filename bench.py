@@ -463,7 +463,7 @@ def main():
         # host buffers in, host buffers out, through the package's streaming front end: every step uploads its inputs
         # and downloads its result; uploads / downloads of neighbouring steps overlap the compute of this one
         from triton_b200.moe import HostStreamingLayer
-        pipe = HostStreamingLayer(lambda xd, ld: step(xd, ld), T, D_MODEL, N_EXPTS, dev, static_output=graphed is not None)
+        pipe = HostStreamingLayer(lambda xd, ld: step(xd, ld), T, D_MODEL, N_EXPTS, dev)
 
         def run_pipelined(n):
             for i in range(n):

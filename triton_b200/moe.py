@@ -96,8 +96,8 @@ class GraphedMoeLayer:
     phase before the first GEMM is a chain of short launches.  `forward(x, logits) -> z` defaults to the single-GPU
     layer on `lw`; any forward without host synchronisation and without collectives can be passed instead (a capture
     of the expert-parallel step, whose NCCL barriers and all-gathers sit inside the graph, stopped making progress
-    on 2 GPUs and is not used).  `__call__` copies the inputs into the graph's static buffers and returns the graph's
-    static output tensor (overwritten by the next call)."""
+    on 2 GPUs and is not used).  `__call__` copies the inputs into the graph's static buffers and returns a copy of the
+    graph's static output tensor."""
 
     def __init__(self, lw: MoeLayerWeights, k: int, n_tokens: int, d_model: int, n_expts: int, device, warmup: int = 3,
                  forward=None):
@@ -119,7 +119,8 @@ class GraphedMoeLayer:
         self.x.copy_(x, non_blocking=True)
         self.logits.copy_(logits, non_blocking=True)
         self.graph.replay()
-        return self.z
+        # a copy, so that the caller may still be reading one result (a download, say) while the next step replays
+        return self.z.clone()
 
 
 class HostStreamingLayer:
