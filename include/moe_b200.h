@@ -188,9 +188,11 @@ typedef struct {
 int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
 
 /* ---- expert-parallel row movement ------------------------------------------------------------------
- * Local halves of convert_dp_to_ep / convert_ep_to_dp (distributed.py:176-211, 256-283): the
- * exchange itself is an NCCL all-to-all issued by the host shim; these kernels pack rows into
- * per-destination contiguous, expert-sorted order and unpack them.                                 */
+ * Local halves of convert_dp_to_ep / convert_ep_to_dp (distributed.py:176-211, 256-283).  Two forms of the
+ * exchange use them: kernels that pull rows straight from peer-mapped buffers of the other ranks
+ * (moe_gather_rows_peers, moe_gather_reduce_rows_peers, ordered by moe_peer_barrier), and an NCCL all-to-all
+ * issued by the host shim, for which these kernels pack rows into per-destination contiguous,
+ * expert-sorted order and unpack them.                                                              */
 /* Exchange keys: keys[p] = (home rank of the token at expert-sorted position p) * world + (rank owning its
  * expert), -1 for padding.  col_sorted is the global col_sorted_indx [n], expt_indx the global [T, k] int16
  * expert ids (flat), owner[e] the rank of expert e, entries_per_rank = T_local * k.  Sorting the positions by

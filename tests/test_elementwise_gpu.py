@@ -110,6 +110,12 @@ def test_peer_barrier_counts_epochs_and_its_wait_is_bounded(device):
     assert 1.5 < time.time() - t0 < 10.0
     assert int(status.item()) == 901
     assert int(sig1[0].item()) == 1 and int(sig0[0].item()) == 1          # rank 0's word arrived on both "ranks"
+    # the same code through the layer's status word is reported as a peer-barrier time-out, not as a GEMM pipeline wait
+    from triton_b200.matmul import _status_word, matmul_check_status
+    _status_word(torch.device(device)).fill_(901)
+    with pytest.raises(RuntimeError, match="peer barrier"):
+        matmul_check_status(device)
+    matmul_check_status(device)                                            # the word was cleared
     assert float((torch.ones(8, device=device) * 2).sum().item()) == 16.0     # the context is still healthy
 
 
@@ -123,6 +129,7 @@ def test_gather_reduce_over_peer_buffers(device):
     allrows = torch.cat(bufs)
     idx = torch.randint(0, 3 * rows_per_peer, (T, k), device=device, dtype=torch.int32)
     idx[::5, 1] = -1
+    idx[1::7, 3] = -1                                 # dropped entries whose neighbours live on the last buffer
     out = torch.empty((T, d), device=device, dtype=torch.bfloat16)
     lib = _lib.load()
     ptrs = (ctypes.c_void_p * 3)(*[b.data_ptr() for b in bufs])

@@ -8,7 +8,8 @@
 // even and one for the odd 128-k tiles, and inside a group each warp owns 16 weight rows: registers <- packed words
 // of the stage, shifts and masks turn them into fp16 A fragments (an e2m1 code with its three magnitude bits at fp16
 // bits 11:9 is value * 2^-14 exactly), the token rows sit in shared memory as fp16 B fragments (each row scaled by a
-// power of two so that it fits fp16: exact), and mma.sync m16n8k16 accumulates one 32-k scale group into fp32, which is then multiplied by the group's
+// power of two that puts its largest element in [2^11, 2^12): exact for every element within 2^25 of the row maximum,
+// error at most max * 2^-25 for smaller ones, which go subnormal in fp16), and mma.sync m16n8k16 accumulates one 32-k scale group into fp32, which is then multiplied by the group's
 // e8m0 scale and added to the running sum; the two groups' sums meet in shared memory before the epilogue.
 // No warp waits for another one except through the weight ring, so there is no per-step hand-off chain as in the
 // tcgen05 pipeline; the legacy tensor path (a quarter of the tcgen05 rate) is far more than 16 tokens need.

@@ -24,48 +24,11 @@
 // returns, so a protocol error can not hang the device.
 #include "gemm_tc_common.cuh"
 
-// Compile-time switches that knock out one pipeline role at a time (results become wrong); used only to
-// attribute time while tuning.  All zero in the shipped library.
 #ifndef MOE_STAGES_SMALL
 #define MOE_STAGES_SMALL 5
 #endif
 #ifndef MOE_RAW_STAGES_SMALL
 #define MOE_RAW_STAGES_SMALL 6
-#endif
-#ifndef MOE_PROBE_NO_A
-#define MOE_PROBE_NO_A 0
-#endif
-#ifndef MOE_PROBE_NO_DEQ
-#define MOE_PROBE_NO_DEQ 0
-#endif
-#ifndef MOE_PROBE_NO_MMA
-#define MOE_PROBE_NO_MMA 0
-#endif
-#ifndef MOE_PROBE_EPI_MODE
-#define MOE_PROBE_EPI_MODE 0     // 1: compute but never store, 2: store without the activation math
-#endif
-#ifndef MOE_PROBE_NO_EPI
-#define MOE_PROBE_NO_EPI 0
-#endif
-
-#ifndef MOE_TC_STATS
-#define MOE_TC_STATS 0
-#endif
-#if MOE_TC_STATS
-// instrumented build only: cycles per CTA and role spent waiting on each barrier / working
-__device__ long long g_tc_stats[160][16];
-#define STAT_T0() long long _st0 = clock64()
-#define STAT_ADD(slot) do { long long _n = clock64(); _stat[slot] += _n - _st0; _st0 = _n; } while (0)
-#define STAT_DECL() long long _stat[4] = {0, 0, 0, 0}
-#define STAT_FLUSH(base) do { for (int _i = 0; _i < 4; ++_i) g_tc_stats[blockIdx.x][(base) + _i] = _stat[_i]; } while (0)
-extern "C" __attribute__((visibility("default"))) int moe_tc_stats_read(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, g_tc_stats, sizeof(g_tc_stats));
-}
-#else
-#define STAT_T0()
-#define STAT_ADD(slot)
-#define STAT_DECL()
-#define STAT_FLUSH(base)
 #endif
 
 namespace {
@@ -204,7 +167,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     if (lane == 0) {
       uint32_t it = 0, tc = 0;
       bool ok = true;
-      STAT_DECL();
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
         int halves = 1, rows_cur = HALF_M;
         {
@@ -219,29 +181,22 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         const int n_tok = max(16, (min(rows_cur, HALF_M) + 15) & ~15);
         const uint32_t idesc = make_idesc(MH == 1 ? n_tok : nh_live * HALF_N);
         const uint32_t ab = tc % ACC_BUFS;
-        STAT_T0();
         ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc / ACC_BUFS) & 1u) ^ 1u, ctl, 101);
         if (!ok) break;
-        STAT_ADD(0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 102);
-          STAT_ADD(1);
           ok = ok && mbar_wait(BAR_B_FULL(s), ph, ctl, 103);
-          STAT_ADD(2);
           if (!ok) break;
           fence_proxy_async();          // the A tile was written by cp.async (generic proxy) of other threads
           tc_fence_after();
-#if MOE_TC_STATS == 2
-          STAT_ADD(0);
-#endif
           const uint64_t adesc = make_desc(sbase + C::OFF_A + s * C::A_STAGE_BYTES);
           const uint64_t bdesc = make_desc(sbase + C::OFF_B + s * B_STAGE_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < (MOE_PROBE_NO_MMA ? 0 : 4); ++kk) {
+          for (int kk = 0; kk < 4; ++kk) {
             if constexpr (MH == 1)
               mma_bf16(d_tmem, bdesc + (uint64_t)(kk * 2), adesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
             else
@@ -250,15 +205,10 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
               mma_bf16(d_tmem + NH * HALF_N, adesc + (uint64_t)((SUBTILE_BYTES >> 4) + kk * 2),
                        bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
           }
-#if MOE_TC_STATS == 2
-          STAT_ADD(2);
-#endif
           mma_commit(BAR_AB_EMPTY(s));
-          STAT_ADD(3);
         }
         if (ok) mma_commit(BAR_ACC_FULL(ab));
       }
-      STAT_FLUSH(0);
       // make sure every MMA issued by this thread has retired before tensor memory is freed
       mma_commit(BAR_DRAIN);
       mbar_wait(BAR_DRAIN, 0, ctl, 104);
@@ -269,7 +219,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      STAT_DECL();
       const uint8_t* wv = (const uint8_t*)p.w;
       const uint8_t* ws = p.w_scale;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -284,10 +233,8 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         const int n_raw = RAWK == 2 ? KT_TILES : KT;                          // raw stages of this tile
         for (int rt = 0; rt < n_raw; ++rt, ++it) {
           const int s = it % RAW_STAGES;
-          STAT_T0();
           ok = mbar_wait(BAR_RAW_EMPTY(s), ((it / RAW_STAGES) & 1u) ^ 1u, ctl, 201);
           if (!ok) break;
-          STAT_ADD(0);
           mbar_expect_tx(BAR_RAW_FULL(s), (uint32_t)nh_live * (RAWK * RAWV_BYTES + RAWS_BYTES));
           for (int h = 0; h < nh_live; ++h) {
             bulk_g2s(sbase + C::OFF_RAWV + s * C::RAWV_STAGE + h * (RAWK * RAWV_BYTES),
@@ -296,10 +243,8 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
                      ws + (tile0 + (int64_t)h * KT_TILES + (RAWK == 2 ? rt : (rt >> 1))) * RAWS_BYTES, RAWS_BYTES,
                      BAR_RAW_FULL(s));
           }
-          STAT_ADD(1);
         }
       }
-      STAT_FLUSH(4);
       if (!ok) {
         // aborting: let the copies that were already issued land before the CTA leaves
         const uint32_t lo = it > (uint32_t)RAW_STAGES ? it - RAW_STAGES : 0;
@@ -359,7 +304,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
           const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
           const uint32_t stage = sbase + C::OFF_A + s * C::A_STAGE_BYTES;
           const uint32_t kc16 = (uint32_t)(k >> 3);
-          for (int r = rq; r < rows && !MOE_PROBE_NO_A; r += 4) {
+          for (int r = rq; r < rows; r += 4) {
             const uint32_t so = trow[r];
             const bool live = so != 0xFFFFFFFFu && kbytes;
             const uint8_t* g = live ? Xb + ((uint64_t)(so + kc16) << 4) : Xb;
@@ -453,7 +398,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         const uint32_t kc16 = (uint32_t)(k >> 3);
 #pragma unroll
         for (int i = 0; i < NR; ++i) {
-          if (i < nr_live && !MOE_PROBE_NO_A) {
+          if (i < nr_live) {
             const bool live = src16[i] != 0xFFFFFFFFu && kbytes;
             const uint8_t* g = live ? Xb + ((uint64_t)(src16[i] + kc16) << 4) : Xb;
             cp_async16(stage + dst_off[i], g, live ? kbytes : 0u);
@@ -487,7 +432,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     const int n_raw = RAWK == 2 ? KT_TILES : KT;    // packed-weight stages per tile
     uint32_t it = 0, raw_base = 0;                  // operand-ring step; packed-weight stage of the tile's first step
     bool ok = true;
-    STAT_DECL();
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, raw_base += n_raw) {
       const int nh_live = min(NH, NT128 - (int)(tile % NT) * NH);
       for (int kt = 0; kt < KT; ++kt, ++it) {
@@ -496,12 +440,9 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         const uint32_t ph = (it / STAGES) & 1u;
         const uint32_t itr = raw_base + (RAWK == 2 ? (kt >> 1) : kt);
         const int rs = itr % RAW_STAGES;
-        STAT_T0();
         bool got = mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402);
-        STAT_ADD(0);
         got = got && mbar_wait(BAR_RAW_FULL(rs), (itr / RAW_STAGES) & 1u, ctl, 401);
         ok = __all_sync(0xFFFFFFFFu, got);
-        STAT_ADD(1);
         if (!ok) break;
         const uint32_t half_off = (RAWK == 2 && (kt & 1)) ? RAWV_BYTES : 0;
         uint4 raw[NH][U];
@@ -529,8 +470,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
               const uint32_t row = sbase + C::OFF_B + s * B_STAGE_BYTES + h * SUBTILE_BYTES + r * 128;
               const uint32_t w[4] = {raw[h][u].x, raw[h][u].y, raw[h][u].z, raw[h][u].w};
               const uint32_t sbu = sb[h][u];
-              if (MOE_PROBE_NO_DEQ) {
-              } else if (sbu <= 128u) {
+              if (sbu <= 128u) {
                 const uint32_t c = sbu ? ((sbu + 126u) << 7) : 0u;
                 const uint32_t c2 = c * 0x10001u;
 #pragma unroll
@@ -557,10 +497,8 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
             mbar_arrive(BAR_RAW_EMPTY(rs));
           }
         }
-        STAT_ADD(2);
       }
     }
-    if (dw == 0 && lane == 0) STAT_FLUSH(8);
   } else if (warp < WARP_EPI0 + 4 || epi_extra) {
     // ================================= epilogue =========================================================
     // Four warps, one per tensor-memory lane quarter.  With the single-thread TMA loader and a SwiGLU epilogue (the
@@ -575,9 +513,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
     uint32_t tc = 0;
     bool ok = true;
-    STAT_DECL();
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tc) {
-      STAT_T0();
       int e; int64_t row0; int rows;
       map_tile<MH>(p, s_prefix, tile / NT, e, row0, rows);
       const int halves = rows > HALF_M ? 2 : 1;
@@ -590,7 +526,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         s_bias[jb * 32 + lane] = (p.bias && gn < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + gn) : 0.0f;
       }
       __syncwarp();
-      STAT_ADD(0);
       if constexpr (MH == 1) {
         // Transposed accumulator [weight row = lane][token = column].  Lane l of warp quarter q owns output column
         // n0 + 32 q + l; token parameters (destination row, beta, gamma) sit one token per lane and are broadcast
@@ -600,7 +535,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         const int n_tok = max(16, (min(rows, HALF_M) + 15) & ~15);
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc / ACC_BUFS) & 1u, ctl, 501));
         if (!ok) break;
-        STAT_ADD(1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * C::ACC_COLS;
         for (int c0 = 0; c0 < n_tok; c0 += 32) {
@@ -641,7 +575,6 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
       } else {
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc / ACC_BUFS) & 1u, ctl, 501));
       if (!ok) break;
-      STAT_ADD(1);
       tc_fence_after();
       for (int h = 0; h < halves; ++h) {
         const int r = h * HALF_M + q * 32 + lane;   // accumulator row = token row inside the tile
@@ -660,7 +593,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
         // two register buffers: the tensor-memory load of the next 16 columns is in flight while this one is
         // turned into output
         auto emit = [&](const uint32_t (&raw)[16], int c0) {
-          if (!store_row || n0 + c0 >= p.N || MOE_PROBE_NO_EPI) return;
+          if (!store_row || n0 + c0 >= p.N) return;
           float v[16];
           const uint32_t bias_addr = smem_u32(s_bias) + (uint32_t)(c0 - c_begin) * 4u;
 #pragma unroll
@@ -679,15 +612,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
             float o[8];
 #pragma unroll
             for (int jx = 0; jx < 8; ++jx)
-              o[jx] = MOE_PROBE_EPI_MODE == 2
-                          ? v[2 * jx] + v[2 * jx + 1]
-                          : gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
-            if (MOE_PROBE_EPI_MODE == 1) {
-              float acc = 0.f;
-#pragma unroll
-              for (int jx = 0; jx < 8; ++jx) acc += o[jx];
-              if (acc == 12345.678f) yrow[0] = from_f32<TY>(acc);
-            } else
+              o[jx] = gemm_swiglu(v[2 * jx], v[2 * jx + 1], p.act_alpha, p.act_limit, p.act_has_limit) * gamma;
             store_out<TY, 8>(yrow + ((n0 + c0) >> 1), o, y_vec && ncols == 16, ncols >> 1);
           } else {
 #pragma unroll
@@ -711,9 +636,7 @@ gemm_tc_kernel(const GemmParams p, const int64_t grid_m_static, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR_ACC_EMPTY(ab));
-      STAT_ADD(2);
     }
-    if (q == 0 && lane == 0 && grp == 0) STAT_FLUSH(12);
   }
 
   // ---- teardown ----------------------------------------------------------------------------------------

@@ -23,26 +23,6 @@
 #include "gemm_tc_common.cuh"
 #include <mutex>
 
-#ifndef MOE_TC_STATS
-#define MOE_TC_STATS 0
-#endif
-#if MOE_TC_STATS
-// instrumented build only: cycles per CTA and role spent waiting on each barrier / working
-__device__ long long g_tcp_stats[160][32];
-#define STAT_T0() long long _st0 = clock64()
-#define STAT_ADD(slot) do { long long _n = clock64(); _stat[slot] += _n - _st0; _st0 = _n; } while (0)
-#define STAT_DECL() long long _stat[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define STAT_FLUSH(base, n) do { for (int _i = 0; _i < (n); ++_i) g_tcp_stats[blockIdx.x][(base) + _i] = _stat[_i]; } while (0)
-extern "C" __attribute__((visibility("default"))) int moe_tcp_stats_read(long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, g_tcp_stats, sizeof(g_tcp_stats));
-}
-#else
-#define STAT_T0()
-#define STAT_ADD(slot)
-#define STAT_DECL()
-#define STAT_FLUSH(base, n)
-#endif
-
 namespace {
 
 constexpr int PAIR_THREADS = 576;
@@ -226,24 +206,18 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
       uint32_t it = 0, tc = 0;
       bool ok = true;
       const uint32_t idesc = make_idesc_pair(P_TILE_N);
-      STAT_DECL();
       for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs, ++tc) {
         const uint32_t ab = tc & 1u;
-        STAT_T0();
         ok = mbar_wait_cluster(BAR_ACC_EMPTY(ab), ((tc >> 1) & 1u) ^ 1u, ctl, 101);
         if (!ok) break;
-        STAT_ADD(0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * P_ACC_COLS;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
           ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 102);
-          STAT_ADD(1);
           ok = ok && mbar_wait(BAR_B_FULL(s), ph, ctl, 103);
-          STAT_ADD(2);
           ok = ok && mbar_wait_cluster(BAR_PEER_FULL(s), ph, ctl, 105);
-          STAT_ADD(3);
           if (!ok) break;
           fence_proxy_async();          // the A stage was written by cp.async (generic proxy) of other threads
           tc_fence_after();
@@ -252,13 +226,10 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             mma_bf16_pair(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (kt | kk) ? 1u : 0u);
-          STAT_ADD(4);
           mma_commit_pair(BAR_AB_EMPTY(s));
-          STAT_ADD(5);
         }
         if (ok) mma_commit_pair(BAR_ACC_FULL(ab));
       }
-      STAT_FLUSH(0, 8);
       // every MMA issued by this thread has retired before tensor memory is freed
       mma_commit_pair_local(BAR_DRAIN);
       mbar_wait(BAR_DRAIN, 0, ctl, 104);
@@ -266,23 +237,17 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
       // ================================= relay (odd CTA) ================================================
       uint32_t it = 0;
       bool ok = true;
-      STAT_DECL();
       for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
-          STAT_T0();
           ok = mbar_wait(BAR_A_FULL(s), ph, ctl, 112);
-          STAT_ADD(0);
           ok = ok && mbar_wait(BAR_B_FULL(s), ph, ctl, 113);
-          STAT_ADD(1);
           if (!ok) break;
           fence_proxy_async();
           mbar_arrive_cluster(BAR_PEER_FULL(s), 0);
-          STAT_ADD(2);
         }
       }
-      STAT_FLUSH(0, 8);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -326,7 +291,6 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
       if (warp == P_WARP_LOADER0 && lane == 0) {
         uint32_t it = 0;
         bool ok = true;
-        STAT_DECL();
         for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
           int e; int64_t row0; int rows;
           map_tile<2>(p, s_prefix, tile / NT, e, row0, rows);
@@ -334,20 +298,16 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
           const int r_first = (int)(row0 + (int64_t)rank * HALF_M);
           for (int kt = 0; kt < KT; ++kt, ++it) {
             const int s = it % P_STAGES;
-            STAT_T0();
             ok = mbar_wait(BAR_AB_EMPTY(s), ((it / P_STAGES) & 1u) ^ 1u, ctl, 301);
             if (!ok) break;
-            STAT_ADD(0);
             if (any) {
               mbar_expect_tx(BAR_A_FULL(s), (uint32_t)C::A_STAGE);
               tma_tile_2d(sbase + C::OFF_A + s * C::A_STAGE, &x_map, kt * BLOCK_K, r_first, BAR_A_FULL(s));
             } else {
               mbar_arrive(BAR_A_FULL(s));
             }
-            STAT_ADD(1);
           }
         }
-        STAT_FLUSH(24, 4);
         if (!ok) {
           // aborting: let the copies that were already issued land before the CTA leaves
           const uint32_t lo = it > (uint32_t)P_STAGES ? it - P_STAGES : 0;
@@ -393,17 +353,14 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
     bool any = false, nxt_any = false;
     uint32_t it = 0;
     bool ok = true;
-    STAT_DECL();
     if (pair < n_tiles) load_rows(pair, src16, any);
     for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
       const int64_t t2 = tile + n_pairs;
       if (t2 < n_tiles) load_rows(t2, nxt16, nxt_any);
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % P_STAGES;
-        STAT_T0();
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_AB_EMPTY(s), ((it / P_STAGES) & 1u) ^ 1u, ctl, 301));
         if (!ok) break;
-        STAT_ADD(0);
         const int k = kt * BLOCK_K + c8 * 8;
         const int kleft = p.K - k;
         const uint32_t kbytes = kleft >= 8 ? 16u : (kleft > 0 ? (uint32_t)kleft * 2u : 0u);
@@ -418,14 +375,12 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
           }
         }
         cp_async_arrive_noinc(BAR_A_FULL(s));
-        STAT_ADD(1);
       }
 #pragma unroll
       for (int i = 0; i < NR; ++i) src16[i] = nxt16[i];
       any = nxt_any;
     }
     cp_async_wait_all();
-    if (t == 0) STAT_FLUSH(24, 4);
     }
   } else if (warp < P_WARP_EPI0) {
     // ================================= dequantiser ======================================================
@@ -438,7 +393,6 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
     const int x7 = r & 7;
     uint32_t it = 0, raw_base = 0;
     bool ok = true;
-    STAT_DECL();
     for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
       const bool b_live = (int)(tile % NT) * 2 + (int)rank < NT128;
       for (int kt = 0; kt < KT; ++kt, ++it) {
@@ -446,12 +400,9 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
         const uint32_t ph = (it / P_STAGES) & 1u;
         const uint32_t itr = raw_base + (uint32_t)(kt >> 1);
         const int rs = itr % P_RAW_STAGES;
-        STAT_T0();
         bool got = mbar_wait(BAR_AB_EMPTY(s), ph ^ 1u, ctl, 402);
-        STAT_ADD(0);
         if (b_live) got = got && mbar_wait(BAR_RAW_FULL(rs), (itr / P_RAW_STAGES) & 1u, ctl, 401);
         ok = __all_sync(0xFFFFFFFFu, got);
-        STAT_ADD(1);
         if (!ok) break;
         if (b_live) {
           const uint32_t rv = sbase + C::OFF_RAWV + rs * C::RAWV_STAGE + ((kt & 1) ? RAWV_BYTES : 0) + g * HALF_N * 16;
@@ -477,11 +428,9 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
           mbar_arrive(BAR_B_FULL(s));
           if (b_live && ((kt & 1) || kt == KT - 1)) mbar_arrive(BAR_RAW_EMPTY(rs));
         }
-        STAT_ADD(2);
       }
       if (b_live) raw_base += (uint32_t)KT_TILES;
     }
-    if (dw == 0 && lane == 0) STAT_FLUSH(12, 4);
   } else {
     // ================================= epilogue =========================================================
     const int q = warp & 3;                         // tensor-memory lane quarter of this warp
@@ -490,9 +439,7 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
     const bool y_vec = ((uintptr_t)p.y % 16 == 0) && (p.ld_y % 8 == 0);
     uint32_t tc = 0;
     bool ok = true;
-    STAT_DECL();
     for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs, ++tc) {
-      STAT_T0();
       int e; int64_t row0; int rows;
       map_tile<2>(p, s_prefix, tile / NT, e, row0, rows);
       const int n0 = (int)(tile % NT) * P_TILE_N;
@@ -516,10 +463,8 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
       }
       const bool store_row = row_live && dst >= 0;
       TY* yrow = store_row ? gemm_out_row<TY>(p, dst) : nullptr;
-      STAT_ADD(0);
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc >> 1) & 1u, ctl, 501));
       if (!ok) break;
-      STAT_ADD(1);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + ab * P_ACC_COLS;
       // two register buffers: the tensor-memory load of the next 16 columns is in flight while this one is
@@ -560,9 +505,7 @@ gemm_tc_pair_kernel(const GemmParams p, const int64_t grid_m_static, const __gri
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(BAR_ACC_EMPTY(ab), 0);
-      STAT_ADD(2);
     }
-    if (q == 0 && lane == 0) STAT_FLUSH(16, 4);
   }
 
   // ---- teardown ----------------------------------------------------------------------------------------

@@ -105,14 +105,34 @@ def _status_word(device):
     return _status_words[key]
 
 
+_STATUS_TEXT = {
+    101: "tcgen05 kernel: the MMA thread waited for a free accumulator", 102: "tcgen05 kernel: the MMA thread waited for activations",
+    103: "tcgen05 kernel: the MMA thread waited for dequantised weights", 104: "tcgen05 kernel: the final MMA drain",
+    201: "tcgen05 kernel: the weight producer waited for a free stage", 301: "tcgen05 kernel: the activation loader waited for a free stage",
+    401: "tcgen05 kernel: the dequantiser waited for packed weights", 402: "tcgen05 kernel: the dequantiser waited for a free stage",
+    501: "tcgen05 kernel: the epilogue waited for an accumulator",
+    601: "block-scaled kernel: the producer waited for a free stage", 602: "block-scaled kernel: the MMA thread waited for a stage",
+    603: "block-scaled kernel: the MMA thread waited for a free accumulator", 604: "block-scaled kernel: the epilogue waited for an accumulator",
+    605: "block-scaled kernel: the final MMA drain",
+    901: "expert-parallel peer barrier: a rank did not arrive within the limit; the step after it read stale peer buffers",
+}
+
+
+def status_message(code: int) -> str:
+    """Text for a device status code (the word every kernel with bounded waits writes when a wait expires)."""
+    return _STATUS_TEXT.get(code, "a bounded wait expired inside a kernel")
+
+
 def matmul_check_status(device=None):
-    """Synchronise and raise if a bounded wait inside the tensor-core kernel expired since the last check."""
+    """Synchronise and raise if a bounded wait expired since the last check: a pipeline wait inside a tensor-core
+    kernel (codes 1xx-6xx) or an expert-parallel peer barrier (901).  Expert-parallel callers should poll this once
+    per step or batch: after a barrier time-out the step carries on with stale peer buffers and its result is wrong."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     w = _status_word(dev)
     code = int(w.item())
     if code != 0:
         w.zero_()
-        raise RuntimeError(f"moe_grouped_gemm: a pipeline wait timed out inside the tcgen05 kernel (code {code})")
+        raise RuntimeError(f"device status {code}: {status_message(code)}")
 
 
 def _canonical_scale(b_scale: Tensor):

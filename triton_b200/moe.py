@@ -220,7 +220,7 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
     lo = rank * T_local * k
     pos = md.row_sorted_indx.reshape(-1)[lo:lo + T_local * k]
     own = expert_owner(expt_assignment).to(torch.int32)[indx16.reshape(-1)[lo:lo + T_local * k].long()]
-    comb = (own * n + pos).to(torch.int32)
+    comb = torch.where(pos < 0, pos, own * n + pos).to(torch.int32)     # dropped entries (-1) stay dropped
     z = torch.empty((T_local, y.shape[1]), dtype=y.dtype, device=dev)
     yptrs = (ctypes.c_void_p * W)(*pool.y_ptrs)
     _lib.check(lib.moe_gather_reduce_rows_peers(yptrs, W, n, y.stride(0), _lib.ptr(comb), T_local, k, y.shape[1],
@@ -231,10 +231,11 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
 def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: int, expt_assignment, pool,
                          gemm_timer=None, fused_exchange=True, exchange="auto"):
     """Expert-parallel layer: tokens are sharded over ranks (x_local [T_local, d_model]), experts over ranks
-    (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered, token
-    rows travel to the expert owners and back by one NCCL all-to-all each way.
+    (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered; token rows
+    travel to the expert owners and back either through kernels that read the other ranks' peer-mapped buffers
+    (the default when the pool has them) or by one NCCL all-to-all each way.
 
-    `exchange`: "peer" (pull-dispatch / push-combine kernels over the pool's peer-mapped buffers, see
+    `exchange`: "peer" (pull-dispatch / pull-combine kernels over the pool's peer-mapped buffers, see
     `SymmetricMemoryPool.enable_peer_buffers`), "nccl" (all-to-all), "auto" (peer when the pool has the buffers).
     With `fused_exchange` (NCCL form) the two GEMMs read and write the exchange buffers through index maps (fc1 gathers from
     the receive buffer, fc2 scatters into the send buffer) and the k-way combine reads the returned rows in

@@ -44,7 +44,6 @@ class BlackwellMXValueLayoutTransformation(LayoutTransformation):
 
     def swizzle_data(self, data):
         ss = self.storage_shape
-        ret = torch.zeros(ss, device=data.device, dtype=data.dtype).as_strided(ss, _strides_major_dim_m2(ss))
         ret = torch.empty_strided(ss, _strides_major_dim_m2(ss), device=data.device, dtype=data.dtype).zero_()
         repack(data, -1, -2, self.is_fp4, out=ret[..., : self.shape[-2] // 2, :])
         return self._validate_storage_shape(ret)
