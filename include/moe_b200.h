@@ -21,16 +21,18 @@
 extern "C" {
 #endif
 
-enum { MOE_F32 = 0, MOE_F16 = 1, MOE_BF16 = 2 };
+enum { MOE_F32 = 0, MOE_F16 = 1, MOE_BF16 = 2, MOE_F8E4M3 = 3 /* activations of the block-scaled GEMM only */ };
 enum { MOE_OK = 0, MOE_ERR_ARG = 1, MOE_ERR_CUDA = 2, MOE_ERR_UNSUPPORTED = 3, MOE_ERR_DEVICE_STATUS = 4 };
 enum { MOE_ROUND_UP = 0, MOE_ROUND_DOWN = 1 };
 enum { MOE_ACT_NONE = 0, MOE_ACT_SWIGLU = 1 };
 /* weight kinds understood by moe_grouped_gemm */
 enum { MOE_W_DENSE = 0,          /* w[e,k,n] in the activation dtype, arbitrary element strides */
        MOE_W_MX4_CANONICAL = 1,  /* e2m1x2 bytes packed along K (K contiguous) + e8m0 scales, byte strides */
-       MOE_W_MX4_B200 = 2        /* tile-contiguous values + scales made by moe_weight_layout_to_b200 */ };
+       MOE_W_MX4_B200 = 2,       /* tile-contiguous values + scales made by moe_weight_layout_to_b200 */
+       MOE_W_MX4_B200MX = 3      /* tiles for the block-scaled MMA made by moe_weight_layout_to_b200mx */ };
 #define MOE_MAX_PEERS 16
-enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3, MOE_GEMM_STREAM = 4 };
+enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3, MOE_GEMM_STREAM = 4,
+       MOE_GEMM_MX = 5 };
 
 const char* moe_last_error(void);
 int moe_abi_version(void);
@@ -140,6 +142,17 @@ int moe_weight_layout_to_b200(const uint8_t* q, int64_t q_stride_e, int64_t q_st
                               int E, int K, int N, uint8_t* out_values, uint8_t* out_scales, void* stream);
 int moe_weight_layout_from_b200(const uint8_t* values, const uint8_t* scales, int E, int K, int N,
                                 uint8_t* q /* [E][N][K/2] */, uint8_t* scale /* [E][N][K/32] */, void* stream);
+/* The layout the block-scaled kernel (tcgen05.mma.kind::mxf8f6f4) streams, same sizes as above
+ * (moe_weight_b200_value_bytes / _scale_bytes): tiles ordered [E][k_tile][n_block]; a value tile is 128 rows x 64
+ * bytes of plain packed e2m1 (the TMA unit expands it to the byte-per-element operand in shared memory), a scale
+ * tile is the 128 x 4 packed block [r % 32][r / 32][group] that tcgen05.cp moves into tensor memory -- the tile of
+ * BlackwellMXScaleLayout (tensor_details/layout_details/blackwell_scale.py:165-175).  out_values must be 32-byte
+ * aligned.  Arguments as for moe_weight_layout_to_b200 / _from_b200.                                          */
+int moe_weight_layout_to_b200mx(const uint8_t* q, int64_t q_stride_e, int64_t q_stride_n,
+                                const uint8_t* scale, int64_t s_stride_e, int64_t s_stride_k, int64_t s_stride_n,
+                                int E, int K, int N, uint8_t* out_values, uint8_t* out_scales, void* stream);
+int moe_weight_layout_from_b200mx(const uint8_t* values, const uint8_t* scales, int E, int K, int N,
+                                  uint8_t* q /* [E][N][K/2] */, uint8_t* scale /* [E][N][K/32] */, void* stream);
 
 /* ---- ragged grouped GEMM -------------------------------------------------------------------------
  * Replaces matmul.py:245-766 (matmul -> matmul_details/_p_matmul.py:62 / _matmul.py:43):
@@ -184,8 +197,19 @@ typedef struct {
   int64_t gather_scratch_bytes;                    /* large gathered problems first copy the gathered rows there (one pass
                                                       over x) and the tensor-core kernel then streams consecutive rows by
                                                       TMA instead of gathering 16 bytes at a time.  NULL: gather in-kernel. */
+  /* block-scaled kernel (w_kind MOE_W_MX4_B200MX; matmul.py:130-132, 311-336 of the reference: a_mx_scale / fp8
+     activations against MXFP4 weights).  x_dtype MOE_F8E4M3 takes e4m3 rows as they are, with x_scale (e8m0,
+     [rows_x, K / 32], row pitch ld_x_scale bytes) for MXFP8 or NULL for unit scales; x_dtype MOE_BF16 is split into
+     two e4m3 terms inside the library.  mx_workspace holds the re-laid-out token blocks:
+     moe_gemm_mx_workspace_bytes(args) bytes, 1024-byte aligned.  For this kernel tile_m is the token block
+     (0 auto, 16, 32, 64, 128) and tile_n 128 / 384 pins one / three weight blocks per CTA tile.                 */
+  const uint8_t* x_scale; int64_t ld_x_scale;
+  void* mx_workspace; int64_t mx_workspace_bytes;
+  int idle_sms;                                    /* persistent kernels leave this many SMs without a CTA
+                                                      (matmul.py:239-243 matmul_set_idle_sms of the reference) */
 } MoeGemmArgs;
 int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
+size_t moe_gemm_mx_workspace_bytes(const MoeGemmArgs* args_host);
 
 /* ---- expert-parallel row movement ------------------------------------------------------------------
  * Local halves of convert_dp_to_ep / convert_ep_to_dp (distributed.py:176-211, 256-283).  Two forms of the

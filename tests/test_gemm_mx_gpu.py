@@ -1,0 +1,183 @@
+"""The block-scaled grouped GEMM (tcgen05.mma.kind::mxf8f6f4: MXFP4 weights straight into the MMA) on the GPU against
+the CPU oracle: e4m3 and MXFP8 activations (the reference's `a_mx_scale` mode, tests/test_matmul.py:282-285), and bf16
+activations split into two e4m3 terms inside the library."""
+import pytest
+import torch
+
+import oracle
+import triton_b200 as tb
+from triton_b200.tensor import FP4, convert_layout, wrap_torch_tensor
+from triton_b200.tensor_details.layout import B200BlockScaledScaleLayout, B200BlockScaledValueLayout
+
+pytestmark = pytest.mark.gpu
+
+MAXTOL_MX4 = 3e-2          # the reference's bound for MXFP4 weights (tests/test_matmul.py:649-650)
+
+
+def quantised_weights(E, K, N, g, unit_scales=False, w_std=0.02):
+    w = (torch.randn(E, K, N, generator=g) * w_std).bfloat16()
+    wq, ws = oracle.downcast_to_mxfp_oracle(w, 1)
+    if unit_scales:
+        ws = torch.full_like(ws, 127)
+    # K contiguous, as downcast_to_mxfp(axis=1) returns it
+    wq = wq.contiguous().transpose(1, 2).contiguous().transpose(1, 2)
+    ws = ws.contiguous().transpose(1, 2).contiguous().transpose(1, 2)
+    return wq, ws, oracle.dequant_weight_oracle(wq, ws)
+
+
+def to_block_scaled(wq, ws, device):
+    tq = convert_layout(wrap_torch_tensor(wq.to(device), dtype=FP4), B200BlockScaledValueLayout())
+    ts = convert_layout(wrap_torch_tensor(ws.to(device)), B200BlockScaledScaleLayout())
+    return tq, ts
+
+
+def test_block_scaled_layout_round_trip(device):
+    g = torch.Generator().manual_seed(3)
+    for E, K, N in [(2, 96, 40), (3, 2880, 200), (1, 128, 128)]:
+        wq = torch.randint(0, 256, (E, N, K // 2), generator=g, dtype=torch.uint8).transpose(1, 2)   # [E, K/2, N], K contiguous
+        ws = torch.randint(0, 255, (E, N, K // 32), generator=g, dtype=torch.uint8).transpose(1, 2)
+        tq, ts = to_block_scaled(wq, ws, device)
+        KT, NB = (K + 127) // 128, (N + 127) // 128
+        assert tq.storage.data.numel() == E * KT * NB * 128 * 64 and ts.storage.data.numel() == E * KT * NB * 512
+        # spot-check the documented positions on the host
+        v = tq.storage.data.cpu().view(E, KT, NB, 128, 64)
+        s = ts.storage.data.cpu().view(E, KT, NB, 32, 4, 4)
+        for (e, n, k) in [(0, 0, 0), (E - 1, N - 1, K - 2), (0, min(N - 1, 33), min(K - 2, 70))]:
+            assert int(v[e, k // 128, n // 128, n % 128, (k % 128) // 2]) == int(wq[e, k // 2, n])
+            assert int(s[e, k // 128, n // 128, (n % 128) % 32, (n % 128) // 32, (k % 128) // 32]) == int(ws[e, k // 32, n])
+        from triton_b200.tensor_details.layout import StridedLayout
+        back_q = convert_layout(tq, StridedLayout(major_dim=-2))
+        back_s = convert_layout(ts, StridedLayout(major_dim=-2))
+        assert torch.equal(back_q.storage.data.cpu(), wq) and torch.equal(back_s.storage.data.cpu(), ws)
+
+
+def run_mx(x, wq, ws, sizes, device, *, a_scale=None, bias=None, gather=None, scatter=None, gammas=None, betas=None,
+           act=None, out_dtype=torch.bfloat16, block_m=None, block_n=None):
+    dev = lambda t: None if t is None else t.to(device)
+    tq, ts = to_block_scaled(wq, ws, device)
+    M = int(sizes.sum())
+    md = tb.make_ragged_tensor_metadata(dev(sizes), M)
+    pc = tb.PrecisionConfig(b_mx_scale=ts, b_microblock_size=32, a_mx_scale=dev(a_scale), out_dtype=out_dtype)
+    fa = None
+    if act:
+        fa = tb.FusedActivation(tb.FnSpecs("swiglu", tb.swiglu_fn, ("alpha", "limit"), reduction_n=2), act)
+    cons = {}
+    if block_m:
+        cons["block_m"] = block_m
+    if block_n:
+        cons["block_n"] = block_n
+    with tb.scoped_opt_flags_constraints(cons):
+        y = tb.matmul(dev(x), tq, dev(bias), md, None, dev(gather), dev(scatter), pc, betas=dev(betas), gammas=dev(gammas),
+                      fused_activation=fa)
+    tb.matmul_check_status()
+    return y.cpu()
+
+
+def dequant_act(x8, a_scale):
+    xf = x8.float()
+    if a_scale is not None:
+        xf = (xf.view(x8.shape[0], -1, 32) * torch.exp2(a_scale.float() - 127.0)[:, :, None]).reshape(x8.shape)
+    return xf
+
+
+@pytest.mark.parametrize("stage", ["unit-scales", "weight-scales", "act-scales"])
+@pytest.mark.parametrize("block_n", [128, 384])
+def test_block_scaled_dense_fp8_exact_products(stage, block_n, device):
+    """One expert, e4m3 activations: every product is exact in the tensor core and the sum is fp32, so the result
+    must match the fp32 oracle closely.  The three stages separate the value path (unit scales), the weight scales
+    (per row and k group) and the activation scales."""
+    g = torch.Generator().manual_seed(1)
+    M, K, N = 48, 384, 384
+    wq, ws, wdeq = quantised_weights(1, K, N, g, unit_scales=(stage == "unit-scales"), w_std=1.0)
+    x8 = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    a_scale = None
+    if stage == "act-scales":
+        a_scale = torch.randint(120, 134, (M, K // 32), generator=g, dtype=torch.uint8)
+    sizes = torch.tensor([M], dtype=torch.int32)
+    y = run_mx(x8, wq, ws, sizes, device, a_scale=a_scale, out_dtype=torch.float32, block_n=block_n)
+    ref = oracle.matmul_oracle(dequant_act(x8, a_scale), wdeq, None, sizes, out_dtype=torch.float32)
+    err = (y - ref).abs().max().item() / ref.abs().max().item()
+    assert err < 1e-5, f"{stage}: max error relative to max|ref| = {err}"
+
+
+CASES = [
+    # E, K, N, sizes, T
+    (4, 96, 64, [13, 0, 29, 8], 50),
+    (3, 512, 256, [130, 1, 64], 200),
+    (8, 2880, 384, [0, 17, 128, 129, 3, 0, 64, 255], 300),
+    (5, 320, 640, [60, 25, 7, 0, 51], 90),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("mode", ["plain", "gather", "scatter_w", "swiglu", "all"])
+@pytest.mark.parametrize("acts", ["bf16", "fp8", "mxfp8"])
+def test_block_scaled_grouped_gemm(case, mode, acts, device):
+    E, K, N, sizes, T = case
+    g = torch.Generator().manual_seed(hash((E, K, N, mode)) % 1000)
+    opts = dict(plain=dict(gather=False), gather=dict(gather=True),
+                scatter_w=dict(gather=True, scatter=True, weights=True), swiglu=dict(gather=True, act=True),
+                all=dict(gather=True, scatter=True, weights=True, act=True))[mode]
+    sizes_t = torch.tensor(sizes, dtype=torch.int32)
+    M = int(sizes_t.sum())
+    rows_x = T if opts.get("gather") else M
+    wq, ws, wdeq = quantised_weights(E, K, N, g)
+    xb = torch.randn(rows_x, K, generator=g).bfloat16()
+    a_scale = None
+    if acts == "bf16":
+        x, xref = xb, xb.float()
+    else:
+        x = xb.to(torch.float8_e4m3fn)
+        if acts == "mxfp8":
+            a_scale = torch.randint(122, 131, (rows_x, K // 32), generator=g, dtype=torch.uint8)
+        xref = dequant_act(x, a_scale)
+    bias = torch.randn(E, N, generator=g) * 0.1
+    gather = torch.randint(0, T, (M,), generator=g, dtype=torch.int32) if opts.get("gather") else None
+    scatter = torch.randperm(M, generator=g).int() if opts.get("scatter") else None
+    gammas = torch.rand(M, generator=g) if opts.get("weights") else None
+    betas = torch.rand(M, generator=g) if opts.get("weights") else None
+    act = (1.702, 7.0) if opts.get("act") else None
+    y = run_mx(x, wq, ws, sizes_t, device, a_scale=a_scale, bias=bias, gather=gather, scatter=scatter, gammas=gammas,
+               betas=betas, act=act)
+    ref = oracle.matmul_oracle(xref, wdeq, bias, sizes_t, gather, None, betas=betas, gammas=None if act else gammas,
+                               out_dtype=torch.float32)
+    if act:
+        ref = oracle.swiglu_oracle(ref, *act)
+        if gammas is not None:
+            ref = ref * gammas[:, None]
+    ref = ref.bfloat16()
+    if scatter is not None:
+        out = torch.zeros_like(ref)
+        out[scatter.long()] = ref
+        ref = out
+    oracle.assert_close_oracle(ref, y, maxtol=MAXTOL_MX4, rmstol=None, what=f"block-scaled gemm {acts}")
+    assert oracle.rel_l2(ref, y) < 1e-2
+
+
+@pytest.mark.parametrize("block_m", [16, 32, 64])
+def test_block_scaled_token_block_sizes(block_m, device):
+    """bf16 activations with every token-block size: experts with more rows than a block take several blocks."""
+    g = torch.Generator().manual_seed(7)
+    E, K, N = 6, 640, 640           # five weight blocks in groups of three: the last group of the last expert is partial
+    sizes = torch.tensor([70, 1, 0, 33, 16, 5], dtype=torch.int32)
+    M = int(sizes.sum())
+    wq, ws, wdeq = quantised_weights(E, K, N, g)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    y = run_mx(x, wq, ws, sizes, device, block_m=block_m, block_n=384)
+    ref = oracle.matmul_oracle(x.float(), wdeq, None, sizes, out_dtype=torch.float32).bfloat16()
+    oracle.assert_close_oracle(ref, y, maxtol=MAXTOL_MX4, rmstol=None, what="block-scaled gemm")
+    assert oracle.rel_l2(ref, y) < 1e-2
+
+
+def test_block_scaled_wide_dynamic_range_rows(device):
+    """bf16 rows whose magnitudes span 2^40: each 32-group has its own pair of scales, so small groups next to large
+    ones keep their precision."""
+    g = torch.Generator().manual_seed(9)
+    E, K, N, M = 1, 512, 128, 20
+    wq, ws, wdeq = quantised_weights(E, K, N, g)
+    x = torch.randn(M, K, generator=g)
+    x = (x * torch.exp2(torch.randint(-20, 20, (M, K // 32), generator=g).float()).repeat_interleave(32, dim=1)).bfloat16()
+    sizes = torch.tensor([M], dtype=torch.int32)
+    y = run_mx(x, wq, ws, sizes, device, out_dtype=torch.float32)
+    ref = oracle.matmul_oracle(x.float(), wdeq, None, sizes, out_dtype=torch.float32)
+    assert oracle.rel_l2(ref, y) < 1e-2

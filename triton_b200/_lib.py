@@ -14,14 +14,15 @@ _HERE = Path(__file__).resolve().parent
 # MOE_B200_LIB points at an alternative build of the library (e.g. an instrumented one)
 LIB_PATH = Path(os.environ["MOE_B200_LIB"]) if os.environ.get("MOE_B200_LIB") else _HERE / "libmoe_b200.so"
 
-MOE_F32, MOE_F16, MOE_BF16 = 0, 1, 2
+MOE_F32, MOE_F16, MOE_BF16, MOE_F8E4M3 = 0, 1, 2, 3
 MOE_ROUND_UP, MOE_ROUND_DOWN = 0, 1
 MOE_ACT_NONE, MOE_ACT_SWIGLU = 0, 1
-MOE_W_DENSE, MOE_W_MX4_CANONICAL, MOE_W_MX4_B200 = 0, 1, 2
-MOE_GEMM_AUTO, MOE_GEMM_SIMT, MOE_GEMM_TCGEN05, MOE_GEMM_TCGEN05_PAIR, MOE_GEMM_STREAM = 0, 1, 2, 3, 4
+MOE_W_DENSE, MOE_W_MX4_CANONICAL, MOE_W_MX4_B200, MOE_W_MX4_B200MX = 0, 1, 2, 3
+MOE_GEMM_AUTO, MOE_GEMM_SIMT, MOE_GEMM_TCGEN05, MOE_GEMM_TCGEN05_PAIR, MOE_GEMM_STREAM, MOE_GEMM_MX = 0, 1, 2, 3, 4, 5
 MOE_MAX_PEERS = 16
 
-_DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: MOE_BF16}
+_DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: MOE_BF16,
+               torch.float8_e4m3fn: MOE_F8E4M3}
 
 i64, i32, vp, sz, f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
 
@@ -47,6 +48,7 @@ class MoeGemmArgs(C.Structure):
         ("kernel", i32), ("tile_m", i32), ("tile_n", i32), ("status", vp),
         ("y_peers", vp * 16), ("n_y_peers", i32), ("y_rows_per_peer", i64),
         ("gather_scratch", vp), ("gather_scratch_bytes", i64),
+        ("x_scale", vp), ("ld_x_scale", i64), ("mx_workspace", vp), ("mx_workspace_bytes", i64), ("idle_sms", i32),
     ]
 
 
@@ -71,7 +73,10 @@ PROTOTYPES = {
     "moe_weight_b200_scale_bytes": (sz, [i32, i32, i32]),
     "moe_weight_layout_to_b200": (i32, [vp, i64, i64, vp, i64, i64, i64, i32, i32, i32, vp, vp, vp]),
     "moe_weight_layout_from_b200": (i32, [vp, vp, i32, i32, i32, vp, vp, vp]),
+    "moe_weight_layout_to_b200mx": (i32, [vp, i64, i64, vp, i64, i64, i64, i32, i32, i32, vp, vp, vp]),
+    "moe_weight_layout_from_b200mx": (i32, [vp, vp, i32, i32, i32, vp, vp, vp]),
     "moe_grouped_gemm": (i32, [C.POINTER(MoeGemmArgs), vp]),
+    "moe_gemm_mx_workspace_bytes": (sz, [C.POINTER(MoeGemmArgs)]),
     "moe_ep_keys": (i32, [vp, vp, vp, i64, i32, i32, vp, vp]),
     "moe_ep_pull_index": (i32, [vp, vp, vp, vp, i64, i32, vp, vp, vp]),
     "moe_gather_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),

@@ -8,6 +8,8 @@ int moe_gemm_tc_pair_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStrea
 bool moe_gemm_tc_pair_supported(const MoeGemmArgs& a, const char** why);
 int moe_gemm_stream_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st);
 bool moe_gemm_stream_supported(const MoeGemmArgs& a, const char** why);
+int moe_gemm_mx_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st);
+bool moe_gemm_mx_supported(const MoeGemmArgs& a, const char** why);
 
 // upper bound on the number of row blocks (triton_kernels tensor_details/ragged_tensor.py:73-77)
 static int64_t n_blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
@@ -61,6 +63,14 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
   }
 
   const char* why = "";
+  if (a->w_kind == MOE_W_MX4_B200MX || a->kernel == MOE_GEMM_MX) {
+    // weights laid out for the block-scaled MMA: that kernel or nothing
+    if (!moe_gemm_mx_supported(*a, &why) || (a->kernel != MOE_GEMM_AUTO && a->kernel != MOE_GEMM_MX)) {
+      moe_set_error("moe_grouped_gemm: block-scaled kernel not applicable: %s", *why ? why : "another kernel was requested");
+      return MOE_ERR_UNSUPPORTED;
+    }
+    return moe_gemm_mx_launch(p, *a, st);
+  }
   bool tc = moe_gemm_tc_supported(*a, &why);
   if ((a->kernel == MOE_GEMM_TCGEN05 || a->kernel == MOE_GEMM_TCGEN05_PAIR || a->kernel == MOE_GEMM_STREAM) && !tc) {
     moe_set_error("moe_grouped_gemm: tcgen05 kernel not applicable: %s", why);
@@ -88,7 +98,7 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
     }
     if (a->kernel != MOE_GEMM_TCGEN05_PAIR) pair = false;
     // Large gathered problems: copy the gathered rows once into the caller's scratch, then stream them by TMA.
-    const bool big = a->tile_m != 128 && (a->tile_m == 256 || a->M / (a->E > 0 ? a->E : 1) >= 12);
+    const bool big = (a->tile_m == 0 || a->tile_m == 256) && (a->tile_m == 256 || a->M / (a->E > 0 ? a->E : 1) >= 12);
     if (a->gather_indx && a->gather_scratch && big && a->gather_scratch_bytes >= (int64_t)a->M * a->K * 2) {
       const int rc = moe_gather_rows(a->x, a->ld_x * 2, a->gather_indx, a->M, (int64_t)a->K * 2, a->gather_scratch,
                                      (int64_t)a->K * 2, stream);

@@ -658,7 +658,9 @@ bool moe_gemm_tc_supported(const MoeGemmArgs& a, const char** why) {
   if ((uintptr_t)a.x % 16 != 0 || a.ld_x % 8 != 0) { *why = "activation rows are not 16-byte aligned"; return false; }
   if ((uintptr_t)a.w % 16 != 0 || (uintptr_t)a.w_scale % 16 != 0) { *why = "weights are not 16-byte aligned"; return false; }
   if ((double)a.rows_x * (double)a.ld_x * 2.0 >= 68719476736.0 * 0.99) { *why = "activations exceed 64 GB"; return false; }
-  if (a.tile_m != 0 && a.tile_m != 128 && a.tile_m != 256) { *why = "tile_m must be 0, 128 or 256"; return false; }
+  if (a.tile_m != 0 && a.tile_m != 16 && a.tile_m != 32 && a.tile_m != 64 && a.tile_m != 128 && a.tile_m != 256) {
+    *why = "tile_m must be 0, 16, 32, 64, 128 or 256"; return false;
+  }
   if (a.tile_n != 0 && a.tile_n != 128 && a.tile_n != 256) { *why = "tile_n must be 0, 128 or 256"; return false; }
   *why = "";
   return true;
@@ -702,7 +704,9 @@ int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
   // 0.51 -> 0.31 ms, 128 rows 0.70 -> 0.36 ms for a 32-expert layer.  128 x 128 tiles remain for the few-row problems
   // the streaming kernel cannot take.
   const int64_t rows_per_expert = a.M / (a.E > 0 ? a.E : 1);
-  int mh = a.tile_m == 256 ? 2 : (a.tile_m == 128 ? 1 : (rows_per_expert >= 12 ? 2 : 1));
+  // token tiles of 16 / 32 / 64 rows run as the 128-row configuration, whose MMA spans only the rows present (rounded
+  // up to 16)
+  int mh = a.tile_m == 256 ? 2 : (a.tile_m != 0 ? 1 : (rows_per_expert >= 12 ? 2 : 1));
   if (mh == 2 && a.slice_sizes && a.E > MAX_PREFIX_EXPERTS) mh = 1;
   int nh = a.tile_n == 256 ? 2 : (a.tile_n == 128 ? 1 : ((mh == 2 && a.N >= 1024) ? 2 : 1));
   if (mh == 1) nh = 1;

@@ -12,15 +12,15 @@ from typing import Callable, Sequence
 import torch
 
 from . import _lib
-from .matmul_details.opt_flags import (InapplicableConstraint, reset_opt_flags_constraints,  # noqa: F401
+from .matmul_details.opt_flags import (InapplicableConstraint, get_idle_sms, reset_opt_flags_constraints,  # noqa: F401
                                        resolve_kernel_choice, resolve_tile_m, resolve_tile_n,
                                        scoped_opt_flags_constraints, set_idle_sms,
                                        update_opt_flags_constraints)
 from .numerics import InFlexData, OutFlexData
 from .specialize import FnSpecs
 from .tensor import FP4, RaggedTensorMetadata, Tensor, convert_layout, wrap_torch_tensor
-from .tensor_details.layout import (B200MXScaleLayout, B200MXValueLayout, BlackwellMXScaleLayout,
-                                    BlackwellMXValueLayout, StridedLayout)
+from .tensor_details.layout import (B200BlockScaledScaleLayout, B200BlockScaledValueLayout, B200MXScaleLayout,
+                                    B200MXValueLayout, BlackwellMXScaleLayout, BlackwellMXValueLayout, StridedLayout)
 
 
 @dataclass(frozen=True)
@@ -191,8 +191,15 @@ def matmul(a, b, bias,
     if epilogue is not None and epilogue.specs.name != "dflt":
         raise NotImplementedError("quantising epilogues are not implemented")
     pc = precision_config
-    if pc.a_mx_scale is not None or pc.c_mx_scale is not None:
-        raise NotImplementedError("microscaled activations / outputs are not implemented")
+    if pc.c_mx_scale is not None:
+        raise NotImplementedError("microscaled outputs are not implemented")
+    a_scale = pc.a_mx_scale
+    if a_scale is not None:
+        assert pc.a_microblock_size in (None, 32), "only 32-element e8m0 micro-blocks are supported"
+        if isinstance(a_scale, Tensor):
+            if not isinstance(a_scale.storage.layout, StridedLayout):
+                raise NotImplementedError("a_mx_scale must be a plain [M, K/32] tensor")
+            a_scale = a_scale.storage.data
     fc = pc.flex_ctx
     if any(s is not None for s in (fc.lhs_data.scale, fc.rhs_data.scale, fc.out_data.expected_scale, fc.acc_data.scale)):
         raise NotImplementedError("flexpoint scales are not implemented")
@@ -222,9 +229,14 @@ def matmul(a, b, bias,
             shape = [1] + shape
         E, K, N = shape
         vl, sl = b.storage.layout, b_scale.storage.layout
-        if isinstance(vl, B200MXValueLayout) != isinstance(sl, B200MXScaleLayout):
-            raise ValueError("B200 tiled weights need both B200MXValueLayout values and B200MXScaleLayout scales")
-        if isinstance(vl, B200MXValueLayout):
+        if (type(vl) in (B200MXValueLayout, B200BlockScaledValueLayout)) != \
+                (type(sl) in (B200MXScaleLayout, B200BlockScaledScaleLayout)) or \
+                isinstance(vl, B200BlockScaledValueLayout) != isinstance(sl, B200BlockScaledScaleLayout):
+            raise ValueError("B200 tiled weights need values and scales in the matching pair of B200 layouts")
+        if isinstance(vl, B200BlockScaledValueLayout):
+            args.w_kind = _lib.MOE_W_MX4_B200MX
+            args.w, args.w_scale = b.storage.data.data_ptr(), b_scale.storage.data.data_ptr()
+        elif isinstance(vl, B200MXValueLayout):
             args.w_kind = _lib.MOE_W_MX4_B200
             args.w, args.w_scale = b.storage.data.data_ptr(), b_scale.storage.data.data_ptr()
         else:
@@ -262,6 +274,22 @@ def matmul(a, b, bias,
         args.w = wd.data_ptr()
         args.w_stride_e, args.w_stride_k, args.w_stride_n = wd.stride(0), wd.stride(1), wd.stride(2)
     assert a.shape[-1] == K, f"inner dimensions differ: {a.shape[-1]} vs {K}"
+    if a.dtype == torch.float8_e4m3fn or a_scale is not None:
+        # e4m3 / MXFP8 activations exist on the block-scaled tensor-core path only
+        if a.dtype != torch.float8_e4m3fn:
+            raise NotImplementedError("a_mx_scale is implemented for e4m3 activations (MXFP8)")
+        if args.w_kind != _lib.MOE_W_MX4_B200MX:
+            raise NotImplementedError("e4m3 / MXFP8 activations need MXFP4 weights in B200BlockScaledValueLayout / "
+                                      "B200BlockScaledScaleLayout")
+        if pc.out_dtype is None:
+            raise ValueError("e4m3 activations: set precision_config.out_dtype (bf16 or fp32)")
+        if a_scale is not None:
+            assert a_scale.dtype == torch.uint8 and tuple(a_scale.shape) == (a.shape[0], K // 32), \
+                f"a_mx_scale must be uint8 [M, K/32], got {a_scale.dtype} {tuple(a_scale.shape)}"
+            if a_scale.stride(-1) != 1:
+                a_scale = a_scale.contiguous()
+            keep.append(a_scale)
+            args.x_scale, args.ld_x_scale = a_scale.data_ptr(), a_scale.stride(0)
 
     # ---- shapes / output ------------------------------------------------------------------------------
     M = a.shape[0] if gather_indx is None else gather_indx.shape[0]
@@ -348,9 +376,17 @@ def matmul(a, b, bias,
         for i, h in enumerate(fused_comm.out_handles):
             args.y_peers[i] = int(h)
     args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05,
-                   "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR, "stream": _lib.MOE_GEMM_STREAM}[kernel_choice]
+                   "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR, "stream": _lib.MOE_GEMM_STREAM,
+                   "mx": _lib.MOE_GEMM_MX}[kernel_choice]
     args.tile_m, args.tile_n = resolve_tile_m(), resolve_tile_n()
+    args.idle_sms = get_idle_sms()
     args.status = _status_word(dev).data_ptr()
+    if args.w_kind == _lib.MOE_W_MX4_B200MX:
+        ws_bytes = lib.moe_gemm_mx_workspace_bytes(args)
+        ws = torch.empty(ws_bytes + 1024, dtype=torch.uint8, device=dev)        # token blocks in the MMA's operand layout
+        keep.append(ws)
+        args.mx_workspace = (ws.data_ptr() + 1023) // 1024 * 1024
+        args.mx_workspace_bytes = ws_bytes
     if gather_indx is not None and args.w_kind == _lib.MOE_W_MX4_B200 and a.dtype == torch.bfloat16 and M >= 2048:
         scratch = torch.empty(M * K, dtype=torch.bfloat16, device=dev)   # the library decides whether to use it
         keep.append(scratch)

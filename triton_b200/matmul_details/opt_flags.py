@@ -19,8 +19,14 @@ class InapplicableConstraint(Exception):
 
 
 def set_idle_sms(num_idle_sms: int):
+    """SMs the persistent grouped-GEMM kernels leave without a CTA, so that kernels on another stream (the
+    expert-parallel row pulls) run beside them (triton_kernels/matmul.py:239-243)."""
     global _idle_sms
-    _idle_sms = num_idle_sms
+    _idle_sms = int(num_idle_sms)
+
+
+def get_idle_sms() -> int:
+    return _idle_sms
 
 
 def get_opt_flags_constraints() -> dict:
@@ -50,22 +56,24 @@ def scoped_opt_flags_constraints(constraints):
 
 
 def resolve_tile_m() -> int:
-    """`block_m` constraint -> token rows per tile of the tensor-core kernel (0 = heuristic)."""
+    """`block_m` constraint -> token rows per tile (0 = heuristic).  The bf16 tensor-core kernel knows 128 and 256,
+    the block-scaled kernel 16, 32, 64 and 128; each kernel ignores a value it does not have."""
     bm = get_opt_flags_constraints().get("block_m")
-    return bm if bm in (128, 256) else 0
+    return bm if bm in (16, 32, 64, 128, 256) else 0
 
 
 def resolve_tile_n() -> int:
-    """`block_n` constraint -> weight rows per tile of the tensor-core kernel (0 = heuristic)."""
+    """`block_n` constraint -> weight rows per tile (0 = heuristic): 128 / 256 for the bf16 tensor-core kernel,
+    128 / 384 for the block-scaled kernel."""
     bn = get_opt_flags_constraints().get("block_n")
-    return bn if bn in (128, 256) else 0
+    return bn if bn in (128, 256, 384) else 0
 
 
 def resolve_kernel_choice() -> str:
     c = get_opt_flags_constraints()
     for k, v in c.items():
         if k == "kernel":
-            if v not in ("auto", "simt", "tcgen05", "tcgen05-pair", "stream"):
+            if v not in ("auto", "simt", "tcgen05", "tcgen05-pair", "stream", "mx"):
                 raise InapplicableConstraint(f"unknown kernel {v!r}")
         elif k == "split_k":
             if v not in (None, 1):

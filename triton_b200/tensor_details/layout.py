@@ -7,10 +7,11 @@ from .layout_details.base import Layout
 from .layout_details.strided import StridedLayout
 from .layout_details.blackwell_scale import BlackwellMXScaleLayout
 from .layout_details.blackwell_value import BlackwellMXValueLayout
-from .layout_details.b200_tiled import B200MXValueLayout, B200MXScaleLayout
+from .layout_details.b200_tiled import (B200BlockScaledScaleLayout, B200BlockScaledValueLayout, B200MXScaleLayout,
+                                        B200MXValueLayout)
 
 __all__ = ["Layout", "StridedLayout", "BlackwellMXScaleLayout", "BlackwellMXValueLayout", "B200MXValueLayout",
-           "B200MXScaleLayout", "make_default_matmul_mxfp4_w_layout", "make_default_matmul_mxfp4_w_scale_layout"]
+           "B200MXScaleLayout", "B200BlockScaledValueLayout", "B200BlockScaledScaleLayout", "make_default_matmul_mxfp4_w_layout", "make_default_matmul_mxfp4_w_scale_layout"]
 
 
 def make_default_matmul_mxfp4_w_layout(mx_axis: int = -2, allow_blackwell_value_shuffle: bool = False,
