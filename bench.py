@@ -296,7 +296,8 @@ def main():
     T = args.tokens
     E_local = N_EXPTS // world
     # every rank builds its own experts with a rank-dependent seed; router bias and tokens are seeded per rank
-    lw = make_synthetic_layer(E_local, D_MODEL, D_FF, dev, seed=1000 + rank)
+    # decode-sized steps run on the block-scaled kernel, which streams its own copy of the weights
+    lw = make_synthetic_layer(E_local, D_MODEL, D_FF, dev, seed=1000 + rank, block_scaled=(T <= 1024))
     g = torch.Generator(device=dev).manual_seed(rank)
     x = torch.randn(T, D_MODEL, device=dev, generator=g).bfloat16()
     gb = torch.Generator(device=dev).manual_seed(12345)

@@ -23,14 +23,15 @@
 //   w scales    one bulk copy of MB x 512 B, already in the [32 lanes][4 quarters][4 k groups] order;
 //   tokens      one bulk copy of a chunk the pack kernel below prepared per (token block, k step): the e4m3 rows in
 //               the swizzled operand layout followed by their 512 B of scales;
-//   scales -> tensor memory by tcgen05.cp (32x128b.warpx4), then MB x 4 MMAs of K = 32.
-// Warps: 0 producer (one thread), 1 MMA issue + tensor-memory owner, 2-5 epilogue.  Every mbarrier wait is bounded.
+//   scales -> tensor memory through registers (tcgen05.st by four loader warps), then MB x 4 MMAs of K = 32.
+// Warps: 0 producer (one thread), 1 MMA issue + tensor-memory owner, 2-5 epilogue, 6-9 scale loaders.  Every mbarrier
+// wait is bounded.
 #include "gemm_tc_common.cuh"
 #include <cuda_fp8.h>
 
 namespace {
 
-constexpr int MX_THREADS = 192;
+constexpr int MX_THREADS = 320;               // warp 0 producer, 1 MMA, 2-5 epilogue, 6-9 scale loaders
 constexpr int MX_MAX_STAGES = 8;
 constexpr int MX_W_TILE = 128 * 128;           // one weight block of a stage in shared memory (unpacked)
 constexpr int MX_W_TILE_TX = 128 * 64;         // what its copy reports to the mbarrier: the packed bytes read
@@ -38,6 +39,13 @@ constexpr int MX_WS_TILE = 512;                // its scales
 constexpr int MX_SF_COLS = 16;                 // tensor-memory columns of scales per stage (MB x 4 + 4)
 constexpr int MX_SF_BASE = 512 - MX_MAX_STAGES * MX_SF_COLS;    // 384: accumulators live below
 constexpr int MX_SMEM_LIMIT = 227 * 1024;
+constexpr int MX_CTL_BARS = 3 * MX_MAX_STAGES + 5;          // full, empty, scales-ready rings; 2 + 2 accumulator; drain
+constexpr int MX_CTL_BYTES = MX_CTL_BARS * 8 + 16;          // + tensor-memory base, abort flag
+// The unpacked weight operand takes twice its packed size in shared memory, so the ring holds only about four k steps
+// (100 KB of packed weights per SM), too few to cover the latency of HBM.  The producer therefore asks L2 for the
+// weights of this many k steps ahead of the ring (cp.async.bulk.prefetch.L2: no shared memory involved), and the
+// ring's own copies then hit L2.
+constexpr int MX_PREFETCH_STAGES = 10;
 
 struct MxParams {
   const uint8_t* xq;            // packed token chunks: [slot][k step][n_mma rows x 128 B | 1024 B scale area]
@@ -177,14 +185,8 @@ __device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap* tma
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
-// 512 bytes of scales in shared memory ([32][16 bytes]) -> 4 tensor-memory columns, replicated over the 4 lane quarters
-__device__ __forceinline__ void tmem_cp_scales(uint32_t taddr, uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);          // start address
-  d |= (uint64_t)(16 >> 4) << 16;                    // leading byte offset (one 16-byte column only: unused)
-  d |= (uint64_t)(128 >> 4) << 32;                   // 8 rows of 16 bytes per core matrix, core matrices 128 bytes apart
-  d |= (uint64_t)1 << 46;                            // no swizzle
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(d) : "memory");
+__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // instruction descriptor of kind::mxf8f6f4: A = e2m1 (code 5), B = e4m3 (code 0), both K-major, e8m0 scales,
 // M = 128, N = n; sf selects the byte (k group) of the scale words for A and B
@@ -219,18 +221,20 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
   const uint32_t ctl0 = sbase + (uint32_t)STAGES * (uint32_t)q.stage_bytes;
   auto BAR_FULL = [&](int s) { return ctl0 + 8u * (uint32_t)s; };
   auto BAR_EMPTY = [&](int s) { return ctl0 + 8u * (uint32_t)(MX_MAX_STAGES + s); };
-  auto BAR_ACC_FULL = [&](int a) { return ctl0 + 8u * (uint32_t)(2 * MX_MAX_STAGES + a); };
-  auto BAR_ACC_EMPTY = [&](int a) { return ctl0 + 8u * (uint32_t)(2 * MX_MAX_STAGES + 2 + a); };
-  const uint32_t BAR_DRAIN = ctl0 + 8u * (uint32_t)(2 * MX_MAX_STAGES + 4);
+  auto BAR_SF = [&](int s) { return ctl0 + 8u * (uint32_t)(2 * MX_MAX_STAGES + s); };      // scales are in tensor memory
+  auto BAR_ACC_FULL = [&](int a) { return ctl0 + 8u * (uint32_t)(3 * MX_MAX_STAGES + a); };
+  auto BAR_ACC_EMPTY = [&](int a) { return ctl0 + 8u * (uint32_t)(3 * MX_MAX_STAGES + 2 + a); };
+  const uint32_t BAR_DRAIN = ctl0 + 8u * (uint32_t)(3 * MX_MAX_STAGES + 4);
   uint8_t* ctl_ptr = smem + (size_t)STAGES * (size_t)q.stage_bytes;
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(ctl_ptr + 8 * (2 * MX_MAX_STAGES + 5));
-  volatile int* s_abort = reinterpret_cast<volatile int*>(ctl_ptr + 8 * (2 * MX_MAX_STAGES + 5) + 4);
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(ctl_ptr + MX_CTL_BARS * 8);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(ctl_ptr + MX_CTL_BARS * 8 + 4);
   Ctl ctl{s_abort, p.status};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < MX_MAX_STAGES; ++s) {
       mbar_init(BAR_FULL(s), 1);
       mbar_init(BAR_EMPTY(s), 1);
+      mbar_init(BAR_SF(s), 4);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(BAR_ACC_FULL(a), 1);
@@ -264,6 +268,30 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      // L2 prefetch cursor: walks the same (item, k step) sequence MX_PREFETCH_STAGES steps ahead of the ring
+      int64_t pf_item = blockIdx.x, pf_tile0 = 0;
+      int pf_kt = 0, pf_live = 0;
+      auto pf_open = [&]() {
+        if (pf_item >= n_items) return;
+        int e; int64_t row0; int rows;
+        mx_map_block(p, q.tb, pf_item % useful_m, e, row0, rows);
+        const int nb0 = (int)(pf_item / useful_m) * MB;
+        pf_tile0 = (int64_t)e * KT * NB + nb0;
+        pf_live = min(MB, NB - nb0);
+        pf_kt = 0;
+      };
+      auto pf_step = [&]() {
+        if (pf_item >= n_items) return;
+        const int64_t tile = pf_tile0 + (int64_t)pf_kt * NB;
+        prefetch_l2((const uint8_t*)p.w + tile * MX_W_TILE_TX, (uint32_t)(pf_live * MX_W_TILE_TX));
+        prefetch_l2(p.w_scale + tile * MX_WS_TILE, (uint32_t)(pf_live * MX_WS_TILE));
+        if (++pf_kt == KT) {
+          pf_item += gridDim.x;
+          pf_open();
+        }
+      };
+      pf_open();
+      for (int i = 0; i < MX_PREFETCH_STAGES; ++i) pf_step();
       for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const int64_t pid_m = item % useful_m;
         const int ng = (int)(item / useful_m);
@@ -274,6 +302,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
         const uint8_t* xsrc = q.xq + pid_m * KT * q.chunk_bytes;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
+          pf_step();
           ok = mbar_wait(BAR_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 601);
           if (!ok) break;
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
@@ -308,23 +337,21 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(BAR_FULL(s), (it / STAGES) & 1u, ctl, 602);
+          ok = ok && mbar_wait(BAR_SF(s), (it / STAGES) & 1u, ctl, 606);
           if (!ok) break;
           tc_fence_after();
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
           const uint32_t sf = tmem_base + (uint32_t)(MX_SF_BASE + s * MX_SF_COLS);
-#pragma unroll
-          for (int mb = 0; mb < MB; ++mb)
-            if (mb < mb_live) tmem_cp_scales(sf + 4u * (uint32_t)mb, st + OFF_WS + (uint32_t)mb * MX_WS_TILE);
-          tmem_cp_scales(sf + 4u * MB, st + OFF_XS);
           const uint64_t bdesc = make_desc(st + OFF_X);
+          // k group outermost: consecutive MMAs go to different accumulators
 #pragma unroll
-          for (int mb = 0; mb < MB; ++mb) {
-            if (mb < mb_live) {
-              const uint64_t adesc = make_desc(st + (uint32_t)mb * MX_W_TILE);
+          for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                mma_mxf8f6f4(d_tmem + (uint32_t)(mb * q.n_mma), adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2),
-                             mx_idesc(q.n_mma, (uint32_t)kk), sf + 4u * (uint32_t)mb, sf + 4u * MB, (kt | kk) ? 1u : 0u);
+            for (int mb = 0; mb < MB; ++mb) {
+              if (mb < mb_live)
+                mma_mxf8f6f4(d_tmem + (uint32_t)(mb * q.n_mma), make_desc(st + (uint32_t)mb * MX_W_TILE) + (uint64_t)(kk * 2),
+                             bdesc + (uint64_t)(kk * 2), mx_idesc(q.n_mma, (uint32_t)kk), sf + 4u * (uint32_t)mb, sf + 4u * MB,
+                             (kt | kk) ? 1u : 0u);
             }
           }
           mma_commit(BAR_EMPTY(s));
@@ -336,6 +363,45 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
       mbar_wait(BAR_DRAIN, 0, ctl, 605);
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ================================= scale loaders ==================================================
+    // The scales of a stage go from shared to tensor memory through registers (tcgen05.st), one warp per lane quarter:
+    // lane l of every quarter holds the 16 bytes of row l of each 512-byte scale block (the MB weight blocks, then the
+    // tokens), i.e. the four columns the MMA reads for rows l, l + 32, l + 64, l + 96.  This keeps the copies out of
+    // the in-order queue of the tensor pipe, where a tcgen05.cp ahead of every k step cost about a third of the step.
+    const int qd = warp & 3;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const int mb_live = min(MB, NB - (int)(item / useful_m) * MB);
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const int s = it % STAGES;
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_FULL(s), (it / STAGES) & 1u, ctl, 607));
+        if (!ok) break;
+        const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
+        const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(MX_SF_BASE + s * MX_SF_COLS);
+        uint4 v[MB + 1];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+          v[mb] = mb < mb_live ? lds128(st + OFF_WS + (uint32_t)mb * MX_WS_TILE + (uint32_t)lane * 16u) : make_uint4(0, 0, 0, 0);
+        v[MB] = lds128(st + OFF_XS + (uint32_t)lane * 16u);
+        if constexpr (MB == 3) {
+          asm volatile(
+              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+              "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z), "r"(v[1].w),
+              "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z), "r"(v[3].w)
+              : "memory");
+        } else {
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0].x),
+                       "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z), "r"(v[1].w)
+                       : "memory");
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_SF(s));
+      }
+    }
   } else {
     // ================================= epilogue =======================================================
     // Accumulator [weight row = lane][token = column]: lane l of the warp that owns lane quarter qd holds output
@@ -458,7 +524,7 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   pl.n_groups = (int)cdiv64(pl.NB, pl.mb);
   pl.chunk_bytes = (int64_t)pl.n_mma * 128 + 1024;
   pl.stage_bytes = pl.mb * MX_W_TILE + (int)pl.chunk_bytes + 2048;
-  const int ctl_bytes = 8 * (2 * MX_MAX_STAGES + 5) + 16;
+  const int ctl_bytes = MX_CTL_BYTES;
   int st = (MX_SMEM_LIMIT - 1024 - ctl_bytes) / pl.stage_bytes;
   pl.stages = st > MX_MAX_STAGES ? MX_MAX_STAGES : st;
   pl.acc_bufs = (2 * pl.mb * pl.n_mma <= MX_SF_BASE) ? 2 : 1;
@@ -501,7 +567,7 @@ int make_w_map(const MoeGemmArgs& a, const MxPlan& pl, CUtensorMap* map) {
 
 template <typename TY, int MB>
 int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const CUtensorMap& w_map, int idle_sms, cudaStream_t st) {
-  const int smem = pl.stages * pl.stage_bytes + 8 * (2 * MX_MAX_STAGES + 5) + 16 + 1024;
+  const int smem = pl.stages * pl.stage_bytes + MX_CTL_BYTES + 1024;
   const int64_t items = pl.grid_m * pl.n_groups;
   int sms = moe_sm_count() - idle_sms;
   if (sms < 1) sms = 1;

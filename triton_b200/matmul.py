@@ -113,7 +113,8 @@ _STATUS_TEXT = {
     501: "tcgen05 kernel: the epilogue waited for an accumulator",
     601: "block-scaled kernel: the producer waited for a free stage", 602: "block-scaled kernel: the MMA thread waited for a stage",
     603: "block-scaled kernel: the MMA thread waited for a free accumulator", 604: "block-scaled kernel: the epilogue waited for an accumulator",
-    605: "block-scaled kernel: the final MMA drain",
+    605: "block-scaled kernel: the final MMA drain", 606: "block-scaled kernel: the MMA thread waited for scales",
+    607: "block-scaled kernel: a scale loader waited for a stage",
     901: "expert-parallel peer barrier: a rank did not arrive within the limit; the step after it read stale peer buffers",
 }
 

@@ -37,10 +37,27 @@ class MoeLayerWeights:
     w1_s: torch.Tensor | None = None
     w2_q: torch.Tensor | None = None
     w2_s: torch.Tensor | None = None
+    # the same weights in the layouts of the block-scaled kernel (B200BlockScaledValueLayout / ...ScaleLayout); when
+    # present, steps with few rows per expert run on it (see `use_block_scaled`)
+    w1_bs: Tensor | None = None
+    w1_bs_scale: Tensor | None = None
+    w2_bs: Tensor | None = None
+    w2_bs_scale: Tensor | None = None
+    block_scaled_max_rows_per_expert: int = 24
 
     @property
     def n_expts(self):
         return self.b1.shape[0]
+
+    def use_block_scaled(self, n_rows: int) -> bool:
+        """Few rows per expert (decode): the block-scaled kernel streams the packed weights straight into the MMA and
+        is bound by HBM; with many rows per expert the bf16 kernel's larger token tiles win."""
+        return self.w1_bs is not None and n_rows <= self.block_scaled_max_rows_per_expert * self.n_expts
+
+    def fc_weights(self, n_rows: int):
+        if self.use_block_scaled(n_rows):
+            return self.w1_bs, self.w1_bs_scale, self.w2_bs, self.w2_bs_scale
+        return self.w1, self.w1_scale, self.w2, self.w2_scale
 
     def weight_bytes(self):
         return sum(t.storage.data.numel() for t in (self.w1, self.w1_scale, self.w2, self.w2_scale)) + \
@@ -79,13 +96,14 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     T = x.shape[0]
     ragged, gather_idx, scatter_idx, sparse = routing(logits, k)
     gammas = sparse.vals.reshape(-1)[scatter_idx.long()]               # routing weights in expert-sorted order
-    pc1 = PrecisionConfig(b_mx_scale=lw.w1_scale, b_microblock_size=32)
-    pc2 = PrecisionConfig(b_mx_scale=lw.w2_scale, b_microblock_size=32)
+    w1, w1_scale, w2, w2_scale = lw.fc_weights(T * k)
+    pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32)
+    pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32)
     with _span(gemm_timer):
-        h = matmul(x, lw.w1, lw.b1, ragged, gather_indx=gather_idx, precision_config=pc1,
+        h = matmul(x, w1, lw.b1, ragged, gather_indx=gather_idx, precision_config=pc1,
                    fused_activation=_activation(lw))
     with _span(gemm_timer):
-        y = matmul(h, lw.w2, lw.b2, ragged, scatter_indx=scatter_idx, precision_config=pc2, gammas=gammas)
+        y = matmul(h, w2, lw.b2, ragged, scatter_indx=scatter_idx, precision_config=pc2, gammas=gammas)
     z, _ = reduce(y.view(T, k, -1), dim=1)
     return z
 
@@ -114,6 +132,11 @@ class GraphedMoeLayer:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.z = self.forward(self.x, self.logits)
+
+    def replay(self):
+        """Replay on the graph's own input buffers (`self.x`, `self.logits`); the result is `self.z`."""
+        self.graph.replay()
+        return self.z
 
     def __call__(self, x, logits):
         self.x.copy_(x, non_blocking=True)

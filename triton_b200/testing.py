@@ -43,13 +43,16 @@ def assert_close(ref, tri, maxtol=None, rmstol=None, description="--", verbose=T
     assert rms_err <= rmstol
 
 
-def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=False, chunk=8):
+def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=False, chunk=8, block_scaled=False):
     """Random-init MoE expert weights of a gpt-oss-shaped layer: bf16 N(0, 0.02) quantised to MXFP4 along K,
-    bias bf16 N(0, 0.01).  Experts are generated and quantised `chunk` at a time to bound peak memory."""
+    bias bf16 N(0, 0.01).  Experts are generated and quantised `chunk` at a time to bound peak memory.
+    `block_scaled` adds a second copy in the layouts of the block-scaled kernel (used for steps with few rows per
+    expert)."""
     from .moe import MoeLayerWeights
     from .numerics_details.mxfp import downcast_to_mxfp
     from .tensor import FP4, convert_layout, wrap_torch_tensor
-    from .tensor_details.layout import make_default_matmul_mxfp4_w_layout, make_default_matmul_mxfp4_w_scale_layout
+    from .tensor_details.layout import (B200BlockScaledScaleLayout, B200BlockScaledValueLayout,
+                                        make_default_matmul_mxfp4_w_layout, make_default_matmul_mxfp4_w_scale_layout)
     g = torch.Generator(device=device).manual_seed(seed)
 
     def quant(K, N):
@@ -64,10 +67,15 @@ def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=
         s = torch.cat([t.transpose(1, 2) for t in ss]).transpose(1, 2)
         tq = convert_layout(wrap_torch_tensor(q, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=-2))
         ts = convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=-2))
-        return tq, ts, (q if keep_canonical else None), (s if keep_canonical else None)
+        bq = bs = None
+        if block_scaled:
+            bq = convert_layout(wrap_torch_tensor(q, dtype=FP4), B200BlockScaledValueLayout())
+            bs = convert_layout(wrap_torch_tensor(s), B200BlockScaledScaleLayout())
+        return tq, ts, (q if keep_canonical else None), (s if keep_canonical else None), bq, bs
 
-    w1, s1, q1, c1 = quant(d_model, 2 * d_ff)
-    w2, s2, q2, c2 = quant(d_ff, d_model)
+    w1, s1, q1, c1, bq1, bs1 = quant(d_model, 2 * d_ff)
+    w2, s2, q2, c2, bq2, bs2 = quant(d_ff, d_model)
     b1 = (torch.randn(n_expts, 2 * d_ff, device=device, generator=g) * 0.01).bfloat16()
     b2 = (torch.randn(n_expts, d_model, device=device, generator=g) * 0.01).bfloat16()
-    return MoeLayerWeights(w1, s1, b1, w2, s2, b2, w1_q=q1, w1_s=c1, w2_q=q2, w2_s=c2)
+    return MoeLayerWeights(w1, s1, b1, w2, s2, b2, w1_q=q1, w1_s=c1, w2_q=q2, w2_s=c2,
+                           w1_bs=bq1, w1_bs_scale=bs1, w2_bs=bq2, w2_bs_scale=bs2)
