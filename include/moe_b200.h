@@ -36,6 +36,9 @@ enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGE
 
 const char* moe_last_error(void);
 int moe_abi_version(void);
+/* Kernels this library has launched in the calling process so far (every launch site counts itself).  Callers
+ * use differences of it, e.g. to count the launches of one step. */
+uint64_t moe_launch_count(void);
 
 /* Device facts used by the host-side heuristics (replaces target_info.py:73-74 num_sms()). */
 typedef struct {
@@ -228,6 +231,11 @@ int moe_ep_keys(const int32_t* col_sorted, const int16_t* expt_indx, const int32
  * (0 for padding).  vals / expt_indx are the flat [T_global * k] routing outputs.                          */
 int moe_ep_pull_index(const int32_t* col_sorted, const int16_t* expt_indx, const float* vals, const int32_t* local_expt,
                       int64_t n, int k, int32_t* src_row, float* gammas, void* stream);
+/* Index of the pull combine: out[i] = owner[expt_indx[lo + i]] * rows_per_peer + row_sorted[lo + i] for the n_local flat
+ * (token, slot) entries of this rank's tokens, -1 where the entry was dropped (row_sorted < 0): the row of the owners'
+ * output buffers that moe_gather_reduce_rows_peers reads.  Replaces the index arithmetic of distributed.py:256-283. */
+int moe_ep_combine_index(const int32_t* row_sorted, const int16_t* expt_indx, const int32_t* owner, int64_t lo,
+                         int64_t n_local, int64_t rows_per_peer, int32_t* out, void* stream);
 int moe_gather_rows(const void* src, int64_t ld_src, const int32_t* row_indx, int64_t n_rows_out, int64_t row_bytes,
                     void* dst, int64_t ld_dst, void* stream);
 /* moe_gather_rows over rows that live on several devices: global row g = row_indx[r] is row g % rows_per_peer of

@@ -99,3 +99,29 @@ def moe_layer_oracle(x, logits, w1, b1, w2, b2, k, alpha, limit, fuse_activation
     h = swiglu_oracle(h.float(), alpha, limit).to(x.dtype)
     y = matmul_oracle(h, w2, b2, col_sum, scatter_indx=col_sorted, gammas=gam)
     return reduce_oracle(y.view(T, k, -1), dim=1)
+
+
+def moe_layer_tokens_oracle(x_rows, logits_rows, expert_weights, k, alpha, limit):
+    """The layer of ``moe_layer_oracle`` for a few token rows of a large problem, without materialising every
+    expert: ``expert_weights(e) -> (w1 [K, 2F], b1 [2F], w2 [F, K], b2 [K])`` returns the dequantised weights of
+    expert ``e`` (float tensors) and is called once per expert the rows are routed to.
+
+    Same steps and roundings as ``moe_layer_oracle``: top-k + softmax over the selected logits (topk.py:144-185),
+    fc1 + bias in fp32 rounded to the activation dtype, SwiGLU (swiglu.py:89-100) rounded to the activation
+    dtype, fc2 + bias times the routing weight rounded to the activation dtype (matmul.py:891-927), then the
+    k-way sum in fp32 rounded once (reduce.py:1181-1214)."""
+    T = x_rows.shape[0]
+    vals, indx, _ = topk_oracle(logits_rows, k, apply_softmax=True)
+    dt = x_rows.dtype
+    y = torch.zeros((T, k, x_rows.shape[1]), dtype=dt)
+    cache = {}
+    for t in range(T):
+        for j in range(k):
+            e = int(indx[t, j])
+            if e not in cache:
+                cache[e] = [w.float() for w in expert_weights(e)]
+            w1, b1, w2, b2 = cache[e]
+            h = (x_rows[t].float() @ w1 + b1).to(dt)
+            h = swiglu_oracle(h.float(), alpha, limit).to(dt)
+            y[t, j] = ((h.float() @ w2 + b2) * vals[t, j].float()).to(dt)
+    return reduce_oracle(y, dim=1)

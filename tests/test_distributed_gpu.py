@@ -1,5 +1,6 @@
-"""Expert-parallel MoE layer on 2 (or 4) GPUs, one process per GPU over NCCL, against the single-GPU layer
-(the reference's tests/test_distributed.py:325-342 compares the same pair)."""
+"""Expert-parallel MoE layer on 2, 4 or 8 GPUs, one process per GPU over NCCL, against the single-GPU layer: the eager
+step with every exchange form, then the step replayed from a CUDA graph on two further inputs (the reference's
+tests/test_distributed.py:306-342 compares the same pairs, graph replay included)."""
 import os
 
 import pytest
@@ -22,7 +23,8 @@ def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
         from triton_b200.moe import MoeLayerWeights, moe_layer_forward, moe_layer_forward_ep
         from triton_b200.testing import make_synthetic_layer
         from triton_b200.tensor import FP4, convert_layout, wrap_torch_tensor
-        from triton_b200.tensor_details.layout import B200MXScaleLayout, B200MXValueLayout
+        from triton_b200.tensor_details.layout import (B200BlockScaledScaleLayout, B200BlockScaledValueLayout,
+                                                       B200MXScaleLayout, B200MXValueLayout)
         torch.manual_seed(0)
         lw = make_synthetic_layer(n_expts, d_model, d_ff, dev, seed=0, keep_canonical=True)     # same on every rank
         x = torch.randn(n_tokens, d_model, device=dev).bfloat16()
@@ -32,14 +34,18 @@ def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
         assign = tb.make_expt_assignment(world, n_expts, expt_dict, dev)
         mine = assign.expt_boolmask[rank]
 
-        def shard(q, s):
-            tq = convert_layout(wrap_torch_tensor(q[mine].transpose(1, 2).contiguous().transpose(1, 2), dtype=FP4), B200MXValueLayout())
-            ts = convert_layout(wrap_torch_tensor(s[mine].transpose(1, 2).contiguous().transpose(1, 2)), B200MXScaleLayout())
+        def shard(q, s, vl=B200MXValueLayout, sl_=B200MXScaleLayout):
+            tq = convert_layout(wrap_torch_tensor(q[mine].transpose(1, 2).contiguous().transpose(1, 2), dtype=FP4), vl())
+            ts = convert_layout(wrap_torch_tensor(s[mine].transpose(1, 2).contiguous().transpose(1, 2)), sl_())
             return tq, ts
 
         w1, s1 = shard(lw.w1_q, lw.w1_s)
         w2, s2 = shard(lw.w2_q, lw.w2_s)
         lw_local = MoeLayerWeights(w1, s1, lw.b1[mine].contiguous(), w2, s2, lw.b2[mine].contiguous())
+        # the block-scaled copy too: steps with few rows per expert run on it
+        lw_local.w1_bs, lw_local.w1_bs_scale = shard(lw.w1_q, lw.w1_s, B200BlockScaledValueLayout, B200BlockScaledScaleLayout)
+        lw_local.w2_bs, lw_local.w2_bs_scale = shard(lw.w2_q, lw.w2_s, B200BlockScaledValueLayout, B200BlockScaledScaleLayout)
+        ret[f"block_scaled{rank}"] = lw_local.use_block_scaled(n_tokens * k // world)
         pool = tb.SymmetricMemoryPool(tb.Mesh(dist.group.WORLD))
         pool.initialize_matmul(n_tokens, d_model, d_model, k, n_expts, torch.bfloat16, dev)
         T_local = n_tokens // world
@@ -57,20 +63,40 @@ def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
             dist.all_gather_into_tensor(z_all, z_loc)
             oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3,
                                        what=f"EP ({exchange}, fused={fused}) vs single GPU")
+        if pool.peer_ok:
+            # what the benchmark times: the collective-free step captured once and replayed on new inputs
+            from triton_b200.moe import GraphedMoeLayer
+            gl = GraphedMoeLayer(lw_local, k, T_local, d_model, n_expts, dev, forward=lambda xi, li: moe_layer_forward_ep(
+                xi, li, lw_local, k, assign, pool, exchange="peer"))
+            for seed in (11, 12):
+                g2 = torch.Generator(device=dev).manual_seed(seed)               # the same batch on every rank
+                x2 = torch.randn(n_tokens, d_model, device=dev, generator=g2).bfloat16()
+                l2 = torch.randn(n_tokens, n_expts, device=dev, generator=g2)
+                z_ref2 = moe_layer_forward(x2, l2, lw, k)
+                z_loc = gl(x2[sl].contiguous(), l2[sl].contiguous())
+                tb.matmul_check_status()
+                z_all = torch.empty_like(z_ref2)
+                dist.all_gather_into_tensor(z_all, z_loc)
+                oracle.assert_close_oracle(z_ref2.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3,
+                                           what=f"EP graph replay (seed {seed}) vs single GPU")
+            ret[f"graph{rank}"] = True
         ret[rank] = 1
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("n_tokens, d_model, d_ff, n_expts, k, mode", [
     (16, 64, 64, 4, 4, "uniform"),
     (128, 512, 256, 16, 4, "random"),
+    (64, 2880, 2880, 32, 4, "random"),            # decode-sized: few rows per expert, the block-scaled kernel
     (4096, 2880, 2880, 128, 4, "uniform"),
 ])
 def test_expert_parallel_layer_matches_single_gpu(world, n_tokens, d_model, d_ff, n_expts, k, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
+    if n_expts % world or n_tokens % world:
+        pytest.skip("experts / tokens do not divide over the ranks")
     port = 29700 + (os.getpid() + world * 7 + n_tokens) % 2000
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()

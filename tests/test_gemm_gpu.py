@@ -299,3 +299,46 @@ def test_host_streaming_layer(layer_20b, device):
     tb.matmul_check_status()
     for i in range(5):
         assert torch.equal(zs[i], want[i]), i
+
+
+def _sampled_layer_check(lw, n_expts, tokens, device, seed, skew, n_sample=8):
+    """Run the layer on `tokens` tokens and compare `n_sample` of its output rows with the CPU oracle, which needs only
+    the experts those rows are routed to."""
+    from triton_b200.moe import moe_layer_forward
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(tokens, 2880, device=device, generator=g).bfloat16()
+    logits = torch.randn(tokens, n_expts, device=device, generator=g)
+    if skew:
+        logits = logits + torch.randn(n_expts, device=device, generator=g)
+    z = moe_layer_forward(x, logits, lw, 4)
+    tb.matmul_check_status()
+    rows = torch.linspace(0, tokens - 1, n_sample).round().long().unique()
+
+    def expert_weights(e):
+        w1 = oracle.dequant_weight_oracle(lw.w1_q[e:e + 1].cpu(), lw.w1_s[e:e + 1].cpu())[0]
+        w2 = oracle.dequant_weight_oracle(lw.w2_q[e:e + 1].cpu(), lw.w2_s[e:e + 1].cpu())[0]
+        return w1, lw.b1[e].cpu(), w2, lw.b2[e].cpu()
+
+    ref = oracle.moe_layer_tokens_oracle(x[rows.to(device)].cpu(), logits[rows.to(device)].cpu(), expert_weights, 4, 1.702, 7.0)
+    got = z[rows.to(device)].cpu()
+    oracle.assert_close_oracle(ref, got, maxtol=MAXTOL_MX4, rmstol=None, what=f"layer E={n_expts} T={tokens}, sampled rows")
+    assert oracle.rel_l2(ref, got) < 1e-2
+    assert torch.isfinite(z.float()).all()
+
+
+def test_gpt_oss_120b_layer_benchmark_configuration_against_oracle(device):
+    """The benchmarked configuration itself -- 128 experts, 16384 tokens, skewed router: 256 x 256 tiles, TMA activation
+    loads, row-gather scratch -- against the CPU oracle on sampled tokens."""
+    from triton_b200.testing import make_synthetic_layer
+    lw = make_synthetic_layer(128, 2880, 2880, device, seed=1000, keep_canonical=True)
+    _sampled_layer_check(lw, 128, 16384, device, seed=0, skew=True)
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 64, 300])
+def test_gpt_oss_120b_layer_decode_path_against_oracle(tokens, device):
+    """Decode-sized steps of the 128-expert layer take the block-scaled kernel (its own copy of the weights); 300 tokens
+    (more than 24 rows per expert on average would switch kernels, 9 do not) still do."""
+    from triton_b200.testing import make_synthetic_layer
+    lw = make_synthetic_layer(128, 2880, 2880, device, seed=1000, keep_canonical=True, block_scaled=True)
+    assert lw.use_block_scaled(tokens * 4)
+    _sampled_layer_check(lw, 128, tokens, device, seed=tokens, skew=True, n_sample=min(tokens, 6))

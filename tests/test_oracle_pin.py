@@ -143,3 +143,20 @@ def test_layouts_match_reference_fixture(golden):
     assert torch.equal(vw[:, :48], g["value_swizzled"][:, :48])
     assert g["value_swizzled_strides"].tolist() == [128 * 40, 1, 128]
     assert torch.equal(oracle.unswizzle_mx_value_bw_oracle(vw, (2, 96, 40)), g["value"])
+
+
+def test_token_sampled_layer_oracle_equals_layer_oracle():
+    """`moe_layer_tokens_oracle` (used to check a few rows of a full-size layer) reproduces the rows of
+    `moe_layer_oracle` exactly."""
+    g = torch.Generator().manual_seed(0)
+    T, E, k, d, ff = 64, 8, 2, 64, 96
+    x = torch.randn(T, d, generator=g).bfloat16()
+    logits = torch.randn(T, E, generator=g)
+    w1 = (torch.randn(E, d, 2 * ff, generator=g) * 0.1).bfloat16()
+    w2 = (torch.randn(E, ff, d, generator=g) * 0.1).bfloat16()
+    b1 = (torch.randn(E, 2 * ff, generator=g) * 0.01).bfloat16()
+    b2 = (torch.randn(E, d, generator=g) * 0.01).bfloat16()
+    full = oracle.moe_layer_oracle(x, logits, w1, b1, w2, b2, k, 1.702, 7.0)
+    rows = torch.tensor([3, 17, 40, 63])
+    part = oracle.moe_layer_tokens_oracle(x[rows], logits[rows], lambda e: (w1[e], b1[e], w2[e], b2[e]), k, 1.702, 7.0)
+    assert torch.equal(full[rows], part)

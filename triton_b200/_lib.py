@@ -56,6 +56,7 @@ class MoeGemmArgs(C.Structure):
 PROTOTYPES = {
     "moe_last_error": (C.c_char_p, []),
     "moe_abi_version": (i32, []),
+    "moe_launch_count": (C.c_uint64, []),
     "moe_device_info": (i32, [i32, C.POINTER(MoeDeviceInfo)]),
     "moe_downcast_mxfp4": (i32, [vp, i32, i64, i64, i64, i64, i64, i64, vp, vp, i32, vp]),
     "moe_upcast_mxfp4": (i32, [vp, vp, vp, i32, i64, i64, i64, i64, i64, i64, vp]),
@@ -79,6 +80,7 @@ PROTOTYPES = {
     "moe_gemm_mx_workspace_bytes": (sz, [C.POINTER(MoeGemmArgs)]),
     "moe_ep_keys": (i32, [vp, vp, vp, i64, i32, i32, vp, vp]),
     "moe_ep_pull_index": (i32, [vp, vp, vp, vp, i64, i32, vp, vp, vp]),
+    "moe_ep_combine_index": (i32, [vp, vp, vp, i64, i64, i64, vp, vp]),
     "moe_gather_rows": (i32, [vp, i64, vp, i64, i64, vp, i64, vp]),
     "moe_gather_rows_peers": (i32, [vp, i32, i64, i64, vp, i64, i64, vp, i64, vp]),
     "moe_peer_barrier": (i32, [vp, i32, i32, vp, vp, vp]),

@@ -1,6 +1,7 @@
 // Error reporting, version and device facts of the C ABI.
 #include "common.cuh"
 #include <stdarg.h>
+#include <atomic>
 
 static thread_local char g_err[512] = "";
 
@@ -22,6 +23,10 @@ int moe_sm_count() {
   }
   return cached[dev];
 }
+
+static std::atomic<uint64_t> g_launches{0};
+void moe_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" __attribute__((visibility("default"))) uint64_t moe_launch_count(void) { return g_launches.load(); }
 
 extern "C" __attribute__((visibility("default"))) const char* moe_last_error(void) { return g_err; }
 extern "C" __attribute__((visibility("default"))) int moe_abi_version(void) { return 1; }

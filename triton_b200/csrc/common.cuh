@@ -27,7 +27,12 @@ void moe_set_error(const char* fmt, ...);
     }                                                                                     \
   } while (0)
 
-#define MOE_CHECK_LAUNCH() MOE_CHECK_CUDA(cudaGetLastError())
+void moe_count_launch();   // one kernel launch (api.cu keeps the process-wide counter)
+#define MOE_CHECK_LAUNCH()              \
+  do {                                  \
+    moe_count_launch();                 \
+    MOE_CHECK_CUDA(cudaGetLastError()); \
+  } while (0)
 
 static inline int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

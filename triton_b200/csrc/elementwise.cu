@@ -459,6 +459,34 @@ extern "C" __attribute__((visibility("default"))) int moe_ep_pull_index(const in
   return MOE_OK;
 }
 
+// Index of the pull combine: for the n_local flat (token, slot) entries of this rank's tokens (flat indices
+// [lo, lo + n_local)), the global row of the owners' output buffers that holds the entry's expert output:
+// owner[expert] * rows_per_peer + row_sorted[flat], or -1 for a dropped entry (row_sorted < 0).
+namespace {
+__global__ void __launch_bounds__(256) ep_combine_index_kernel(const int32_t* __restrict__ row_sorted,
+                                                               const int16_t* __restrict__ expt_indx,
+                                                               const int32_t* __restrict__ owner, int64_t lo, int64_t n_local,
+                                                               int64_t rows_per_peer, int32_t* __restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_local; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t pos = row_sorted[lo + i];
+    const int e = expt_indx[lo + i];
+    out[i] = (pos < 0 || e < 0) ? -1 : (int32_t)((int64_t)owner[e] * rows_per_peer + pos);
+  }
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_ep_combine_index(const int32_t* row_sorted, const int16_t* expt_indx,
+                                                                           const int32_t* owner, int64_t lo, int64_t n_local,
+                                                                           int64_t rows_per_peer, int32_t* out, void* stream) {
+  MOE_CHECK_ARG(lo >= 0 && n_local >= 0 && rows_per_peer > 0, "moe_ep_combine_index: bad extents");
+  if (n_local == 0) return MOE_OK;
+  MOE_CHECK_ARG(row_sorted && expt_indx && owner && out, "moe_ep_combine_index: NULL pointer");
+  ep_combine_index_kernel<<<grid_for(n_local, 256), 256, 0, (cudaStream_t)stream>>>(row_sorted, expt_indx, owner, lo, n_local,
+                                                                                   rows_per_peer, out);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // y[t, :] = sum_{j < k} src[row_indx[t * k + j], :]   (row_indx < 0: skipped), fp32 accumulation, bf16 rows.
 // The k-way combine of an expert-parallel layer read straight out of the receive buffer of the combine

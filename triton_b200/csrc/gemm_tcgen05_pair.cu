@@ -569,6 +569,7 @@ template <typename TY> int launch_pair(const GemmParams& p, int64_t grid_m, int6
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
+  moe_count_launch();
   MOE_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, grid_m, x_map));
   return MOE_OK;
 }

@@ -94,8 +94,19 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     """x [T, d_model] bf16, logits [T, E] -> [T, d_model]: sum over the k selected experts of
     softmax-weight * (SwiGLU(x W1 + b1) W2 + b2)."""
     T = x.shape[0]
-    ragged, gather_idx, scatter_idx, sparse = routing(logits, k)
-    gammas = sparse.vals.reshape(-1)[scatter_idx.long()]               # routing weights in expert-sorted order
+    sparse = topk(logits, k, apply_softmax=True)
+    md = sparse.mask_metadata
+    n = T * k
+    ragged = make_ragged_tensor_metadata(md.col_sum, n)
+    scatter_idx = md.col_sorted_indx                                    # sorted position -> flat (token, slot) row
+    # token row and routing weight of every expert-sorted position, by one kernel (padding positions read no row)
+    from . import _lib
+    gather_idx = torch.empty(n, dtype=torch.int32, device=x.device)
+    gammas = torch.empty(n, dtype=torch.float32, device=x.device)
+    indx16 = sparse.indx if sparse.indx.dtype == torch.int16 else sparse.indx.to(torch.int16)
+    _lib.check(_lib.load().moe_ep_pull_index(_lib.ptr(scatter_idx.reshape(-1)), _lib.ptr(indx16.contiguous()),
+                                             _lib.ptr(sparse.vals.contiguous()), _lib.ptr(_all_local(logits.shape[1], x.device)),
+                                             n, k, _lib.ptr(gather_idx), _lib.ptr(gammas), _lib.stream()), "moe_ep_pull_index")
     w1, w1_scale, w2, w2_scale = lw.fc_weights(T * k)
     pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32)
     pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32)
@@ -106,6 +117,17 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
         y = matmul(h, w2, lw.b2, ragged, scatter_indx=scatter_idx, precision_config=pc2, gammas=gammas)
     z, _ = reduce(y.view(T, k, -1), dim=1)
     return z
+
+
+_all_local_cache = {}
+
+
+def _all_local(n_expts, device):
+    """int32 zeros [n_expts]: the "every expert lives here" table of moe_ep_pull_index."""
+    key = (n_expts, torch.device(device).index)
+    if key not in _all_local_cache:
+        _all_local_cache[key] = torch.zeros(n_expts, dtype=torch.int32, device=device)
+    return _all_local_cache[key]
 
 
 class GraphedMoeLayer:
@@ -195,7 +217,7 @@ class HostStreamingLayer:
         torch.cuda.current_stream(self.dev).wait_stream(self.s_in)
 
 
-def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer):
+def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer, mark=None):
     """Expert-parallel layer over peer-mapped buffers: the dispatch is one gather kernel that pulls every routed token
     row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want); fc2 writes its rows
     into this rank's symmetric output buffer, and the combine is one kernel in which every token reads its k rows from
@@ -216,48 +238,74 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
     # positions whose expert lives here pull their token's row; all others are skipped (and never read by the GEMMs)
     src_row = torch.empty(n, dtype=torch.int32, device=dev)
     gammas = torch.empty(n, dtype=torch.float32, device=dev)
+    mark = mark or (lambda name: None)
     indx16 = sparse.indx if sparse.indx.dtype == torch.int16 else sparse.indx.to(torch.int16)
-    local_expt = expt_assignment.expt_map[rank, :].to(torch.int32).contiguous()
-    _lib.check(lib.moe_ep_pull_index(_lib.ptr(col), _lib.ptr(indx16.contiguous()), _lib.ptr(sparse.vals.contiguous()),
+    indx16 = indx16.contiguous()
+    local_expt, owner = _ep_tables(expt_assignment, rank)
+    mark("metadata")
+    _lib.check(lib.moe_ep_pull_index(_lib.ptr(col), _lib.ptr(indx16), _lib.ptr(sparse.vals.contiguous()),
                                      _lib.ptr(local_expt), n, k, _lib.ptr(src_row), _lib.ptr(gammas), _lib.stream()),
                "moe_ep_pull_index")
-    pool.xbuf.copy_(x_local)
+    if x_local.data_ptr() != pool.xbuf.data_ptr():                     # a caller may keep its tokens in the pool's buffer
+        pool.xbuf.copy_(x_local)
     pool.barrier()                                                     # every rank's tokens are in its buffer
+    mark("pull index + token barrier")
     x_sorted = torch.empty((n, d), dtype=x_local.dtype, device=dev)
     ptrs = (ctypes.c_void_p * W)(*pool.x_ptrs)
     _lib.check(lib.moe_gather_rows_peers(ptrs, W, T_local, d * x_local.element_size(), _lib.ptr(src_row), n,
                                          d * x_local.element_size(), _lib.ptr(x_sorted),
                                          d * x_local.element_size(), _lib.stream()), "moe_gather_rows_peers")
-    pc1 = PrecisionConfig(b_mx_scale=lw_local.w1_scale, b_microblock_size=32)
-    pc2 = PrecisionConfig(b_mx_scale=lw_local.w2_scale, b_microblock_size=32)
+    mark("dispatch pull")
+    w1, w1_scale, w2, w2_scale = lw_local.fc_weights(n // W)            # rows this rank multiplies, on average
+    pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32)
+    pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32)
     with _span(gemm_timer):
-        h = matmul(x_sorted, lw_local.w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
+        h = matmul(x_sorted, w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
                    fused_activation=_activation(lw_local))
+    mark("fc1")
     with _span(gemm_timer):
-        y = matmul(h, lw_local.w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas,
+        y = matmul(h, w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas,
                    c=pool.ybuf)
+    mark("fc2")
     pool.barrier()                                                     # every rank's expert outputs are written
     # combine: each (local token, slot) reads its row from the buffer of the rank that owns the slot's expert and
-    # the k rows are summed on the fly
-    from .distributed import expert_owner
+    # the k rows are summed on the fly; dropped entries (-1) stay dropped
     lo = rank * T_local * k
-    pos = md.row_sorted_indx.reshape(-1)[lo:lo + T_local * k]
-    own = expert_owner(expt_assignment).to(torch.int32)[indx16.reshape(-1)[lo:lo + T_local * k].long()]
-    comb = torch.where(pos < 0, pos, own * n + pos).to(torch.int32)     # dropped entries (-1) stay dropped
+    comb = torch.empty(T_local * k, dtype=torch.int32, device=dev)
+    _lib.check(lib.moe_ep_combine_index(_lib.ptr(md.row_sorted_indx.reshape(-1)), _lib.ptr(indx16), _lib.ptr(owner), lo,
+                                        T_local * k, n, _lib.ptr(comb), _lib.stream()), "moe_ep_combine_index")
     z = torch.empty((T_local, y.shape[1]), dtype=y.dtype, device=dev)
     yptrs = (ctypes.c_void_p * W)(*pool.y_ptrs)
     _lib.check(lib.moe_gather_reduce_rows_peers(yptrs, W, n, y.stride(0), _lib.ptr(comb), T_local, k, y.shape[1],
                                                 _lib.ptr(z), z.stride(0), _lib.stream()), "moe_gather_reduce_rows_peers")
+    mark("output barrier + combine")
     return z
 
 
+_ep_table_cache = {}
+
+
+def _ep_tables(expt_assignment, rank):
+    """(local index of every expert on `rank` or -1, owner rank of every expert) as int32 device tensors, computed once
+    per assignment (they are pure functions of it)."""
+    key = (id(expt_assignment), rank)
+    hit = _ep_table_cache.get(key)
+    if hit is None or hit[0] is not expt_assignment:
+        from .distributed import expert_owner
+        local_expt = expt_assignment.expt_map[rank, :].to(torch.int32).contiguous()
+        owner = expert_owner(expt_assignment).to(torch.int32).contiguous()
+        _ep_table_cache[key] = hit = (expt_assignment, local_expt, owner)
+    return hit[1], hit[2]
+
+
 def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: int, expt_assignment, pool,
-                         gemm_timer=None, fused_exchange=True, exchange="auto"):
+                         gemm_timer=None, fused_exchange=True, exchange="auto", mark=None):
     """Expert-parallel layer: tokens are sharded over ranks (x_local [T_local, d_model]), experts over ranks
     (lw_local holds this rank's experts, in increasing global id).  Routing metadata is all-gathered; token rows
     travel to the expert owners and back either through kernels that read the other ranks' peer-mapped buffers
     (the default when the pool has them) or by one NCCL all-to-all each way.
 
+    `mark` (optional): called with a phase name after each phase has been enqueued (a benchmark records an event).
     `exchange`: "peer" (pull-dispatch / pull-combine kernels over the pool's peer-mapped buffers, see
     `SymmetricMemoryPool.enable_peer_buffers`), "nccl" (all-to-all), "auto" (peer when the pool has the buffers).
     With `fused_exchange` (NCCL form) the two GEMMs read and write the exchange buffers through index maps (fc1 gathers from
@@ -276,8 +324,10 @@ def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: in
     peer_fit = pool.peer_ok and pool.peer_shape == (T_local, x_local.shape[1], lw_local.w2.shape[-1], k, x_local.dtype)
     if exchange == "peer" and not peer_fit:
         raise RuntimeError(f"peer exchange is not available: {pool.peer_error}")
+    if mark is not None:
+        mark("routing + all-gather + expert sort")
     if exchange in ("auto", "peer") and peer_fit:
-        return _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer)
+        return _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer, mark)
     md = sparse.mask_metadata
     n_entries = md.row_sorted_indx.shape[0]
     meta_global = make_ragged_tensor_metadata(md.col_sum, n_entries)

@@ -43,11 +43,13 @@ def assert_close(ref, tri, maxtol=None, rmstol=None, description="--", verbose=T
     assert rms_err <= rmstol
 
 
-def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=False, chunk=8, block_scaled=False):
+def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=False, chunk=8, block_scaled=False,
+                         layouts=True):
     """Random-init MoE expert weights of a gpt-oss-shaped layer: bf16 N(0, 0.02) quantised to MXFP4 along K,
     bias bf16 N(0, 0.01).  Experts are generated and quantised `chunk` at a time to bound peak memory.
     `block_scaled` adds a second copy in the layouts of the block-scaled kernel (used for steps with few rows per
-    expert)."""
+    expert).  `layouts=False` skips every re-layout and returns the canonical tensors only (a checker that wants the
+    very weights another process generated from the same seed)."""
     from .moe import MoeLayerWeights
     from .numerics_details.mxfp import downcast_to_mxfp
     from .tensor import FP4, convert_layout, wrap_torch_tensor
@@ -65,13 +67,15 @@ def make_synthetic_layer(n_expts, d_model, d_ff, device, seed=0, keep_canonical=
             ss.append(s)
         q = torch.cat([t.transpose(1, 2) for t in qs]).transpose(1, 2)          # keeps K contiguous
         s = torch.cat([t.transpose(1, 2) for t in ss]).transpose(1, 2)
-        tq = convert_layout(wrap_torch_tensor(q, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=-2))
-        ts = convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=-2))
-        bq = bs = None
-        if block_scaled:
+        tq = ts = bq = bs = None
+        if layouts:
+            tq = convert_layout(wrap_torch_tensor(q, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=-2))
+            ts = convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=-2))
+        if block_scaled and layouts:
             bq = convert_layout(wrap_torch_tensor(q, dtype=FP4), B200BlockScaledValueLayout())
             bs = convert_layout(wrap_torch_tensor(s), B200BlockScaledScaleLayout())
-        return tq, ts, (q if keep_canonical else None), (s if keep_canonical else None), bq, bs
+        keep = keep_canonical or not layouts
+        return tq, ts, (q if keep else None), (s if keep else None), bq, bs
 
     w1, s1, q1, c1, bq1, bs1 = quant(d_model, 2 * d_ff)
     w2, s2, q2, c2, bq2, bs2 = quant(d_ff, d_model)
