@@ -523,8 +523,21 @@ def micro_record(dev, peaks, steps=5):
             ts.append(e0.elapsed_time(e1))
         return median(ts), launches
 
+    # a write-dominated kernel cannot reach the copy bandwidth (half reads, half writes): measure the pure-write rate too
+    big = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    fill_ms = []
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        big.zero_()
+        e1.record()
+        torch.cuda.synchronize()
+        fill_ms.append(e0.elapsed_time(e1))
+    write_gbs = (1 << 30) / (min(fill_ms[2:]) * 1e-3) / 1e9
+    del big
     out = {"l2": "flushed by a 512 MB write before every timed call", "peak_gbs": peaks["hbm_gbs"],
-           "peak_source": f"{peaks['source']} copy bandwidth", "kernels": {}}
+           "peak_source": f"{peaks['source']} copy bandwidth", "write_only_gbs": write_gbs,
+           "write_only_source": "torch zero_ of 1 GiB, best of 4, measured in this run", "kernels": {}}
 
     def add(name, res, nbytes):
         ms, launches = res
@@ -545,6 +558,10 @@ def micro_record(dev, peaks, steps=5):
     nb = R * C * 2 + R * C // 2 + R * C // 32
     add("downcast_to_mxfp bf16 [8192,8192] axis 1", timed(lambda: downcast_to_mxfp(x, torch.uint8, axis=1)), nb)
     add("upcast_from_mxfp -> bf16 [8192,8192] axis 1", timed(lambda: upcast_from_mxfp(q, sc, torch.bfloat16, axis=1)), nb)
+    up = out["kernels"]["upcast_from_mxfp -> bf16 [8192,8192] axis 1"]
+    # 79 % of the dequantiser's bytes are writes: its bound is the time to write R * C * 2 bytes at the write-only rate
+    up["write_bound_ms"] = R * C * 2 / write_gbs / 1e6
+    up["frac_of_write_bound"] = up["write_bound_ms"] / up["ms"]
     add("downcast_to_mxfp bf16 [8192,8192] axis 0 (strided)", timed(lambda: downcast_to_mxfp(x, torch.uint8, axis=0)), nb)
     return out
 

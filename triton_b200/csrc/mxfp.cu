@@ -9,7 +9,8 @@
 //            bits(ds) & 0x7F800000                  (ROUND_DOWN)
 //   scale  = u >> 23 ;  inv = (u == 0) ? 0 : 1 / float(u)
 //   code   = RTNE_e2m1(x * inv), saturating at +-6
-// Both kernels are HBM-bound: 16-byte loads/stores, four threads per 32-group on the contiguous path.
+// Both kernels are HBM-bound: 16-byte loads/stores, one thread per 32-group on the contiguous path (one division and
+// one scale per group, 16 bytes of codes per store).
 #include "common.cuh"
 #include <cuda_fp4.h>
 #include <type_traits>
@@ -32,18 +33,19 @@ __device__ __forceinline__ float inv_scale(uint32_t u) {
 }
 
 // Position of a grid-stride loop over [rows][chunks per row] without a division per iteration.
-struct RowCursor {
-  int64_t row, c, step_row, step_c, per_row;
-  __device__ __forceinline__ RowCursor(int64_t first, int64_t stride, int64_t chunks_per_row) {
-    per_row = chunks_per_row;
-    row = first / chunks_per_row; c = first - row * chunks_per_row;
-    step_row = stride / chunks_per_row; step_c = stride - step_row * chunks_per_row;
+template <typename I> struct RowCursorT {
+  I row, c, step_row, step_c, per_row;
+  __device__ __forceinline__ RowCursorT(int64_t first, int64_t stride, int64_t chunks_per_row) {
+    per_row = (I)chunks_per_row;
+    row = (I)(first / chunks_per_row); c = (I)(first - (int64_t)row * chunks_per_row);
+    step_row = (I)(stride / chunks_per_row); step_c = (I)(stride - (int64_t)step_row * chunks_per_row);
   }
   __device__ __forceinline__ void next() {
     row += step_row; c += step_c;
     if (c >= per_row) { c -= per_row; ++row; }
   }
 };
+using RowCursor = RowCursorT<int64_t>;
 
 // two fp32 -> one byte: `lo` in bits 0..3, `hi` in bits 4..7 (round-to-nearest-even, saturating)
 __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
@@ -56,64 +58,175 @@ template <> struct Vec16<__half> { static constexpr int N = 8; };
 template <> struct Vec16<float> { static constexpr int N = 4; };
 
 // ---- contiguous path: quant axis has unit stride, rows 16-byte aligned ------------------------------
-// One thread owns 8 consecutive elements; 4 consecutive lanes own one 32-group.  A block walks tiles of
-// ROWS_UNROLL x 256 chunks and every thread issues the loads of its ROWS_UNROLL chunks before it converts the first,
-// so that enough bytes are in flight per SM to cover the HBM latency.
-constexpr int ROWS_UNROLL = 4;
+// One thread owns whole 32-groups: 64 (or 128) contiguous input bytes as 16-byte loads, one division and one scale
+// per group, one 16-byte store of the 32 codes and one byte of scale.  GROUPS_UNROLL groups are loaded before the first
+// is converted, so that enough bytes are in flight per SM to cover the HBM latency.
+constexpr int GROUPS_UNROLL = 2;
 
-template <typename T>
-__global__ void __launch_bounds__(256) downcast_rows_kernel(const T* __restrict__ x, int64_t n_rows, int64_t quant,
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& r, float* v);
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& r, float* v) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(w[j] << 16);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+  }
+}
+template <> __device__ __forceinline__ void unpack16<__half>(const uint4& r, float* v) {
+  const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(h[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& r, float* v) {
+  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+}
+
+// the 32 values of a group as VPG raw 16-byte vectors -> scale bits and 16 bytes of codes.  The vectors are unpacked
+// twice (once for the maximum, once for the codes) instead of holding 32 floats across the division.
+template <typename T, int VPG>
+__device__ __forceinline__ uint4 quantise_raw(const uint4 (&raw)[VPG], int mode, uint32_t& sc) {
+  constexpr int EPV = 32 / VPG;
+  float m = 0.0f;
+#pragma unroll
+  for (int k = 0; k < VPG; ++k) {
+    float v[EPV];
+    unpack16<T>(raw[k], v);
+#pragma unroll
+    for (int j = 0; j < EPV; ++j) m = fmaxf(m, fabsf(v[j]));
+  }
+  sc = scale_bits(m, mode);
+  const float inv = inv_scale(sc);
+  uint32_t w[4];
+  if constexpr (EPV == 8) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float v[8];
+      unpack16<T>(raw[k], v);
+      const uint32_t b0 = e2m1x2(v[0] * inv, v[1] * inv), b1 = e2m1x2(v[2] * inv, v[3] * inv);
+      const uint32_t b2 = e2m1x2(v[4] * inv, v[5] * inv), b3 = e2m1x2(v[6] * inv, v[7] * inv);
+      w[k] = __byte_perm(b0 | (b1 << 8), b2 | (b3 << 8), 0x5410);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float v[8];
+      unpack16<T>(raw[2 * k], v);
+      unpack16<T>(raw[2 * k + 1], v + 4);
+      const uint32_t b0 = e2m1x2(v[0] * inv, v[1] * inv), b1 = e2m1x2(v[2] * inv, v[3] * inv);
+      const uint32_t b2 = e2m1x2(v[4] * inv, v[5] * inv), b3 = e2m1x2(v[6] * inv, v[7] * inv);
+      w[k] = __byte_perm(b0 | (b1 << 8), b2 | (b3 << 8), 0x5410);
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// 32 fp32 values -> scale bits and 16 bytes of codes
+__device__ __forceinline__ uint4 quantise_group(const float (&v)[32], int mode, uint32_t& sc) {
+  float m = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) m = fmaxf(m, fabsf(v[j]));
+  sc = scale_bits(m, mode);
+  const float inv = inv_scale(sc);
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t b0 = e2m1x2(v[8 * k] * inv, v[8 * k + 1] * inv), b1 = e2m1x2(v[8 * k + 2] * inv, v[8 * k + 3] * inv);
+    const uint32_t b2 = e2m1x2(v[8 * k + 4] * inv, v[8 * k + 5] * inv), b3 = e2m1x2(v[8 * k + 6] * inv, v[8 * k + 7] * inv);
+    w[k] = __byte_perm(b0 | (b1 << 8), b2 | (b3 << 8), 0x5410);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <typename T, typename I>
+__global__ void __launch_bounds__(256, sizeof(T) == 2 ? 3 : 2) downcast_rows_kernel(const T* __restrict__ x, int64_t n_rows, int64_t quant,
                                                             int64_t outer, int64_t sx_batch, int64_t sx_outer,
                                                             uint8_t* __restrict__ q, uint8_t* __restrict__ scale,
                                                             int mode) {
-  constexpr int VPC = sizeof(T) == 2 ? 1 : 2;            // 16-byte vectors per 8-element chunk
-  const int64_t chunks_per_row = quant >> 3;
-  const int64_t total = n_rows * chunks_per_row;
-  const int64_t stride = (int64_t)gridDim.x * (ROWS_UNROLL * 256);
-  const int64_t tile0 = (int64_t)blockIdx.x * (ROWS_UNROLL * 256);
-  RowCursor cur[ROWS_UNROLL] = {RowCursor(tile0 + threadIdx.x, stride, chunks_per_row),
-                                RowCursor(tile0 + 256 + threadIdx.x, stride, chunks_per_row),
-                                RowCursor(tile0 + 512 + threadIdx.x, stride, chunks_per_row),
-                                RowCursor(tile0 + 768 + threadIdx.x, stride, chunks_per_row)};
+  constexpr int EPV = 16 / (int)sizeof(T);               // elements per 16-byte vector
+  constexpr int VPG = 32 / EPV;                          // vectors per group
+  const int64_t groups_per_row = quant >> 5;
+  const int64_t total = n_rows * groups_per_row;
+  const int64_t stride = (int64_t)gridDim.x * (GROUPS_UNROLL * 256);
+  const int64_t tile0 = (int64_t)blockIdx.x * (GROUPS_UNROLL * 256);
+  RowCursorT<I> cur[GROUPS_UNROLL] = {RowCursorT<I>(tile0 + threadIdx.x, stride, groups_per_row),
+                                      RowCursorT<I>(tile0 + 256 + threadIdx.x, stride, groups_per_row)};
   const bool one_batch = outer == n_rows;
-  // every lane of a warp runs the same trip count (the shuffles below need the whole warp); lanes past the
-  // end compute on zeros and store nothing
   for (int64_t tile = tile0; tile < total; tile += stride) {
-    uint4 raw[ROWS_UNROLL][VPC];
-    bool live[ROWS_UNROLL];
+    uint4 raw[GROUPS_UNROLL][VPG];
+    bool live[GROUPS_UNROLL];
 #pragma unroll
-    for (int u = 0; u < ROWS_UNROLL; ++u) {
+    for (int u = 0; u < GROUPS_UNROLL; ++u) {
       live[u] = tile + u * 256 + threadIdx.x < total;
-      const int64_t row = live[u] ? cur[u].row : 0, c = live[u] ? cur[u].c : 0;
-      int64_t b = 0, o = row;
-      if (!one_batch) { b = row / outer; o = row - b * outer; }
-      const uint4* src = reinterpret_cast<const uint4*>(x + b * sx_batch + o * sx_outer + c * 8);
-#pragma unroll
-      for (int k = 0; k < VPC; ++k) raw[u][k] = src[k];
-    }
-#pragma unroll
-    for (int u = 0; u < ROWS_UNROLL; ++u) {
-      float v[8];
-      const T* e = reinterpret_cast<const T*>(&raw[u][0]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = to_f32<T>(e[j]);
-      float m = 0.0f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
-      m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
-      m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
-      const uint32_t sc = scale_bits(m, mode);
-      const float inv = inv_scale(sc);
-      uint32_t packed = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) packed |= e2m1x2(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
       if (live[u]) {
         const int64_t row = cur[u].row, c = cur[u].c;
-        *reinterpret_cast<uint32_t*>(q + row * (quant >> 1) + c * 4) = packed;
-        if ((c & 3) == 0) scale[row * (quant >> 5) + (c >> 2)] = (uint8_t)(sc >> 23);
+        int64_t b = 0, o = row;
+        if (!one_batch) { b = row / outer; o = row - b * outer; }
+        const uint4* src = reinterpret_cast<const uint4*>(x + b * sx_batch + o * sx_outer + c * 32);
+#pragma unroll
+        for (int k = 0; k < VPG; ++k) raw[u][k] = src[k];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < GROUPS_UNROLL; ++u) {
+      if (live[u]) {
+        uint32_t sc;
+        const uint4 codes = quantise_raw<T, VPG>(raw[u], mode, sc);
+        const int64_t row = cur[u].row, c = cur[u].c;
+        *reinterpret_cast<uint4*>(q + row * (quant >> 1) + c * 16) = codes;
+        scale[row * groups_per_row + c] = (uint8_t)(sc >> 23);
       }
       cur[u].next();
     }
+  }
+}
+
+// ---- quantised axis strided, the other axis contiguous (axis 0 of a row-major matrix): a thread owns the 32-groups of
+// two neighbouring columns, so that a warp load covers 128 (bf16 / fp16) contiguous bytes; each column's codes are 16
+// contiguous bytes of the output.
+template <typename T>
+__global__ void __launch_bounds__(128) downcast_cols2_kernel(const T* __restrict__ x, int64_t batch, int64_t outer,
+                                                             int64_t quant, int64_t sx_batch, int64_t sx_quant,
+                                                             uint8_t* __restrict__ q, uint8_t* __restrict__ scale, int mode) {
+  const int64_t groups = quant >> 5;
+  const int64_t pairs = outer >> 1;
+  const int64_t total = batch * groups * pairs;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t op = i % pairs;
+    const int64_t t = i / pairs;
+    const int64_t g = t % groups;
+    const int64_t b = t / groups;
+    const T* src = x + b * sx_batch + g * 32 * sx_quant + op * 2;
+    float v0[32], v1[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if constexpr (sizeof(T) == 2) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + j * sx_quant);
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          v0[j] = __uint_as_float(w << 16);
+          v1[j] = __uint_as_float(w & 0xFFFF0000u);
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+          v0[j] = f.x;
+          v1[j] = f.y;
+        }
+      } else {
+        const float2 f = *reinterpret_cast<const float2*>(src + j * sx_quant);
+        v0[j] = f.x;
+        v1[j] = f.y;
+      }
+    }
+    uint32_t s0, s1;
+    const uint4 c0 = quantise_group(v0, mode, s0), c1 = quantise_group(v1, mode, s1);
+    const int64_t row = b * outer + op * 2;
+    *reinterpret_cast<uint4*>(q + row * (quant >> 1) + g * 16) = c0;
+    *reinterpret_cast<uint4*>(q + (row + 1) * (quant >> 1) + g * 16) = c1;
+    scale[row * groups + g] = (uint8_t)(s0 >> 23);
+    scale[(row + 1) * groups + g] = (uint8_t)(s1 >> 23);
   }
 }
 
@@ -206,6 +319,7 @@ __device__ __forceinline__ uint4 upcast8_bf16(uint32_t w, uint32_t sb) {
                     __byte_perm(r[2], r[3], 0x7632));
 }
 
+constexpr int ROWS_UNROLL = 4;
 // contiguous output: thread owns 8 elements (4 input bytes) of each of ROWS_UNROLL chunks per iteration
 template <typename T>
 __global__ void __launch_bounds__(256) upcast_rows_kernel(const uint8_t* __restrict__ q,
@@ -308,10 +422,21 @@ extern "C" __attribute__((visibility("default"))) int moe_downcast_mxfp4(const v
     const int64_t align = 16 / (int64_t)sizeof(T);
     const bool rows_ok = sx_quant == 1 && ((uintptr_t)x % 16 == 0) && (sx_outer % align == 0) &&
                          (sx_batch % align == 0) && ((uintptr_t)q % 4 == 0);
-    if (rows_ok) {
-      const int64_t total = batch * outer * (quant >> 3);
-      downcast_rows_kernel<T><<<grid_for(total, ROWS_UNROLL * 256), 256, 0, st>>>((const T*)x, batch * outer, quant, outer, sx_batch,
-                                                                    sx_outer, q, scale, rounding_mode);
+    const int64_t align2 = 2;                                         // two columns per thread: 4- or 8-byte loads
+    const bool cols2_ok = sx_outer == 1 && sx_quant != 1 && outer % 2 == 0 && ((uintptr_t)x % (2 * sizeof(T)) == 0) &&
+                          (sx_quant % align2 == 0) && (sx_batch % align2 == 0) && ((uintptr_t)q % 16 == 0);
+    if (rows_ok && (uintptr_t)q % 16 == 0) {
+      const int64_t total = batch * outer * (quant >> 5);
+      if (total + (int64_t)GROUPS_UNROLL * 256 * moe_sm_count() * 16 < 2147483647LL)       // 32-bit row / group counters
+        downcast_rows_kernel<T, int32_t><<<grid_for(total, GROUPS_UNROLL * 256), 256, 0, st>>>(
+            (const T*)x, batch * outer, quant, outer, sx_batch, sx_outer, q, scale, rounding_mode);
+      else
+        downcast_rows_kernel<T, int64_t><<<grid_for(total, GROUPS_UNROLL * 256), 256, 0, st>>>(
+            (const T*)x, batch * outer, quant, outer, sx_batch, sx_outer, q, scale, rounding_mode);
+    } else if (cols2_ok) {
+      const int64_t total = batch * (outer >> 1) * (quant >> 5);
+      downcast_cols2_kernel<T><<<grid_for(total, 128), 128, 0, st>>>((const T*)x, batch, outer, quant, sx_batch, sx_quant, q,
+                                                                     scale, rounding_mode);
     } else {
       MOE_CHECK_ARG((uintptr_t)q % 16 == 0, "moe_downcast_mxfp4: q must be 16-byte aligned");
       const int64_t total = batch * outer * (quant >> 5);
