@@ -500,8 +500,9 @@ def sweep_20b_record(lw20, dev, expert_bias, peaks):
 
 def micro_record(dev, peaks, steps=5):
     """Standalone routing / MXFP4 quantiser timings against the measured copy bandwidth.  Every timed call runs
-    after a 512 MB write that evicts its inputs from L2; the time is the median of per-call CUDA event pairs.  Bytes
-    are algorithmic: what the operator must read and write once."""
+    after a 512 MB write that evicts its inputs from L2 and a short spin kernel that lets the host enqueue the call
+    ahead of the GPU; the time is the median of per-call CUDA event pairs.  Bytes are algorithmic: what the operator must
+    read and write once."""
     import triton_b200 as tb
     from triton_b200.numerics_details.mxfp import downcast_to_mxfp, upcast_from_mxfp
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
@@ -513,6 +514,7 @@ def micro_record(dev, peaks, steps=5):
         ts, launches = [], 0
         for _ in range(steps):
             flush.fill_(1)
+            torch.cuda._sleep(400000)          # the host enqueues the call while the GPU spins: no launch gap in the span
             l0 = launch_count()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

@@ -84,6 +84,20 @@ int moe_bitmatrix_metadata(const int16_t* indx, int64_t ld_indx, int64_t T, int 
                            const int32_t* n_rows_dev, int32_t* col_sum, int32_t* col_sorted,
                            int32_t* row_sorted, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The whole routing step of a layer in three launches: moe_topk_fwd + moe_bitmatrix_metadata + moe_ragged_metadata
+ * (topk.py:106-141 -> tensor.py:202-209 -> ragged_tensor.py:183-210 of the reference, what its test helper `routing`
+ * composes, tests/test_distributed.py:203-210) with the expert histogram taken in the top-k pass and the ragged
+ * metadata computed by the block that scans the histogram.  Every one of the T rows is valid (no device-side row
+ * bound, no provided indices); n_expts <= 256, otherwise MOE_ERR_UNSUPPORTED and the caller uses the separate entry
+ * points.  Outputs and the workspace (moe_bitmatrix_metadata_workspace bytes) as for those entry points.           */
+int moe_route(const void* logits, int dtype, int64_t T, int E, int k, int apply_softmax, int64_t ld_logits,
+              void* vals, int64_t ld_vals, int16_t* indx, int64_t ld_indx,
+              uint32_t* bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,
+              int32_t* col_sum, int32_t* col_sorted, int32_t* row_sorted,
+              int32_t* slice_offs, int32_t* block_offs, int64_t ld_block_offs,
+              int32_t* block_sched, int64_t ld_sched, int64_t n_sched,
+              void* workspace, size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  The same computation as moe_bitmatrix_metadata for callers that cannot
  * supply a workspace because they cannot allocate device memory when they call: a serving process that gave
  * all device memory to its own pools at start-up, or a latency-critical section where cudaMalloc, which

@@ -149,3 +149,36 @@ def test_routing_full_size(device):
     assert torch.equal(ragged.slice_offs.cpu(), so) and torch.equal(ragged.block_offs_data.cpu(), bo)
     assert torch.equal(ragged.block_schedule_data.cpu(), bs)
     assert torch.equal(gather_idx.cpu(), col // 4) and torch.equal(scatter_idx.cpu(), col)
+
+
+@pytest.mark.parametrize("T, E, k", [(1, 128, 4), (7, 13, 2), (255, 32, 4), (256, 128, 4), (257, 200, 8), (4099, 256, 4),
+                                     (16384, 128, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_route_equals_separate_entry_points(T, E, k, dtype, device, monkeypatch):
+    """`route` (three launches: top-k + histogram, scan + ragged metadata, rank) returns exactly what the five-launch
+    composition topk -> make_bitmatrix_metadata -> make_ragged_tensor_metadata returns, and what the oracle computes."""
+    from triton_b200 import routing as routing_mod
+    from triton_b200.routing import route
+    monkeypatch.setattr(routing_mod, "FUSED_MAX_TOKENS", 1 << 30)      # the fused form at every size
+    torch.manual_seed(T * 131 + E)
+    logits = torch.randn(T, E, device=device).to(dtype)
+    if T > 2:
+        logits[1] = logits[0]                      # equal rows and ties inside a row
+        logits[2, : E // 2] = logits[2, E // 2: 2 * (E // 2)]
+    ragged, sp = route(logits, k)
+    sp2 = topk(logits, k)
+    md, md2 = sp.mask_metadata, sp2.mask_metadata
+    rg2 = make_ragged_tensor_metadata(md2.col_sum, T * k)
+    assert torch.equal(sp.indx, sp2.indx) and torch.equal(sp.vals, sp2.vals)
+    assert torch.equal(sp.mask.storage.data[:T], sp2.mask.storage.data[:T])
+    assert torch.equal(md.col_sum, md2.col_sum) and torch.equal(md.col_sorted_indx, md2.col_sorted_indx)
+    assert torch.equal(md.row_sorted_indx, md2.row_sorted_indx)
+    assert torch.equal(ragged.slice_offs, rg2.slice_offs) and torch.equal(ragged.block_offs_data, rg2.block_offs_data)
+    assert torch.equal(ragged.block_schedule_data, rg2.block_schedule_data)
+    # and the oracle
+    vals_o, indx_o, _ = oracle.topk_oracle(logits.cpu(), k, apply_softmax=True)
+    assert torch.equal(sp.indx.cpu().long(), indx_o.long())
+    col_sum_o, col_sorted_o, row_sorted_o = oracle.bitmatrix_metadata_oracle(indx_o, E)
+    assert torch.equal(md.col_sum.cpu().long(), col_sum_o.long())
+    assert torch.equal(md.col_sorted_indx.cpu().long(), col_sorted_o.long())
+    assert torch.equal(md.row_sorted_indx.cpu().long(), row_sorted_o.long())

@@ -63,6 +63,8 @@ PROTOTYPES = {
     "moe_topk_fwd": (i32, [vp, i32, i64, i32, i32, i32, i64, vp, i64, vp, i64, vp, i64, i64, vp, i32, vp]),
     "moe_bitmatrix_metadata_workspace": (sz, [i64, i32, i32]),
     "moe_bitmatrix_metadata": (i32, [vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]),
+    "moe_route": (i32, [vp, i32, i64, i32, i32, i32, i64, vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, vp, vp, i64, vp, i64,
+                        i64, vp, sz, vp]),
     "moe_bitmatrix_metadata_noalloc_capacity": (sz, []),
     "moe_bitmatrix_metadata_noalloc": (i32, [vp, i64, i64, i32, i32, vp, vp, vp, vp, vp]),
     "moe_ragged_metadata": (i32, [vp, i32, vp, vp, i64, vp, i64, i64, vp]),

@@ -462,6 +462,227 @@ extern "C" __attribute__((visibility("default"))) int moe_ragged_metadata_remap(
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// moe_route: the whole routing step in three launches (the standalone entry points above take five).
+//   A  route_topk_hist_kernel   top-k + softmax + bitmatrix row of every token, and the expert histogram of each block
+//                               of 256 tokens (partial[blk][e]) in the same pass over the logits;
+//   B  route_scan_ragged_kernel one block: exclusive scan of partial over the blocks, the expert totals (col_sum), their
+//                               exclusive scan (col_offs), then slice_offs / block_offs / block schedules of the ragged
+//                               metadata, which depend on col_sum only;
+//   C  bm_rank_kernel           positions of the entries (unchanged).
+// Every token row is valid in this form (no device-side row bound, no provided indices), so each (token, slot) entry
+// receives a position and the index arrays need no -1 pre-fill.
+namespace {
+
+constexpr int kRouteWarps = 32;                 // warps per block of kernel A: 8 token rows each
+constexpr int kRowsPerWarp = kTokPerBlock / kRouteWarps;
+
+// One warp per token row, rows of up to 256 experts held as order-preserving keys in registers.  A pick is two warp
+// reductions (redux.sync): the largest value key, then the smallest expert index among the lanes that hold it.
+template <typename T>
+__global__ void __launch_bounds__(kRouteWarps * 32) route_topk_hist_kernel(
+    const T* __restrict__ logits, int64_t ld_logits, int64_t T_rows, int E, int k, int apply_softmax,
+    T* __restrict__ vals, int64_t ld_vals, int16_t* __restrict__ indx, int64_t ld_indx,
+    uint32_t* __restrict__ bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word, int32_t* __restrict__ partial) {
+  extern __shared__ int32_t s_hist[];                     // [E]
+  __shared__ float s_val[kRouteWarps][kMaxTopK];
+  __shared__ int s_idx[kRouteWarps][kMaxTopK];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  constexpr int kRegKeys = 8;
+  const int64_t row0 = (int64_t)blockIdx.x * kTokPerBlock + warp * kRowsPerWarp;
+  const int words = (E + 31) >> 5;
+  // the next row's logits are loaded before this row's picks start
+  uint32_t nxt[kRegKeys];
+  auto load_row = [&](int64_t row) {
+#pragma unroll
+    for (int u = 0; u < kRegKeys; ++u) {
+      const int e = lane + 32 * u;
+      nxt[u] = (row < T_rows && e < E) ? float_key(to_f32<T>(logits[row * ld_logits + e])) : 0u;
+    }
+  };
+  load_row(row0);
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    const int64_t row = row0 + i;
+    if (row >= T_rows) break;                              // warp-uniform
+    uint32_t key[kRegKeys];
+#pragma unroll
+    for (int u = 0; u < kRegKeys; ++u) key[u] = nxt[u];
+    if (i + 1 < kRowsPerWarp) load_row(row + 1);
+    uint32_t alive = 0;
+#pragma unroll
+    for (int u = 0; u < kRegKeys; ++u)
+      if (lane + 32 * u < E) alive |= 1u << u;
+    for (int j = 0; j < k; ++j) {
+      uint32_t bk = 0;
+      int bu = -1;
+#pragma unroll
+      for (int u = 0; u < kRegKeys; ++u)
+        if (((alive >> u) & 1u) && (bu < 0 || key[u] > bk)) { bk = key[u]; bu = u; }
+      const uint32_t m = __reduce_max_sync(0xFFFFFFFFu, bu >= 0 ? bk : 0u);
+      const uint32_t cand = (bu >= 0 && bk == m) ? (uint32_t)(lane + 32 * bu) : 0x7FFFFFFFu;
+      const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, cand);
+      if ((int)(win & 31u) == lane && win != 0x7FFFFFFFu) alive &= ~(1u << (win >> 5));
+      if (lane == 0) {
+        s_idx[warp][j] = (int)win;
+        s_val[warp][j] = key_float(m);
+      }
+    }
+    __syncwarp();
+    if (apply_softmax) {
+      float mx = -INFINITY;
+      for (int j = 0; j < k; ++j) mx = fmaxf(mx, s_val[warp][j]);
+      float sum = 0.0f;
+      for (int j = 0; j < k; ++j) sum += expf(s_val[warp][j] - mx);
+      for (int j = lane; j < k; j += 32) vals[row * ld_vals + j] = from_f32<T>(__fdiv_rn(expf(s_val[warp][j] - mx), sum));
+    } else {
+      for (int j = lane; j < k; j += 32) vals[row * ld_vals + j] = from_f32<T>(s_val[warp][j]);
+    }
+    for (int j = lane; j < k; j += 32) {
+      const int e = s_idx[warp][j];
+      indx[row * ld_indx + j] = (int16_t)e;
+      atomicAdd(&s_hist[e], 1);
+    }
+    for (int w = lane; w < words; w += 32) {
+      uint32_t bits = 0;
+      for (int j = 0; j < k; ++j) {
+        const int e = s_idx[warp][j];
+        if ((e >> 5) == w) bits |= 1u << (e & 31);
+      }
+      bitmatrix[row * bm_stride_row + (int64_t)w * bm_stride_word] = bits;
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) partial[(int64_t)blockIdx.x * E + e] = s_hist[e];
+}
+
+// One block of 1024 threads.  n_experts <= 1024.
+__global__ void __launch_bounds__(1024) route_scan_ragged_kernel(int32_t* __restrict__ partial, int64_t n_blocks, int E,
+                                                                 int32_t* __restrict__ col_sum, int32_t* __restrict__ col_offs,
+                                                                 int32_t* __restrict__ slice_offs, int32_t* __restrict__ block_offs,
+                                                                 int64_t ld_block_offs, int32_t* __restrict__ block_sched,
+                                                                 int64_t ld_sched, int64_t n_sched) {
+  extern __shared__ int32_t s_mem[];             // [1024] segment sums, then [E + 1] sizes, [E + 1] scan input, [E + 1] offsets
+  __shared__ int32_t s_warp[33];
+  int32_t* s_seg = s_mem;
+  int32_t* s_size = s_mem + 1024;
+  int32_t* s_nb = s_size + (E + 1);
+  int32_t* s_offs = s_nb + (E + 1);
+  // ---- 1. exclusive scan of partial[.][e] over the blocks of tokens, by S segments of blocks per expert -------------
+  int Ep = 1;
+  while (Ep < E) Ep <<= 1;
+  const int S = 1024 / Ep;                        // threads (segments) per expert
+  const int e = threadIdx.x % Ep, seg = threadIdx.x / Ep;
+  const int64_t per = (n_blocks + S - 1) / S;
+  const int64_t b_lo = min((int64_t)seg * per, n_blocks), b_hi = min(b_lo + per, n_blocks);
+  int sum = 0;
+  if (e < E)
+    for (int64_t b0 = b_lo; b0 < b_hi; b0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = b0 + u < b_hi ? partial[(b0 + u) * E + e] : 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) sum += v[u];
+    }
+  s_seg[threadIdx.x] = sum;
+  __syncthreads();
+  int run = 0, total = 0;
+  for (int s2 = 0; s2 < S; ++s2) {
+    const int v = s_seg[s2 * Ep + e];
+    if (s2 < seg) run += v;
+    total += v;
+  }
+  if (e < E) {
+    for (int64_t b0 = b_lo; b0 < b_hi; b0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = b0 + u < b_hi ? partial[(b0 + u) * E + e] : 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (b0 + u < b_hi) partial[(b0 + u) * E + e] = run;
+        run += v[u];
+      }
+    }
+    if (seg == 0) {
+      col_sum[e] = total;
+      s_size[e] = total;
+    }
+  }
+  if (threadIdx.x == 0) s_size[E] = 0;
+  __syncthreads();
+  // ---- 2. expert offsets, then the ragged metadata: row 0 = slice_offs (= col_offs), rows 1..4 = block sizes 16..128 --
+  for (int row = 0; row < 5; ++row) {
+    const int log2bs = row == 0 ? 0 : row + 3;
+    for (int i = threadIdx.x; i <= E; i += blockDim.x)
+      s_nb[i] = (i < E) ? (int32_t)(((int64_t)s_size[i] + ((1 << log2bs) - 1)) >> log2bs) : 0;
+    __syncthreads();
+    block_exclusive_scan(s_nb, s_offs, E + 1, s_warp);
+    __syncthreads();
+    int32_t* dst = row == 0 ? slice_offs : block_offs + (int64_t)(row - 1) * ld_block_offs;
+    for (int i = threadIdx.x; i <= E; i += blockDim.x) {
+      dst[i] = s_offs[i];
+      if (row == 0 && i < E) col_offs[i] = s_offs[i];
+    }
+    if (row > 0) {
+      const int32_t tot = s_offs[E];
+      int32_t* sched = block_sched + (int64_t)(row - 1) * ld_sched;
+      for (int64_t p = threadIdx.x; p < n_sched; p += blockDim.x) {
+        int32_t v = -1;
+        if (p < tot) {
+          int lo = 0, hi = E;  // largest e with offs[e] <= p
+          while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_offs[mid] <= p) lo = mid; else hi = mid;
+          }
+          v = (int32_t)(((uint32_t)(p - s_offs[lo]) << 16) | (uint32_t)lo);
+        }
+        sched[p] = v;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int moe_route(
+    const void* logits, int dtype, int64_t T, int E, int k, int apply_softmax, int64_t ld_logits, void* vals, int64_t ld_vals,
+    int16_t* indx, int64_t ld_indx, uint32_t* bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word, int32_t* col_sum,
+    int32_t* col_sorted, int32_t* row_sorted, int32_t* slice_offs, int32_t* block_offs, int64_t ld_block_offs,
+    int32_t* block_sched, int64_t ld_sched, int64_t n_sched, void* workspace, size_t workspace_bytes, void* stream) {
+  MOE_CHECK_ARG(T > 0 && E > 0 && k > 0 && k <= kMaxTopK && k <= E, "moe_route: bad extents T=%lld E=%d k=%d", (long long)T, E, k);
+  if (E > 256) {
+    moe_set_error("moe_route: the fused routing handles up to 256 experts (got %d); use the separate entry points", E);
+    return MOE_ERR_UNSUPPORTED;
+  }
+  MOE_CHECK_ARG(logits && vals && indx && bitmatrix && col_sum && col_sorted && row_sorted && slice_offs && block_offs &&
+                    (block_sched || n_sched == 0) && workspace,
+                "moe_route: NULL pointer");
+  MOE_CHECK_ARG(ld_block_offs >= E + 1 && ld_sched >= n_sched, "moe_route: leading dimensions too small");
+  MOE_CHECK_ARG(workspace_bytes >= moe_bitmatrix_metadata_workspace(T, E, k), "moe_route: workspace too small (%zu < %zu)",
+                workspace_bytes, moe_bitmatrix_metadata_workspace(T, E, k));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t nb = cdiv64(T, kTokPerBlock);
+  int32_t* partial = (int32_t*)workspace;
+  int32_t* col_offs = partial + nb * E;
+  MOE_DISPATCH_FLOAT(dtype, Tv, {
+    route_topk_hist_kernel<Tv><<<(int)nb, kRouteWarps * 32, (size_t)E * sizeof(int32_t), st>>>(
+        (const Tv*)logits, ld_logits, T, E, k, apply_softmax, (Tv*)vals, ld_vals, indx, ld_indx, bitmatrix, bm_stride_row,
+        bm_stride_word, partial);
+  });
+  MOE_CHECK_LAUNCH();
+  const size_t smem_b = (size_t)(1024 + 3 * (E + 1)) * sizeof(int32_t);
+  route_scan_ragged_kernel<<<1, 1024, smem_b, st>>>(partial, nb, E, col_sum, col_offs, slice_offs, block_offs, ld_block_offs,
+                                                    block_sched, ld_sched, n_sched);
+  MOE_CHECK_LAUNCH();
+  const size_t smem_rank = (size_t)8 * E * sizeof(int32_t);
+  bm_rank_kernel<<<(int)nb, 256, smem_rank, st>>>(indx, ld_indx, T, E, k, nullptr, partial, col_offs, col_sorted, row_sorted);
+  MOE_CHECK_LAUNCH();
+  return MOE_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // moe_bitmatrix_metadata_noalloc: the same histogram + expert-major sort for hosts that cannot give this
 // library a scratch buffer because they cannot allocate one at that point -- a serving process that handed
 // all device memory to its own pools at start-up, or a latency-critical section in which cudaMalloc (which

@@ -13,7 +13,7 @@ import torch
 from .matmul import FusedActivation, PrecisionConfig, matmul
 from .numerics_details.mxfp import downcast_to_mxfp
 from .reduce import reduce
-from .routing import routing
+from .routing import route, routing  # noqa: F401
 from .specialize import FnSpecs
 from .swiglu import swiglu_fn
 from .tensor import (FP4, Tensor, convert_layout, make_ragged_tensor_metadata, remap_ragged_tensor_metadata,
@@ -94,10 +94,9 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     """x [T, d_model] bf16, logits [T, E] -> [T, d_model]: sum over the k selected experts of
     softmax-weight * (SwiGLU(x W1 + b1) W2 + b2)."""
     T = x.shape[0]
-    sparse = topk(logits, k, apply_softmax=True)
+    ragged, sparse = route(logits, k, apply_softmax=True)
     md = sparse.mask_metadata
     n = T * k
-    ragged = make_ragged_tensor_metadata(md.col_sum, n)
     scatter_idx = md.col_sorted_indx                                    # sorted position -> flat (token, slot) row
     # token row and routing weight of every expert-sorted position, by one kernel (padding positions read no row)
     from . import _lib

@@ -99,9 +99,11 @@ class SparseMatrix:
     indx: torch.Tensor
     vals: torch.Tensor
     mask: Tensor
+    mask_metadata: BitmatrixMetadata | None = None      # computed here unless the producer already has it
 
     def __post_init__(self):
-        self.mask_metadata = make_bitmatrix_metadata(self.indx, self.mask)
+        if self.mask_metadata is None:
+            self.mask_metadata = make_bitmatrix_metadata(self.indx, self.mask)
 
 
 def dtype_to_torch_dtype(dtype) -> torch.dtype:
