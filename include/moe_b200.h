@@ -228,6 +228,14 @@ typedef struct {
 int moe_grouped_gemm(const MoeGemmArgs* args_host, void* stream);
 size_t moe_gemm_mx_workspace_bytes(const MoeGemmArgs* args_host);
 
+/* Tensor-pipe roof of one MMA kind on this device, for the benchmark's roofline: one CTA per SM issues `iters` x 4
+ * back-to-back tcgen05.mma (M 128, N 256) over operand tiles resident in shared memory.  kind 0: bf16 (kind::f16),
+ * 1: e4m3 x e4m3 (kind::f8f6f4), 2: padded e2m1 x e4m3 with e8m0 block scales (kind::mxf8f6f4), 3: packed e2m1 x e2m1
+ * with block scales (kind::mxf4).  The caller times the call with events; *flop_out receives the FLOPs it issued.
+ * `status` (optional device word) is set if the final wait expires.  Stands in for the peak tables the reference
+ * quotes (roofline.py; tutorials/gluon/11-tcgen05-mma-scaled.py:1530-1535).                                       */
+int moe_tensor_roof(int kind, int iters, double* flop_out_host, int32_t* status, void* stream);
+
 /* ---- expert-parallel row movement ------------------------------------------------------------------
  * Local halves of convert_dp_to_ep / convert_ep_to_dp (distributed.py:176-211, 256-283).  Two forms of the
  * exchange use them: kernels that pull rows straight from peer-mapped buffers of the other ranks

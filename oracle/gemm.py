@@ -101,7 +101,7 @@ def moe_layer_oracle(x, logits, w1, b1, w2, b2, k, alpha, limit, fuse_activation
     return reduce_oracle(y.view(T, k, -1), dim=1)
 
 
-def moe_layer_tokens_oracle(x_rows, logits_rows, expert_weights, k, alpha, limit):
+def moe_layer_tokens_oracle(x_rows, logits_rows, expert_weights, k, alpha, limit, h_dtype=None, out_dtype=None):
     """The layer of ``moe_layer_oracle`` for a few token rows of a large problem, without materialising every
     expert: ``expert_weights(e) -> (w1 [K, 2F], b1 [2F], w2 [F, K], b2 [K])`` returns the dequantised weights of
     expert ``e`` (float tensors) and is called once per expert the rows are routed to.
@@ -109,10 +109,14 @@ def moe_layer_tokens_oracle(x_rows, logits_rows, expert_weights, k, alpha, limit
     Same steps and roundings as ``moe_layer_oracle``: top-k + softmax over the selected logits (topk.py:144-185),
     fc1 + bias in fp32 rounded to the activation dtype, SwiGLU (swiglu.py:89-100) rounded to the activation
     dtype, fc2 + bias times the routing weight rounded to the activation dtype (matmul.py:891-927), then the
-    k-way sum in fp32 rounded once (reduce.py:1181-1214)."""
+    k-way sum in fp32 rounded once (reduce.py:1181-1214).
+
+    With ``h_dtype`` (e.g. ``torch.float8_e4m3fn``: e4m3 activations between the two GEMMs, the reference's fp8 mode) the
+    SwiGLU sees the fp32 accumulator and its result is rounded to ``h_dtype``; ``x_rows`` may then be any float dtype
+    holding the (already quantised) inputs and ``out_dtype`` names the dtype of fc2's rows."""
     T = x_rows.shape[0]
     vals, indx, _ = topk_oracle(logits_rows, k, apply_softmax=True)
-    dt = x_rows.dtype
+    dt = out_dtype or x_rows.dtype
     y = torch.zeros((T, k, x_rows.shape[1]), dtype=dt)
     cache = {}
     for t in range(T):
@@ -121,7 +125,10 @@ def moe_layer_tokens_oracle(x_rows, logits_rows, expert_weights, k, alpha, limit
             if e not in cache:
                 cache[e] = [w.float() for w in expert_weights(e)]
             w1, b1, w2, b2 = cache[e]
-            h = (x_rows[t].float() @ w1 + b1).to(dt)
-            h = swiglu_oracle(h.float(), alpha, limit).to(dt)
+            if h_dtype is None:
+                h = (x_rows[t].float() @ w1 + b1).to(dt)
+                h = swiglu_oracle(h.float(), alpha, limit).to(dt)
+            else:
+                h = swiglu_oracle(x_rows[t].float() @ w1 + b1, alpha, limit).to(h_dtype)
             y[t, j] = ((h.float() @ w2 + b2) * vals[t, j].float()).to(dt)
     return reduce_oracle(y, dim=1)

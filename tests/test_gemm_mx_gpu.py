@@ -181,3 +181,50 @@ def test_block_scaled_wide_dynamic_range_rows(device):
     y = run_mx(x, wq, ws, sizes, device, out_dtype=torch.float32)
     ref = oracle.matmul_oracle(x.float(), wdeq, None, sizes, out_dtype=torch.float32)
     assert oracle.rel_l2(ref, y) < 1e-2
+
+
+def test_block_scaled_e4m3_output(device):
+    """fc1 of the fp8 mode: e4m3 rows in, SwiGLU, e4m3 rows out (saturating round to nearest)."""
+    g = torch.Generator().manual_seed(21)
+    E, K, N = 3, 512, 512
+    sizes = torch.tensor([40, 0, 77], dtype=torch.int32)
+    M = int(sizes.sum())
+    wq, ws, wdeq = quantised_weights(E, K, N, g, w_std=0.05)
+    x8 = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    bias = torch.randn(E, N, generator=g) * 0.1
+    y = run_mx(x8, wq, ws, sizes, device, bias=bias, act=(1.702, 7.0), out_dtype=torch.float8_e4m3fn)
+    assert y.dtype == torch.float8_e4m3fn
+    ref32 = oracle.swiglu_oracle(oracle.matmul_oracle(x8.float(), wdeq, bias, sizes, out_dtype=torch.float32), 1.702, 7.0)
+    ref8 = ref32.to(torch.float8_e4m3fn)
+    # equal up to one e4m3 step where the fp32 sums differ in their last bits right at a rounding boundary
+    diff = (y.float() - ref8.float()).abs()
+    step = ref8.float().abs().clamp_min(2.0 ** -6) * 0.125
+    assert (diff <= step).all()
+    assert (diff > 0).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("tokens", [64, 2048])
+def test_layer_with_e4m3_activations_against_oracle(tokens, device):
+    """The layer in fp8 mode (e4m3 tokens in, e4m3 between the GEMMs) against the oracle fed the same quantised rows."""
+    from triton_b200.moe import moe_layer_forward
+    from triton_b200.testing import make_synthetic_layer
+    E, k = 16, 4
+    lw = make_synthetic_layer(E, 2880, 2880, device, seed=5, keep_canonical=True, block_scaled=True)
+    g = torch.Generator(device=device).manual_seed(tokens)
+    x8 = torch.randn(tokens, 2880, device=device, generator=g).to(torch.float8_e4m3fn)
+    logits = torch.randn(tokens, E, device=device, generator=g)
+    z = moe_layer_forward(x8, logits, lw, k)
+    tb.matmul_check_status()
+    assert z.dtype == torch.bfloat16
+    rows = torch.linspace(0, tokens - 1, 6).round().long().unique()
+
+    def expert_weights(e):
+        w1 = oracle.dequant_weight_oracle(lw.w1_q[e:e + 1].cpu(), lw.w1_s[e:e + 1].cpu())[0]
+        w2 = oracle.dequant_weight_oracle(lw.w2_q[e:e + 1].cpu(), lw.w2_s[e:e + 1].cpu())[0]
+        return w1, lw.b1[e].cpu(), w2, lw.b2[e].cpu()
+
+    ref = oracle.moe_layer_tokens_oracle(x8[rows.to(device)].cpu().float(), logits[rows.to(device)].cpu(), expert_weights, k,
+                                         1.702, 7.0, h_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16)
+    got = z[rows.to(device)].cpu()
+    oracle.assert_close_oracle(ref, got, maxtol=MAXTOL_MX4, rmstol=None, what="fp8 layer")
+    assert oracle.rel_l2(ref, got) < 1e-2

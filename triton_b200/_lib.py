@@ -80,6 +80,7 @@ PROTOTYPES = {
     "moe_weight_layout_from_b200mx": (i32, [vp, vp, i32, i32, i32, vp, vp, vp]),
     "moe_grouped_gemm": (i32, [C.POINTER(MoeGemmArgs), vp]),
     "moe_gemm_mx_workspace_bytes": (sz, [C.POINTER(MoeGemmArgs)]),
+    "moe_tensor_roof": (i32, [i32, i32, C.POINTER(C.c_double), vp, vp]),
     "moe_ep_keys": (i32, [vp, vp, vp, i64, i32, i32, vp, vp]),
     "moe_ep_pull_index": (i32, [vp, vp, vp, vp, i64, i32, vp, vp, vp]),
     "moe_ep_combine_index": (i32, [vp, vp, vp, i64, i64, i64, vp, vp]),

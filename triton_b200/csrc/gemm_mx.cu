@@ -29,6 +29,13 @@
 #include "gemm_tc_common.cuh"
 #include <cuda_fp8.h>
 
+// e4m3 output (the next GEMM's activations): round to nearest, saturating at +-448 like the MMA's own conversions
+template <> __device__ __forceinline__ __nv_fp8_e4m3 from_f32<__nv_fp8_e4m3>(float v) {
+  __nv_fp8_e4m3 r;
+  r.__x = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+  return r;
+}
+
 namespace {
 
 constexpr int MX_THREADS = 320;               // warp 0 producer, 1 MMA, 2-5 epilogue, 6-9 scale loaders
@@ -583,7 +590,7 @@ int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const CU
 bool moe_gemm_mx_supported(const MoeGemmArgs& a, const char** why) {
   if (a.w_kind != MOE_W_MX4_B200MX) { *why = "weights are not in the block-scaled B200 layout"; return false; }
   if (a.x_dtype != MOE_BF16 && a.x_dtype != MOE_F8E4M3) { *why = "activations are neither bf16 nor e4m3"; return false; }
-  if (a.y_dtype != MOE_BF16 && a.y_dtype != MOE_F32) { *why = "output is neither bf16 nor fp32"; return false; }
+  if (a.y_dtype != MOE_BF16 && a.y_dtype != MOE_F32 && a.y_dtype != MOE_F8E4M3) { *why = "output is neither bf16, fp32 nor e4m3"; return false; }
   if ((uintptr_t)a.x % 16 != 0 || (a.ld_x * (a.x_dtype == MOE_BF16 ? 2 : 1)) % 16 != 0) {
     *why = "activation rows are not 16-byte aligned"; return false;
   }
@@ -635,6 +642,8 @@ int moe_gemm_mx_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
   CUtensorMap w_map;
   if (int rc = make_w_map(a, pl, &w_map)) return rc;
   const int idle = a.idle_sms > 0 ? a.idle_sms : 0;
+  if (a.y_dtype == MOE_F8E4M3)
+    return pl.mb == 3 ? launch_mx<__nv_fp8_e4m3, 3>(p, q, pl, w_map, idle, st) : launch_mx<__nv_fp8_e4m3, 1>(p, q, pl, w_map, idle, st);
   if (a.y_dtype == MOE_BF16)
     return pl.mb == 3 ? launch_mx<__nv_bfloat16, 3>(p, q, pl, w_map, idle, st) : launch_mx<__nv_bfloat16, 1>(p, q, pl, w_map, idle, st);
   return pl.mb == 3 ? launch_mx<float, 3>(p, q, pl, w_map, idle, st) : launch_mx<float, 1>(p, q, pl, w_map, idle, st);

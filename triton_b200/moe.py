@@ -92,7 +92,10 @@ def _activation(lw):
 
 def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     """x [T, d_model] bf16, logits [T, E] -> [T, d_model]: sum over the k selected experts of
-    softmax-weight * (SwiGLU(x W1 + b1) W2 + b2)."""
+    softmax-weight * (SwiGLU(x W1 + b1) W2 + b2).
+
+    e4m3 activations (`x.dtype == torch.float8_e4m3fn`, the reference's fp8 mode: bench/bench_mlp.py `x_dtype="fp8"`) run
+    both GEMMs on the block-scaled kernel at every size: fc1 writes e4m3 rows, fc2 reads them and writes bf16."""
     T = x.shape[0]
     ragged, sparse = route(logits, k, apply_softmax=True)
     md = sparse.mask_metadata
@@ -106,9 +109,15 @@ def moe_layer_forward(x, logits, lw: MoeLayerWeights, k: int, gemm_timer=None):
     _lib.check(_lib.load().moe_ep_pull_index(_lib.ptr(scatter_idx.reshape(-1)), _lib.ptr(indx16.contiguous()),
                                              _lib.ptr(sparse.vals.contiguous()), _lib.ptr(_all_local(logits.shape[1], x.device)),
                                              n, k, _lib.ptr(gather_idx), _lib.ptr(gammas), _lib.stream()), "moe_ep_pull_index")
-    w1, w1_scale, w2, w2_scale = lw.fc_weights(T * k)
-    pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32)
-    pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32)
+    if x.dtype == torch.float8_e4m3fn:
+        assert lw.w1_bs is not None, "e4m3 activations need the block-scaled copy of the weights"
+        w1, w1_scale, w2, w2_scale = lw.w1_bs, lw.w1_bs_scale, lw.w2_bs, lw.w2_bs_scale
+        pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32, out_dtype=torch.float8_e4m3fn)
+        pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32, out_dtype=torch.bfloat16)
+    else:
+        w1, w1_scale, w2, w2_scale = lw.fc_weights(T * k)
+        pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32)
+        pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32)
     with _span(gemm_timer):
         h = matmul(x, w1, lw.b1, ragged, gather_indx=gather_idx, precision_config=pc1,
                    fused_activation=_activation(lw))
