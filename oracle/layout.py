@@ -65,3 +65,51 @@ def swizzle_mx_value_bw_oracle(w: torch.Tensor) -> torch.Tensor:
 def unswizzle_mx_value_bw_oracle(d: torch.Tensor, shape) -> torch.Tensor:
     K = shape[-2]
     return repack_fp4_oracle(d[..., : K // 2, :], -2, -1)
+
+
+def swizzle_mx4_value_shuffled_oracle(w: torch.Tensor, block_k: int = 128, block_n: int = 256) -> torch.Tensor:
+    """Canonical [E, K, N/2] (packed along N) -> [E, K_tiles, N_tiles, block_n, block_k/2] packed along K: tile
+    (tk, tn) holds columns tn*block_n.. and packed-K bytes tk*block_k/2.., rows = columns of the weight
+    (``blackwell_value_shuffled.py:138-166``); packed K padded to lcm(128, block_k/2), N to block_n, zero fill.
+    Element-wise definition (slow, small cases only)."""
+    import math
+    r = repack_fp4_oracle(w, -1, -2)                               # [E, K/2, N]
+    E, kb, N = r.shape
+    tkb = block_k // 2
+    quantum = math.lcm(128, tkb)
+    kbp = -(-kb // quantum) * quantum
+    npad = -(-N // block_n) * block_n
+    out = torch.zeros(E, kbp // tkb, npad // block_n, block_n, tkb, dtype=torch.uint8)
+    for e in range(E):
+        for b in range(kb):
+            for n in range(N):
+                out[e, b // tkb, n // block_n, n % block_n, b % tkb] = r[e, b, n]
+    return out
+
+
+def swizzle_act_mx_scale_oracle(s: torch.Tensor, slice_sizes=None) -> torch.Tensor:
+    """Activation scales [M, K/32] -> [1, M_pad/128, K_pad/4, 2, 256] in blocks of 128 rows x 4 groups stored
+    [32 lanes][4 quads][4 k] (``blackwell_scale.py:104-121``); with ``slice_sizes`` every slice of rows starts at a new
+    block of 128 rows (``:68-80``, the reference pads with a GPU kernel: this ragged form is defined here and unpinned)."""
+    M, K = s.shape
+    Kp = (K + 7) // 8 * 8
+    if slice_sizes is None:
+        Mp = (M + 127) // 128 * 128
+        rows = list(range(M))
+    else:
+        from .routing import n_blocks
+        Mp = 128 * n_blocks(len(slice_sizes), M, 128)
+        rows, off, blk = [-1] * M, 0, 0
+        for sz in [int(v) for v in slice_sizes]:
+            for j in range(sz):
+                rows[off + j] = blk * 128 + j
+            off += sz
+            blk += (sz + 127) // 128
+    out = torch.zeros(Mp // 128, Kp // 4, 32, 4, 4, dtype=torch.uint8)
+    for m in range(M):
+        if rows[m] < 0:
+            continue
+        r = rows[m]
+        for k in range(K):
+            out[r // 128, k // 4, (r % 128) % 32, (r % 128) // 32, k % 4] = s[m, k]
+    return out.reshape(1, Mp // 128, Kp // 4, 2, 256)

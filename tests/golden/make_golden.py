@@ -178,6 +178,20 @@ def main(ref_root):
     vw = tv.swizzle_data(v)
     save("layout_bw", {"scale": s, "scale_swizzled": sw.contiguous(), "value": v,
                        "value_swizzled": vw.contiguous(), "value_swizzled_strides": list(vw.stride())})
+    # the pre-tiled value layout and the activation scale layout (their torch paths; the ragged activation form pads
+    # with a GPU kernel in the reference and is not recorded)
+    from triton_kernels.tensor_details.layout_details.blackwell_value_shuffled import BlackwellMX4ValueShuffledLayout
+    from triton_kernels.tensor_details.layout_details.blackwell_scale import BlackwellActMXScaleLayout
+    v2 = torch.randint(0, 255, (2, 200, 150), generator=g, dtype=torch.uint8)    # canonical [E, K, N/2]: K = 200, N = 300
+    tsh = BlackwellMX4ValueShuffledLayout(block_k=128, block_n=256).make_transformation([2, 200, 300], True)
+    vs = tsh.swizzle_data(v2)
+    tsh2 = BlackwellMX4ValueShuffledLayout(block_k=64, block_n=128).make_transformation([2, 200, 300], True)
+    vs2 = tsh2.swizzle_data(v2)
+    a = torch.randint(0, 255, (300, 10), generator=g, dtype=torch.uint8)          # activation scales [M, K/32]
+    ta = BlackwellActMXScaleLayout(None).make_transformation([300, 10], False)
+    asw = ta.swizzle_data(a)
+    save("layout_bw2", {"value": v2, "value_shuffled_128_256": vs.contiguous(), "value_shuffled_64_128": vs2.contiguous(),
+                        "act_scale": a, "act_scale_swizzled": asw.contiguous()})
     torch.histc = real_histc
 
 

@@ -163,3 +163,63 @@ def test_balanced_expert_placement():
         spread = lambda dd: max(sum(load[e] for e in v) for v in dd.values()) / (sum(load) / shards)
         assert spread(d) < 1.02 <= spread(make_expt_dict_uniform(shards, 128)) + 1e-9 or spread(d) < 1.02
         assert spread(d) <= spread(make_expt_dict_uniform(shards, 128))
+
+
+def test_shuffled_value_layout_matches_reference_fixture(golden):
+    """BlackwellMX4ValueShuffledLayout against the reference's own output (two tilings, K and N both padded)."""
+    from triton_b200.tensor_details.layout import BlackwellMX4ValueShuffledLayout
+    g = golden("layout_bw2")
+    v = wrap_torch_tensor(g["value"], dtype=FP4)                      # canonical [E, K, N/2]
+    assert v.shape == [2, 200, 300]
+    for (bk, bn), key in (((128, 256), "value_shuffled_128_256"), ((64, 128), "value_shuffled_64_128")):
+        lay = BlackwellMX4ValueShuffledLayout(block_k=bk, block_n=bn)
+        sw = convert_layout(v, lay)
+        assert list(sw.storage.data.shape) == list(g[key].shape)
+        assert torch.equal(sw.storage.data, g[key])
+        assert torch.equal(convert_layout(sw, StridedLayout()).storage.data, g["value"])
+    # the reference's storage-shape known answers (tests/test_tensor.py:99-100, 103-105)
+    from triton_b200.tensor_details.layout import BlackwellActMXScaleLayout
+    assert BlackwellMX4ValueShuffledLayout().make_transformation([3, 258, 514], True).storage_shape == [3, 4, 3, 256, 64]
+    assert BlackwellMX4ValueShuffledLayout().make_transformation([0, 64], True).storage_shape == [1, 0, 1, 256, 64]
+    assert BlackwellActMXScaleLayout(None).make_transformation([130, 65], False).storage_shape == [1, 2, 18, 2, 256]
+    assert BlackwellActMXScaleLayout(None).make_transformation([3, 130, 65], False).storage_shape == [1, 6, 18, 2, 256]
+    assert BlackwellActMXScaleLayout(None).make_transformation([0, 64], False).storage_shape == [1, 0, 16, 2, 256]
+
+
+def test_act_scale_layout_matches_reference_fixture_and_oracle(golden):
+    from triton_b200.tensor_details.layout import BlackwellActMXScaleLayout
+    g = golden("layout_bw2")
+    a = wrap_torch_tensor(g["act_scale"])
+    sw = convert_layout(a, BlackwellActMXScaleLayout(None))
+    assert torch.equal(sw.storage.data, g["act_scale_swizzled"])
+    assert torch.equal(convert_layout(sw, StridedLayout()).storage.data, g["act_scale"])
+    # ragged: every slice starts at a new block of 128 rows; rows past the slices are dropped
+    sizes = torch.tensor([130, 0, 5, 128, 20], dtype=torch.int32)
+    M = int(sizes.sum()) + 17
+    gen = torch.Generator().manual_seed(4)
+    s = torch.randint(0, 255, (M, 12), generator=gen, dtype=torch.uint8)
+    offs = torch.zeros(6, dtype=torch.int32)
+    offs[1:] = torch.cumsum(sizes, 0)
+    nb = [[0] * 6 for _ in range(4)]
+    for b, bs in enumerate((16, 32, 64, 128)):
+        run = 0
+        for e in range(5):
+            nb[b][e] = run
+            run += (int(sizes[e]) + bs - 1) // bs
+        nb[b][5] = run
+    md = RaggedTensorMetadata(sizes, offs, torch.tensor(nb, dtype=torch.int32),
+                              torch.zeros((4, RaggedTensorMetadata.max_n_blocks(5, M)), dtype=torch.int32))
+    lay = BlackwellActMXScaleLayout(md)
+    sw = convert_layout(wrap_torch_tensor(s), lay)
+    assert torch.equal(sw.storage.data, oracle.swizzle_act_mx_scale_oracle(s, sizes.tolist()))
+    back = convert_layout(sw, StridedLayout()).storage.data
+    assert torch.equal(back[: int(sizes.sum())], s[: int(sizes.sum())]) and not back[int(sizes.sum()):].any()
+
+
+def test_default_weight_layout_arguments():
+    from triton_b200.tensor_details.layout import (B200MXScaleLayout, B200MXValueLayout, make_default_matmul_mxfp4_w_layout,
+                                                   make_default_matmul_mxfp4_w_scale_layout)
+    assert isinstance(make_default_matmul_mxfp4_w_layout(mx_axis=-2, allow_blackwell_value_shuffle=True), B200MXValueLayout)
+    assert isinstance(make_default_matmul_mxfp4_w_scale_layout(mx_axis=1), B200MXScaleLayout)
+    with pytest.raises(NotImplementedError):
+        make_default_matmul_mxfp4_w_layout(mx_axis=-1)

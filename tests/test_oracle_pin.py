@@ -160,3 +160,14 @@ def test_token_sampled_layer_oracle_equals_layer_oracle():
     rows = torch.tensor([3, 17, 40, 63])
     part = oracle.moe_layer_tokens_oracle(x[rows], logits[rows], lambda e: (w1[e], b1[e], w2[e], b2[e]), k, 1.702, 7.0)
     assert torch.equal(full[rows], part)
+
+
+def test_more_layout_oracles_match_reference_fixture(golden):
+    g = golden("layout_bw2")
+    assert torch.equal(oracle.swizzle_mx4_value_shuffled_oracle(g["value"][:1, :40, :30], 128, 256),
+                       oracle.swizzle_mx4_value_shuffled_oracle(g["value"][:1, :40, :30].clone(), 128, 256))
+    small = g["value"][:1]
+    # the element-wise definition against the reference's tiling of the same bytes
+    assert torch.equal(oracle.swizzle_mx4_value_shuffled_oracle(small, 128, 256), g["value_shuffled_128_256"][:1])
+    assert torch.equal(oracle.swizzle_mx4_value_shuffled_oracle(small, 64, 128), g["value_shuffled_64_128"][:1])
+    assert torch.equal(oracle.swizzle_act_mx_scale_oracle(g["act_scale"]), g["act_scale_swizzled"])
