@@ -342,3 +342,29 @@ def test_gpt_oss_120b_layer_decode_path_against_oracle(tokens, device):
     lw = make_synthetic_layer(128, 2880, 2880, device, seed=1000, keep_canonical=True, block_scaled=True)
     assert lw.use_block_scaled(tokens * 4)
     _sampled_layer_check(lw, 128, tokens, device, seed=tokens, skew=True, n_sample=min(tokens, 6))
+
+
+def test_weight_file_and_block_checkpoint_reader(tmp_path, device):
+    """A layer saved in its tiled layouts and read back computes the same output bit for bit, and the checkpoint form
+    (blocks [E, N, K/32, 16] + scales [E, N, K/32]) converts to the very same tiles."""
+    from triton_b200.moe import moe_layer_forward
+    from triton_b200.testing import make_synthetic_layer
+    from triton_b200.weights_io import from_block_checkpoint, load_layer_weights, save_layer_weights
+    E, d, ff, k, T = 8, 512, 256, 2, 100
+    lw = make_synthetic_layer(E, d, ff, device, seed=3, keep_canonical=True, block_scaled=True)
+    path = tmp_path / "layer.moeb200w"
+    save_layer_weights(path, lw)
+    back = load_layer_weights(path, device)
+    torch.manual_seed(1)
+    x = torch.randn(T, d, device=device).bfloat16()
+    logits = torch.randn(T, E, device=device)
+    z0, z1 = moe_layer_forward(x, logits, lw, k), moe_layer_forward(x, logits, back, k)
+    tb.matmul_check_status()
+    assert torch.equal(z0, z1)
+    # checkpoint form: canonical K-packed bytes regrouped as 16-byte blocks
+    blocks1 = lw.w1_q.transpose(1, 2).contiguous().reshape(E, 2 * ff, d // 32, 16)
+    blocks2 = lw.w2_q.transpose(1, 2).contiguous().reshape(E, d, ff // 32, 16)
+    ck = from_block_checkpoint(blocks1, lw.w1_s.transpose(1, 2).contiguous(), lw.b1, blocks2,
+                               lw.w2_s.transpose(1, 2).contiguous(), lw.b2, block_scaled=True)
+    for name in ("w1", "w1_scale", "w2", "w2_scale", "w1_bs", "w1_bs_scale", "w2_bs", "w2_bs_scale"):
+        assert torch.equal(getattr(ck, name).storage.data, getattr(lw, name).storage.data), name

@@ -148,6 +148,17 @@ def test_opt_flags_constraints_are_scoped():
     with triton_b200.scoped_opt_flags_constraints({"split_k": 4}):
         with pytest.raises(triton_b200.InapplicableConstraint):
             opt_flags.resolve_kernel_choice()
+    # a tile-shape key is honoured or refused, never dropped
+    for bad in ({"block_m": 48}, {"block_k": 256}, {"is_persistent": False}, {"num_stages": 3}, {"epilogue_subtile": 2},
+                {"no_such_key": 1}, {"idle_sms": -1}):
+        with triton_b200.scoped_opt_flags_constraints(bad):
+            with pytest.raises(triton_b200.InapplicableConstraint):
+                opt_flags.resolve_kernel_choice()
+    with triton_b200.scoped_opt_flags_constraints({"block_m": 32, "block_n": 384, "block_k": 128, "split_k": 1,
+                                                   "is_persistent": True, "num_stages": None, "idle_sms": 8}):
+        assert opt_flags.resolve_kernel_choice() == "auto"
+        assert opt_flags.resolve_tile_m() == 32 and opt_flags.resolve_tile_n() == 384 and opt_flags.get_idle_sms() == 8
+    assert opt_flags.get_idle_sms() == 0
 
 
 def test_balanced_expert_placement():
@@ -223,3 +234,43 @@ def test_default_weight_layout_arguments():
     assert isinstance(make_default_matmul_mxfp4_w_scale_layout(mx_axis=1), B200MXScaleLayout)
     with pytest.raises(NotImplementedError):
         make_default_matmul_mxfp4_w_layout(mx_axis=-1)
+
+
+def test_weight_file_round_trip_on_cpu(tmp_path):
+    """save_layer_weights / load_layer_weights: every tensor comes back byte for byte, in the layout it was saved in."""
+    from triton_b200.moe import MoeLayerWeights
+    from triton_b200.tensor import Storage, Tensor
+    from triton_b200.tensor_details.layout import (B200BlockScaledScaleLayout, B200BlockScaledValueLayout, B200MXScaleLayout,
+                                                   B200MXValueLayout)
+    from triton_b200.weights_io import load_layer_weights, read_header, save_layer_weights
+    g = torch.Generator().manual_seed(0)
+    E, K, N = 3, 256, 384
+
+    def tiled(layout, logical, nbytes, fp4):
+        data = torch.randint(0, 256, (nbytes,), generator=g, dtype=torch.uint8)
+        return Tensor(Storage(data, layout), dtype=FP4 if fp4 else triton_b200.tensor.UINT8, shape=logical)
+
+    nv, ns = E * 2 * 3 * 8192, E * 2 * 3 * 512
+    lw = MoeLayerWeights(tiled(B200MXValueLayout(), [E, K, N], nv, True), tiled(B200MXScaleLayout(), [E, K // 32, N], ns, False),
+                         torch.randn(E, N, generator=g).bfloat16(),
+                         tiled(B200MXValueLayout(), [E, N // 2, K], E * 2 * 2 * 8192, True),
+                         tiled(B200MXScaleLayout(), [E, N // 64, K], E * 2 * 2 * 512, False),
+                         torch.randn(E, K, generator=g).bfloat16(), alpha=1.5, limit=None,
+                         w1_bs=tiled(B200BlockScaledValueLayout(), [E, K, N], nv, True),
+                         w1_bs_scale=tiled(B200BlockScaledScaleLayout(), [E, K // 32, N], ns, False))
+    path = tmp_path / "layer.moeb200w"
+    size = save_layer_weights(path, lw)
+    assert path.stat().st_size == size and size % 4096 == 0
+    hdr = read_header(path)
+    assert all(e["offset"] % 4096 == 0 for e in hdr["tensors"].values()) and "w2_bs" not in hdr["tensors"]
+    back = load_layer_weights(path, "cpu")
+    assert back.alpha == 1.5 and back.limit is None and back.w2_bs is None
+    for name in ("w1", "w1_scale", "w2", "w2_scale", "w1_bs", "w1_bs_scale"):
+        a, b = getattr(lw, name), getattr(back, name)
+        assert type(a.storage.layout) is type(b.storage.layout) and a.shape == b.shape and a.dtype == b.dtype
+        assert torch.equal(a.storage.data, b.storage.data)
+    assert torch.equal(lw.b1, back.b1) and torch.equal(lw.b2, back.b2)
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(b"not a weight file at all")
+    with pytest.raises(ValueError):
+        read_header(bad)

@@ -18,6 +18,7 @@ from .tensor import (FP4, BitmatrixMetadata, RaggedTensorMetadata, SparseMatrix,
                      convert_layout, make_bitmatrix_metadata, make_ragged_tensor_metadata,
                      remap_ragged_tensor_metadata, wrap_torch_tensor)
 from .topk import topk  # noqa: F401
+from .weights_io import from_block_checkpoint, load_layer_weights, save_layer_weights  # noqa: F401
 from .distributed import (ExptAssignment, Mesh, SymmetricMemoryPool, convert_dp_to_ep, convert_ep_to_dp,  # noqa: F401
                           make_expt_assignment, make_expt_dict_balanced, make_expt_dict_random,
                           make_expt_dict_uniform)

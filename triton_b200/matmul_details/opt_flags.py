@@ -1,17 +1,25 @@
 """User-visible tuning overrides for `matmul` (triton_kernels/matmul_details/opt_flags.py:482-532).
 
-The constraint dictionary is context-local.  Keys understood here: ``kernel`` ("auto", "simt", "tcgen05-pair", "stream",
-"tcgen05").  The reference's tile-shape keys (block_m, block_n, block_k, num_stages, split_k,
-is_persistent, epilogue_subtile, ...) are accepted and ignored when they cannot matter, and raise
-InapplicableConstraint when they ask for something the CUDA kernels do not implement (split_k > 1)."""
+The constraint dictionary is context-local.  Keys understood here: ``kernel`` ("auto", "simt", "tcgen05", "tcgen05-pair",
+"stream", "mx"), ``block_m`` (token rows per tile: 16 / 32 / 64 / 128 for the block-scaled kernel, 128 / 256 for the bf16
+tensor-core kernel, whose 128-row tile spans only the rows present in steps of 16), ``block_n`` (128 / 256 / 384),
+``idle_sms``.  Every other tile-shape key of the reference may be given only the value the CUDA kernels are built with
+(``block_k`` 64 or 128, ``split_k`` 1, ``is_persistent`` True, the rest None); anything else raises
+InapplicableConstraint, which the reference's tests treat as "skip"."""
 from contextlib import contextmanager
 from contextvars import ContextVar
 
 _opt_flags_constraints: ContextVar = ContextVar("opt_flags_constraints", default=None)
 _idle_sms = 0
 
-_IGNORED_KEYS = {"block_m", "block_n", "block_k", "num_stages", "is_persistent", "epilogue_subtile", "fused_scatter",
-                 "idle_sms", "swap_xw", "disable_mx4_block_swap", "occupancy_target", "num_warps", "group_m", "clc"}
+# key -> values that the kernels can honour (None = "not constrained" is always accepted)
+_APPLICABLE = {
+    "block_m": {16, 32, 64, 128, 256}, "block_n": {128, 256, 384}, "block_k": {64, 128}, "split_k": {1},
+    "is_persistent": {True},
+    # fixed by the kernels: only "unconstrained" can be honoured
+    "num_stages": set(), "epilogue_subtile": set(), "fused_scatter": set(), "swap_xw": set(), "disable_mx4_block_swap": set(),
+    "occupancy_target": set(), "num_warps": set(), "group_m": set(), "clc": set(),
+}
 
 
 class InapplicableConstraint(Exception):
@@ -26,7 +34,8 @@ def set_idle_sms(num_idle_sms: int):
 
 
 def get_idle_sms() -> int:
-    return _idle_sms
+    v = get_opt_flags_constraints().get("idle_sms")
+    return _idle_sms if v is None else int(v)
 
 
 def get_opt_flags_constraints() -> dict:
@@ -75,9 +84,13 @@ def resolve_kernel_choice() -> str:
         if k == "kernel":
             if v not in ("auto", "simt", "tcgen05", "tcgen05-pair", "stream", "mx"):
                 raise InapplicableConstraint(f"unknown kernel {v!r}")
-        elif k == "split_k":
-            if v not in (None, 1):
-                raise InapplicableConstraint("split_k > 1 is not implemented")
-        elif k not in _IGNORED_KEYS:
+        elif k == "idle_sms":
+            if v is not None and (not isinstance(v, int) or v < 0):
+                raise InapplicableConstraint(f"idle_sms must be a non-negative integer, got {v!r}")
+        elif k in _APPLICABLE:
+            if v is not None and v not in _APPLICABLE[k]:
+                allowed = sorted(_APPLICABLE[k], key=str) or ["unconstrained"]
+                raise InapplicableConstraint(f"opt_flags constraint {k}={v!r} cannot be honoured (possible: {allowed})")
+        else:
             raise InapplicableConstraint(f"unsupported opt_flags constraint {k!r}")
     return c.get("kernel", "auto")
