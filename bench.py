@@ -669,6 +669,9 @@ def main():
                     help="pin the grouped-GEMM kernel (default: the library's choice)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "uniform"],
                     help="expert placement over ranks: equal counts balanced by measured load, or contiguous blocks")
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="expert-parallel layer: pull the token rows in this many expert groups, overlapped with fc1")
+    ap.add_argument("--ep-idle-sms", type=int, default=0, help="SMs the overlapped fc1 launches leave to the pull kernel")
     ap.add_argument("--micro", default=None, choices=["routing", "mxfp", "all"],
                     help="print only the memory-bound micro-benchmarks")
     args = ap.parse_args()
@@ -737,6 +740,7 @@ def main():
         pool.initialize_matmul(T * world, D_MODEL, D_MODEL, TOP_K, N_EXPTS, torch.bfloat16, dev)
         if args.exchange != "nccl":
             pool.enable_peer_buffers(T, D_MODEL, D_MODEL, TOP_K, torch.bfloat16, dev)
+        pool.overlap_chunks, pool.overlap_idle_sms = args.ep_chunks, args.ep_idle_sms
 
     def eager(xi, li, timer=None, mark=None):
         if world > 1:
@@ -1036,6 +1040,7 @@ def main():
                        "expert_placement": placement_note,
                        "exchange": None if world == 1 else ("peer-mapped buffers" if pool.peer_ok else
                                                             f"NCCL all-to-all ({pool.peer_error})"),
+                       "ep_overlap": None if world == 1 else {"chunks": args.ep_chunks, "idle_sms": args.ep_idle_sms},
                        "l2": "inputs larger than L2 (weights streamed once per step)",
                        "tflops_per_step_algorithmic": T * world * TOP_K * (FLOP_PER_ROW_FC1 + FLOP_PER_ROW_FC2) / 1e12},
             "clocks": clocks.summary(), "blocks": blocks, "sustained": sustained, "e2e": e2e,

@@ -64,6 +64,16 @@ def _worker(rank, world, port, n_tokens, d_model, d_ff, n_expts, k, mode, ret):
             oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3,
                                        what=f"EP ({exchange}, fused={fused}) vs single GPU")
         if pool.peer_ok:
+            # the dispatch pull in groups of experts on a side stream, overlapped with fc1 of the previous group
+            for chunks, idle in ((2, 0), (3, 8)):
+                pool.overlap_chunks, pool.overlap_idle_sms = chunks, idle
+                z_loc = moe_layer_forward_ep(x[sl].contiguous(), logits[sl].contiguous(), lw_local, k, assign, pool, exchange="peer")
+                tb.matmul_check_status()
+                z_all = torch.empty_like(z_ref)
+                dist.all_gather_into_tensor(z_all, z_loc)
+                oracle.assert_close_oracle(z_ref.cpu(), z_all.cpu(), maxtol=2e-2, rmstol=4e-3,
+                                           what=f"EP (peer, {chunks} overlapped groups) vs single GPU")
+            pool.overlap_chunks, pool.overlap_idle_sms = 2, 0          # the replayed step below keeps one overlapped form
             # what the benchmark times: the collective-free step captured once and replayed on new inputs
             from triton_b200.moe import GraphedMoeLayer
             gl = GraphedMoeLayer(lw_local, k, T_local, d_model, n_expts, dev, forward=lambda xi, li: moe_layer_forward_ep(

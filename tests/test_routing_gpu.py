@@ -157,8 +157,9 @@ def test_routing_full_size(device):
 def test_fused_route_equals_separate_entry_points(T, E, k, dtype, device, monkeypatch):
     """`route` (three launches: top-k + histogram, scan + ragged metadata, rank) returns exactly what the five-launch
     composition topk -> make_bitmatrix_metadata -> make_ragged_tensor_metadata returns, and what the oracle computes."""
-    from triton_b200 import routing as routing_mod
-    from triton_b200.routing import route
+    import importlib
+    routing_mod = importlib.import_module("triton_b200.routing")      # (the package exports a function of the same name)
+    route = routing_mod.route
     monkeypatch.setattr(routing_mod, "FUSED_MAX_TOKENS", 1 << 30)      # the fused form at every size
     torch.manual_seed(T * 131 + E)
     logits = torch.randn(T, E, device=device).to(dtype)

@@ -48,11 +48,6 @@ constexpr int MX_SF_BASE = 512 - MX_MAX_STAGES * MX_SF_COLS;    // 384: accumula
 constexpr int MX_SMEM_LIMIT = 227 * 1024;
 constexpr int MX_CTL_BARS = 3 * MX_MAX_STAGES + 5;          // full, empty, scales-ready rings; 2 + 2 accumulator; drain
 constexpr int MX_CTL_BYTES = MX_CTL_BARS * 8 + 16;          // + tensor-memory base, abort flag
-// The unpacked weight operand takes twice its packed size in shared memory, so the ring holds only about four k steps
-// (100 KB of packed weights per SM), too few to cover the latency of HBM.  The producer therefore asks L2 for the
-// weights of this many k steps ahead of the ring (cp.async.bulk.prefetch.L2: no shared memory involved), and the
-// ring's own copies then hit L2.
-constexpr int MX_PREFETCH_STAGES = 10;
 
 struct MxParams {
   const uint8_t* xq;            // packed token chunks: [slot][k step][n_mma rows x 128 B | 1024 B scale area]
@@ -192,9 +187,6 @@ __device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap* tma
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 // instruction descriptor of kind::mxf8f6f4: A = e2m1 (code 5), B = e4m3 (code 0), both K-major, e8m0 scales,
 // M = 128, N = n; sf selects the byte (k group) of the scale words for A and B
 __device__ __forceinline__ uint32_t mx_idesc(int n, uint32_t sf) {
@@ -275,30 +267,6 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      // L2 prefetch cursor: walks the same (item, k step) sequence MX_PREFETCH_STAGES steps ahead of the ring
-      int64_t pf_item = blockIdx.x, pf_tile0 = 0;
-      int pf_kt = 0, pf_live = 0;
-      auto pf_open = [&]() {
-        if (pf_item >= n_items) return;
-        int e; int64_t row0; int rows;
-        mx_map_block(p, q.tb, pf_item % useful_m, e, row0, rows);
-        const int nb0 = (int)(pf_item / useful_m) * MB;
-        pf_tile0 = (int64_t)e * KT * NB + nb0;
-        pf_live = min(MB, NB - nb0);
-        pf_kt = 0;
-      };
-      auto pf_step = [&]() {
-        if (pf_item >= n_items) return;
-        const int64_t tile = pf_tile0 + (int64_t)pf_kt * NB;
-        prefetch_l2((const uint8_t*)p.w + tile * MX_W_TILE_TX, (uint32_t)(pf_live * MX_W_TILE_TX));
-        prefetch_l2(p.w_scale + tile * MX_WS_TILE, (uint32_t)(pf_live * MX_WS_TILE));
-        if (++pf_kt == KT) {
-          pf_item += gridDim.x;
-          pf_open();
-        }
-      };
-      pf_open();
-      for (int i = 0; i < MX_PREFETCH_STAGES; ++i) pf_step();
       for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const int64_t pid_m = item % useful_m;
         const int ng = (int)(item / useful_m);
@@ -309,7 +277,6 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
         const uint8_t* xsrc = q.xq + pid_m * KT * q.chunk_bytes;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
-          pf_step();
           ok = mbar_wait(BAR_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 601);
           if (!ok) break;
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;

@@ -359,7 +359,7 @@ bool moe_gemm_stream_supported(const MoeGemmArgs& a, const char** why) {
 }
 
 int moe_gemm_stream_launch(const GemmParams& p, const MoeGemmArgs& a, cudaStream_t st) {
-  const int sms = moe_sm_count();
+  const int sms = (moe_sm_count() - (a.idle_sms > 0 ? a.idle_sms : 0)) > 0 ? moe_sm_count() - (a.idle_sms > 0 ? a.idle_sms : 0) : 1;
   // at most one CTA per SM (shared memory); fewer when there cannot be that many items
   const int64_t nt = cdiv64(a.N, HALF_N);
   const int64_t max_items = (a.slice_sizes ? (int64_t)a.E + cdiv64(a.M, S_ROWS) : cdiv64(a.M, S_ROWS)) * nt;

@@ -674,9 +674,10 @@ static int64_t n_blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
 }
 
 template <typename TY, int MH, int NH>
-static int launch_tc(const GemmParams& p, int64_t grid_m, int64_t N, cudaStream_t st) {
+static int launch_tc(const GemmParams& p, int64_t grid_m, int64_t N, int idle_sms, cudaStream_t st) {
   const int64_t tiles = grid_m * cdiv64(N, HALF_N * NH);
-  const int sms = moe_sm_count();
+  // persistent CTAs, one per SM, minus the SMs the caller keeps free for kernels of another stream (matmul_set_idle_sms)
+  const int sms = max(1, moe_sm_count() - max(idle_sms, 0));
   const int grid = (int)(tiles < sms ? tiles : sms);
   MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TY, MH, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg<MH, NH>::SMEM_ALLOC));
@@ -690,10 +691,10 @@ static int launch_tc(const GemmParams& p, int64_t grid_m, int64_t N, cudaStream_
 }
 
 template <typename TY>
-static int launch_tc_shape(const GemmParams& p, int mh, int nh, int64_t grid_m, int64_t N, cudaStream_t st) {
-  if (mh == 2 && nh == 2) return launch_tc<TY, 2, 2>(p, grid_m, N, st);
-  if (mh == 2) return launch_tc<TY, 2, 1>(p, grid_m, N, st);
-  return launch_tc<TY, 1, 1>(p, grid_m, N, st);
+static int launch_tc_shape(const GemmParams& p, int mh, int nh, int64_t grid_m, int64_t N, int idle_sms, cudaStream_t st) {
+  if (mh == 2 && nh == 2) return launch_tc<TY, 2, 2>(p, grid_m, N, idle_sms, st);
+  if (mh == 2) return launch_tc<TY, 2, 1>(p, grid_m, N, idle_sms, st);
+  return launch_tc<TY, 1, 1>(p, grid_m, N, idle_sms, st);
 }
 
 int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_t st) {
@@ -719,6 +720,6 @@ int moe_gemm_tc_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
     grid_m = cdiv64(a.M, 128 * mh);
   }
   if (grid_m == 0) return MOE_OK;
-  if (a.y_dtype == MOE_BF16) return launch_tc_shape<__nv_bfloat16>(p, mh, nh, grid_m, a.N, st);
-  return launch_tc_shape<float>(p, mh, nh, grid_m, a.N, st);
+  if (a.y_dtype == MOE_BF16) return launch_tc_shape<__nv_bfloat16>(p, mh, nh, grid_m, a.N, a.idle_sms, st);
+  return launch_tc_shape<float>(p, mh, nh, grid_m, a.N, a.idle_sms, st);
 }

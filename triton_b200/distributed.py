@@ -122,6 +122,18 @@ class SymmetricMemoryPool:
         # the expert sort reads the gathered expert indices, not the bitmatrix: a caller that only needs the routing
         # metadata may switch the bitmatrix exchange off (the other ranks' rows of the mask are then undefined)
         self.gather_bitmatrix = True
+        # expert-parallel layer over peer buffers: pull the token rows in this many groups of experts, group c + 1 on a
+        # side stream under fc1 of group c (1 = one pull, then one fc1); the GEMMs of all but the last group leave
+        # `overlap_idle_sms` SMs without a CTA for the pull kernel (matmul_set_idle_sms of the reference, matmul.py:239-243)
+        self.overlap_chunks = 1
+        self.overlap_idle_sms = 0
+        self._side = {}
+
+    def side_stream(self, device):
+        key = torch.device(device).index
+        if key not in self._side:
+            self._side[key] = torch.cuda.Stream(device=device)
+        return self._side[key]
 
     def enable_peer_buffers(self, n_tokens_local, d_in, d_out, k, dtype, device) -> bool:
         """x buffer [T_local, d_in] (this rank's tokens) and y buffer [T_global * k, d_out] (expert outputs in

@@ -254,23 +254,71 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
     _lib.check(lib.moe_ep_pull_index(_lib.ptr(col), _lib.ptr(indx16), _lib.ptr(sparse.vals.contiguous()),
                                      _lib.ptr(local_expt), n, k, _lib.ptr(src_row), _lib.ptr(gammas), _lib.stream()),
                "moe_ep_pull_index")
+    chunks = int(getattr(pool, "overlap_chunks", 1))
+    w1, w1_scale, w2, w2_scale = lw_local.fc_weights(n // W)            # rows this rank multiplies, on average
+    E_loc = lw_local.n_expts
+    if lw_local.use_block_scaled(n // W) or E_loc < 2:
+        chunks = 1
+    chunks = max(1, min(chunks, E_loc))
+    plan = None
+    if chunks > 1:
+        # Pipeline: the experts of this rank in `chunks` groups; the rows of group c + 1 are pulled on a side stream while
+        # fc1 runs on group c.  Everything a group needs -- its pull index (rows of other groups: -2 = leave alone) and its
+        # ragged metadata (other experts masked out, offsets kept global) -- is computed before the token barrier.
+        bounds = [(E_loc * c) // chunks for c in range(chunks + 1)]
+        plan = []
+        for c in range(chunks):
+            lo_e, hi_e = bounds[c], bounds[c + 1]
+            table = torch.where((local_expt >= lo_e) & (local_expt < hi_e), local_expt - lo_e, torch.full_like(local_expt, -1))
+            rows_c = torch.empty(n, dtype=torch.int32, device=dev)
+            _lib.check(lib.moe_ep_pull_index(_lib.ptr(col), _lib.ptr(indx16), _lib.ptr(sparse.vals.contiguous()),
+                                             _lib.ptr(table), n, k, _lib.ptr(rows_c), _lib.ptr(gammas), _lib.stream()),
+                       "moe_ep_pull_index")
+            plan.append((rows_c, remap_ragged_tensor_metadata(meta_global, table), lo_e, hi_e))
     if x_local.data_ptr() != pool.xbuf.data_ptr():                     # a caller may keep its tokens in the pool's buffer
         pool.xbuf.copy_(x_local)
     pool.barrier()                                                     # every rank's tokens are in its buffer
     mark("pull index + token barrier")
     x_sorted = torch.empty((n, d), dtype=x_local.dtype, device=dev)
     ptrs = (ctypes.c_void_p * W)(*pool.x_ptrs)
-    _lib.check(lib.moe_gather_rows_peers(ptrs, W, T_local, d * x_local.element_size(), _lib.ptr(src_row), n,
-                                         d * x_local.element_size(), _lib.ptr(x_sorted),
-                                         d * x_local.element_size(), _lib.stream()), "moe_gather_rows_peers")
-    mark("dispatch pull")
-    w1, w1_scale, w2, w2_scale = lw_local.fc_weights(n // W)            # rows this rank multiplies, on average
+    row_bytes = d * x_local.element_size()
     pc1 = PrecisionConfig(b_mx_scale=w1_scale, b_microblock_size=32)
     pc2 = PrecisionConfig(b_mx_scale=w2_scale, b_microblock_size=32)
-    with _span(gemm_timer):
-        h = matmul(x_sorted, w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
-                   fused_activation=_activation(lw_local))
-    mark("fc1")
+    if plan is None:
+        _lib.check(lib.moe_gather_rows_peers(ptrs, W, T_local, row_bytes, _lib.ptr(src_row), n, row_bytes, _lib.ptr(x_sorted),
+                                             row_bytes, _lib.stream()), "moe_gather_rows_peers")
+        mark("dispatch pull")
+        with _span(gemm_timer):
+            h = matmul(x_sorted, w1, lw_local.b1, a_ragged_metadata=meta_local, precision_config=pc1,
+                       fused_activation=_activation(lw_local))
+    else:
+        from .matmul_details import opt_flags
+        main = torch.cuda.current_stream(dev)
+        side = pool.side_stream(dev)
+        start = torch.cuda.Event()
+        start.record(main)
+        side.wait_event(start)
+        pulled = []
+        with torch.cuda.stream(side):
+            for rows_c, _, _, _ in plan:
+                _lib.check(lib.moe_gather_rows_peers(ptrs, W, T_local, row_bytes, _lib.ptr(rows_c), n, row_bytes,
+                                                     _lib.ptr(x_sorted), row_bytes, side.cuda_stream), "moe_gather_rows_peers")
+                ev = torch.cuda.Event()
+                ev.record(side)
+                pulled.append(ev)
+        h = torch.empty((n, w1.shape[-1] // 2), dtype=x_local.dtype, device=dev)
+        idle = int(getattr(pool, "overlap_idle_sms", 0))
+        with _span(gemm_timer):
+            for (rows_c, meta_c, lo_e, hi_e), ev in zip(plan, pulled):
+                main.wait_event(ev)
+                last = hi_e == E_loc
+                with opt_flags.scoped_opt_flags_constraints({"idle_sms": None if last else idle}):
+                    matmul(x_sorted, _expert_range(w1, lo_e, hi_e), lw_local.b1[lo_e:hi_e], a_ragged_metadata=meta_c,
+                           precision_config=PrecisionConfig(b_mx_scale=_expert_range(w1_scale, lo_e, hi_e), b_microblock_size=32),
+                           fused_activation=_activation(lw_local), c=h)
+        mark("dispatch pull + fc1 (pipelined)")
+    if plan is None:
+        mark("fc1")
     with _span(gemm_timer):
         y = matmul(h, w2, lw_local.b2, a_ragged_metadata=meta_local, precision_config=pc2, gammas=gammas,
                    c=pool.ybuf)
@@ -288,6 +336,15 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
                                                 _lib.ptr(z), z.stride(0), _lib.stream()), "moe_gather_reduce_rows_peers")
     mark("output barrier + combine")
     return z
+
+
+def _expert_range(t: Tensor, lo: int, hi: int) -> Tensor:
+    """Experts [lo, hi) of a tiled weight tensor (the tiled layouts are expert-major: a range of experts is a range of
+    the storage)."""
+    from .tensor import Storage
+    E = t.shape[0]
+    per = t.storage.data.numel() // E
+    return Tensor(Storage(t.storage.data[per * lo: per * hi], t.storage.layout), dtype=t.dtype, shape=[hi - lo] + list(t.shape[1:]))
 
 
 _ep_table_cache = {}
