@@ -627,6 +627,23 @@ def micro_record(dev, peaks, steps=5):
         T * E * 4 + T * k * (4 + 2) + T * (E // 8))
     add("routing (topk + expert sort + ragged metadata)", timed([lambda l=l: tb.routing(l, k) for l in lgs]),
         T * E * 4 + T * k * (4 + 2) + T * (E // 8) + T * k * (2 + 4 + 4) + E * 4 * 12)
+    # the router: logits = x @ Wg + bg and the top-k in one kernel, against the two steps apart (library GEMM + topk)
+    K = D_MODEL
+    rx = [torch.randn(T, K, device=dev, generator=g).bfloat16() for _ in range(NV)]
+    wg = tb.prepare_router_weight((torch.randn(K, E, device=dev, generator=g) / K ** 0.5).bfloat16())
+    wg_rows = wg.contiguous()
+    bg = torch.randn(E, device=dev, generator=g)
+    bgb = bg.bfloat16()
+    r_bytes = T * K * 2 + K * E * 2 + T * k * (2 + 2) + T * (E // 8)
+    add("router_topk fused [16384,2880] x [2880,128] -> top-4", timed([lambda x=x: tb.router_topk(x, wg, bg, k) for x in rx]), r_bytes)
+    add("router as two steps: library GEMM (bf16 logits) + topk",
+        timed([lambda x=x: tb.topk(torch.addmm(bgb, x, wg_rows), k) for x in rx]), r_bytes + 2 * T * E * 2)
+    for name in ("router_topk fused [16384,2880] x [2880,128] -> top-4", "router as two steps: library GEMM (bf16 logits) + topk"):
+        out["kernels"][name]["note"] = "includes the three expert-sort launches that build the SparseMatrix metadata"
+    rx64 = [x[:64].contiguous() for x in rx]
+    add("router_topk fused, 64 tokens", timed([lambda x=x: tb.router_topk(x, wg, bg, k) for x in rx64]), 64 * K * 2 + K * E * 2)
+    add("router as two steps, 64 tokens", timed([lambda x=x: tb.topk(torch.addmm(bgb, x, wg_rows), k) for x in rx64]), 64 * K * 2 + K * E * 2)
+    del rx, rx64
     R = C = 8192
     xs = []
     for _ in range(NV):

@@ -32,7 +32,9 @@ enum { MOE_W_DENSE = 0,          /* w[e,k,n] in the activation dtype, arbitrary 
        MOE_W_MX4_B200MX = 3      /* tiles for the block-scaled MMA made by moe_weight_layout_to_b200mx */ };
 #define MOE_MAX_PEERS 16
 enum { MOE_GEMM_AUTO = 0, MOE_GEMM_SIMT = 1, MOE_GEMM_TCGEN05 = 2, MOE_GEMM_TCGEN05_PAIR = 3, MOE_GEMM_STREAM = 4,
-       MOE_GEMM_MX = 5 };
+       MOE_GEMM_MX = 5,          /* block-scaled kernel; bf16 tokens in the form it picks by block size */
+       MOE_GEMM_MX_F8 = 6,       /* ... bf16 tokens as two e4m3 terms (kind::mxf8f6f4) */
+       MOE_GEMM_MX_F4 = 7 };     /* ... bf16 tokens as four e2m1 terms (kind::mxf4), blocks of at most 32 rows */
 
 const char* moe_last_error(void);
 int moe_abi_version(void);
@@ -97,6 +99,27 @@ int moe_route(const void* logits, int dtype, int64_t T, int E, int k, int apply_
               int32_t* slice_offs, int32_t* block_offs, int64_t ld_block_offs,
               int32_t* block_sched, int64_t ld_sched, int64_t n_sched,
               void* workspace, size_t workspace_bytes, void* stream);
+
+/* The router product and the top-k selection in one kernel: logits = x @ Wg + bg on the tensor cores, then what
+ * moe_topk_fwd does, in the epilogue (the reference runs `matmul(x, wg, bg)` and `topk` apart:
+ * triton_kernels bench/bench_mlp.py:70, topk.py:25-141).
+ *   x [T, K] bf16, row pitch ld_x; wg_t = Wg transposed, [E, K] bf16 with K contiguous, row pitch ld_wg (a [K, E] tensor
+ *   whose stride along K is 1); bias [E] fp32 or bf16, may be NULL; E <= 256; k in {1, 2, 4, 8, 16}; K, ld_x, ld_wg
+ *   multiples of 8 -- otherwise MOE_ERR_UNSUPPORTED and the caller runs the two steps apart.
+ *   round_bf16: round every logit to bf16 before the selection (what a bf16 router output does in the two-step form).
+ *   logits_out: NULL, or [T, E] fp32 that receives the logits the selection saw.
+ *   vals [T, k] fp32 or bf16, indx, bitmatrix: as for moe_topk_fwd.
+ * With few tokens K is cut into slices over the SMs and the partial logits meet in `workspace`
+ * (moe_router_topk_workspace_bytes, 16-byte aligned): it must be ALL ZERO when the call starts and the call leaves it
+ * all zero again, so one cudaMemset after allocating it serves every later call on the same stream (calls that share a
+ * workspace must not overlap; clear it again after a call that reported a device status).  The fp32 sums of the slices
+ * are formed in no fixed order.  A bounded wait that expires writes 801..804 to *status.                            */
+size_t moe_router_topk_workspace_bytes(int64_t T, int64_t K, int E);
+int moe_router_topk(const void* x, int64_t T, int64_t K, int64_t ld_x, const void* wg_t, int64_t ld_wg,
+                    const void* bias, int bias_dtype, int E, int k, int apply_softmax, int round_bf16,
+                    float* logits_out, int64_t ld_logits, void* vals, int vals_dtype, int64_t ld_vals,
+                    int16_t* indx, int64_t ld_indx, uint32_t* bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,
+                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* No counterpart in the reference.  The same computation as moe_bitmatrix_metadata for callers that cannot
  * supply a workspace because they cannot allocate device memory when they call: a serving process that gave

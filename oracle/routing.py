@@ -55,6 +55,19 @@ def topk_oracle(logits: torch.Tensor, k: int, apply_softmax: bool = True, y_indx
     return vals, indx, torch.from_numpy(bm.view(np.int32))
 
 
+def router_topk_oracle(x: torch.Tensor, wg: torch.Tensor, bg, k: int, apply_softmax: bool = True, logits_dtype=None):
+    """The router of the reference's MoE layer: `logits = matmul(x, wg, bg)` (bench/bench_mlp.py:70; fp32 accumulation,
+    bias added in fp32, result cast to the activation dtype: matmul.py:772-931) followed by `topk` (topk.py:144-185).
+    -> (logits in `logits_dtype` (default x.dtype), vals, indx, bitmatrix) with the last three as `topk_oracle` gives them."""
+    logits_dtype = x.dtype if logits_dtype is None else logits_dtype
+    logits = x.float() @ wg.float()
+    if bg is not None:
+        logits = logits + bg.float()
+    logits = logits.to(logits_dtype)
+    vals, indx, bm = topk_oracle(logits, k, apply_softmax)
+    return logits, vals, indx, bm
+
+
 def bitmatrix_metadata_oracle(indx: torch.Tensor, n_expts: int):
     """indx [T,k] (int, -1 = dropped) -> (col_sum [E], col_sorted_indx [T*k], row_sorted_indx [T*k]), int32.
 

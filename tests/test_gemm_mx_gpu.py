@@ -1,6 +1,7 @@
 """The block-scaled grouped GEMM (tcgen05.mma.kind::mxf8f6f4: MXFP4 weights straight into the MMA) on the GPU against
 the CPU oracle: e4m3 and MXFP8 activations (the reference's `a_mx_scale` mode, tests/test_matmul.py:282-285), and bf16
-activations split into two e4m3 terms inside the library."""
+activations split inside the library into two e4m3 terms, or (small token blocks) into four e2m1 terms for
+tcgen05.mma.kind::mxf4."""
 import pytest
 import torch
 
@@ -52,7 +53,7 @@ def test_block_scaled_layout_round_trip(device):
 
 
 def run_mx(x, wq, ws, sizes, device, *, a_scale=None, bias=None, gather=None, scatter=None, gammas=None, betas=None,
-           act=None, out_dtype=torch.bfloat16, block_m=None, block_n=None):
+           act=None, out_dtype=torch.bfloat16, block_m=None, block_n=None, kernel=None):
     dev = lambda t: None if t is None else t.to(device)
     tq, ts = to_block_scaled(wq, ws, device)
     M = int(sizes.sum())
@@ -66,6 +67,8 @@ def run_mx(x, wq, ws, sizes, device, *, a_scale=None, bias=None, gather=None, sc
         cons["block_m"] = block_m
     if block_n:
         cons["block_n"] = block_n
+    if kernel:
+        cons["kernel"] = kernel
     with tb.scoped_opt_flags_constraints(cons):
         y = tb.matmul(dev(x), tq, dev(bias), md, None, dev(gather), dev(scatter), pc, betas=dev(betas), gammas=dev(gammas),
                       fused_activation=fa)
@@ -154,8 +157,46 @@ def test_block_scaled_grouped_gemm(case, mode, acts, device):
     assert oracle.rel_l2(ref, y) < 1e-2
 
 
-@pytest.mark.parametrize("block_m", [16, 32, 64])
-def test_block_scaled_token_block_sizes(block_m, device):
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("mode", ["plain", "scatter_w", "all"])
+@pytest.mark.parametrize("kernel", ["mx-f8", "mx-f4"])
+def test_block_scaled_bf16_token_forms(case, mode, kernel, device):
+    """bf16 tokens in each of the two forms the kernel can split them into, pinned (the automatic choice depends on
+    the block size): two e4m3 terms and four e2m1 terms."""
+    E, K, N, sizes, T = case
+    g = torch.Generator().manual_seed(hash((E, K, N, mode)) % 1000 + 1)
+    opts = dict(plain={}, scatter_w=dict(gather=True, scatter=True, weights=True),
+                all=dict(gather=True, scatter=True, weights=True, act=True))[mode]
+    sizes_t = torch.tensor(sizes, dtype=torch.int32)
+    M = int(sizes_t.sum())
+    rows_x = T if opts.get("gather") else M
+    wq, ws, wdeq = quantised_weights(E, K, N, g)
+    x = torch.randn(rows_x, K, generator=g).bfloat16()
+    bias = torch.randn(E, N, generator=g) * 0.1
+    gather = torch.randint(0, T, (M,), generator=g, dtype=torch.int32) if opts.get("gather") else None
+    scatter = torch.randperm(M, generator=g).int() if opts.get("scatter") else None
+    gammas = torch.rand(M, generator=g) if opts.get("weights") else None
+    betas = torch.rand(M, generator=g) if opts.get("weights") else None
+    act = (1.702, 7.0) if opts.get("act") else None
+    y = run_mx(x, wq, ws, sizes_t, device, bias=bias, gather=gather, scatter=scatter, gammas=gammas, betas=betas, act=act,
+               out_dtype=torch.float32, kernel=kernel)
+    ref = oracle.matmul_oracle(x.float(), wdeq, bias, sizes_t, gather, None, betas=betas, gammas=None if act else gammas,
+                               out_dtype=torch.float32)
+    if act:
+        ref = oracle.swiglu_oracle(ref, *act)
+        if gammas is not None:
+            ref = ref * gammas[:, None]
+    if scatter is not None:
+        out = torch.zeros_like(ref)
+        out[scatter.long()] = ref
+        ref = out
+    # fp32 output: what is left is the split of the tokens (two e4m3 terms hold a bf16 value exactly up to underflow;
+    # four e2m1 terms leave about 2^-14 of a group's maximum) and the order of the fp32 sums
+    assert oracle.rel_l2(ref, y) < (5e-4 if kernel == "mx-f4" else 2e-5)
+
+
+@pytest.mark.parametrize("block_m, kernel", [(16, "mx"), (32, "mx"), (64, "mx"), (16, "mx-f8"), (16, "mx-f4"), (32, "mx-f4")])
+def test_block_scaled_token_block_sizes(block_m, kernel, device):
     """bf16 activations with every token-block size: experts with more rows than a block take several blocks."""
     g = torch.Generator().manual_seed(7)
     E, K, N = 6, 640, 640           # five weight blocks in groups of three: the last group of the last expert is partial
@@ -163,24 +204,25 @@ def test_block_scaled_token_block_sizes(block_m, device):
     M = int(sizes.sum())
     wq, ws, wdeq = quantised_weights(E, K, N, g)
     x = torch.randn(M, K, generator=g).bfloat16()
-    y = run_mx(x, wq, ws, sizes, device, block_m=block_m, block_n=384)
+    y = run_mx(x, wq, ws, sizes, device, block_m=block_m, block_n=384, kernel=kernel)
     ref = oracle.matmul_oracle(x.float(), wdeq, None, sizes, out_dtype=torch.float32).bfloat16()
     oracle.assert_close_oracle(ref, y, maxtol=MAXTOL_MX4, rmstol=None, what="block-scaled gemm")
     assert oracle.rel_l2(ref, y) < 1e-2
 
 
-def test_block_scaled_wide_dynamic_range_rows(device):
-    """bf16 rows whose magnitudes span 2^40: each 32-group has its own pair of scales, so small groups next to large
-    ones keep their precision."""
+@pytest.mark.parametrize("kernel", ["mx-f8", "mx-f4"])
+def test_block_scaled_wide_dynamic_range_rows(kernel, device):
+    """bf16 rows whose magnitudes span 2^40: each 32-group has its own scales, so small groups next to large ones keep
+    their precision."""
     g = torch.Generator().manual_seed(9)
     E, K, N, M = 1, 512, 128, 20
     wq, ws, wdeq = quantised_weights(E, K, N, g)
     x = torch.randn(M, K, generator=g)
     x = (x * torch.exp2(torch.randint(-20, 20, (M, K // 32), generator=g).float()).repeat_interleave(32, dim=1)).bfloat16()
     sizes = torch.tensor([M], dtype=torch.int32)
-    y = run_mx(x, wq, ws, sizes, device, out_dtype=torch.float32)
+    y = run_mx(x, wq, ws, sizes, device, out_dtype=torch.float32, kernel=kernel)
     ref = oracle.matmul_oracle(x.float(), wdeq, None, sizes, out_dtype=torch.float32)
-    assert oracle.rel_l2(ref, y) < 1e-2
+    assert oracle.rel_l2(ref, y) < 1e-3
 
 
 def test_block_scaled_e4m3_output(device):

@@ -11,6 +11,7 @@ from .matmul import (Epilogue, FlexCtx, FnName, FusedActivation, FusedComm, Inap
 from .numerics import InFlexData, OutFlexData  # noqa: F401
 from .numerics_details.mxfp import DequantScaleRoundingMode, downcast_to_mxfp, upcast_from_mxfp  # noqa: F401
 from .reduce import reduce  # noqa: F401
+from .router import prepare_router_weight, router_topk  # noqa: F401
 from .routing import routing  # noqa: F401
 from .specialize import FnSpecs  # noqa: F401
 from .swiglu import swiglu, swiglu_fn  # noqa: F401

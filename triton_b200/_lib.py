@@ -19,6 +19,7 @@ MOE_ROUND_UP, MOE_ROUND_DOWN = 0, 1
 MOE_ACT_NONE, MOE_ACT_SWIGLU = 0, 1
 MOE_W_DENSE, MOE_W_MX4_CANONICAL, MOE_W_MX4_B200, MOE_W_MX4_B200MX = 0, 1, 2, 3
 MOE_GEMM_AUTO, MOE_GEMM_SIMT, MOE_GEMM_TCGEN05, MOE_GEMM_TCGEN05_PAIR, MOE_GEMM_STREAM, MOE_GEMM_MX = 0, 1, 2, 3, 4, 5
+MOE_GEMM_MX_F8, MOE_GEMM_MX_F4 = 6, 7
 MOE_MAX_PEERS = 16
 
 _DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: MOE_BF16,
@@ -65,6 +66,9 @@ PROTOTYPES = {
     "moe_bitmatrix_metadata": (i32, [vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]),
     "moe_route": (i32, [vp, i32, i64, i32, i32, i32, i64, vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, vp, vp, i64, vp, i64,
                         i64, vp, sz, vp]),
+    "moe_router_topk_workspace_bytes": (sz, [i64, i64, i32]),
+    "moe_router_topk": (i32, [vp, i64, i64, i64, vp, i64, vp, i32, i32, i32, i32, i32, vp, i64, vp, i32, i64, vp, i64, vp, i64,
+                              i64, vp, sz, vp, vp]),
     "moe_bitmatrix_metadata_noalloc_capacity": (sz, []),
     "moe_bitmatrix_metadata_noalloc": (i32, [vp, i64, i64, i32, i32, vp, vp, vp, vp, vp]),
     "moe_ragged_metadata": (i32, [vp, i32, vp, vp, i64, vp, i64, i64, vp]),

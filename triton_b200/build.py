@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libmoe_b200.so"
 SOURCES = ["api.cu", "mxfp.cu", "routing.cu", "elementwise.cu", "layout.cu", "gemm.cu", "gemm_simt.cu",
-           "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_stream.cu", "gemm_mx.cu", "tensor_roof.cu"]
+           "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_stream.cu", "gemm_mx.cu", "tensor_roof.cu", "router.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

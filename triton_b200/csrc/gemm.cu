@@ -63,9 +63,10 @@ extern "C" __attribute__((visibility("default"))) int moe_grouped_gemm(const Moe
   }
 
   const char* why = "";
-  if (a->w_kind == MOE_W_MX4_B200MX || a->kernel == MOE_GEMM_MX) {
+  const bool mx_asked = a->kernel == MOE_GEMM_MX || a->kernel == MOE_GEMM_MX_F8 || a->kernel == MOE_GEMM_MX_F4;
+  if (a->w_kind == MOE_W_MX4_B200MX || mx_asked) {
     // weights laid out for the block-scaled MMA: that kernel or nothing
-    if (!moe_gemm_mx_supported(*a, &why) || (a->kernel != MOE_GEMM_AUTO && a->kernel != MOE_GEMM_MX)) {
+    if (!moe_gemm_mx_supported(*a, &why) || (a->kernel != MOE_GEMM_AUTO && !mx_asked)) {
       moe_set_error("moe_grouped_gemm: block-scaled kernel not applicable: %s", *why ? why : "another kernel was requested");
       return MOE_ERR_UNSUPPORTED;
     }

@@ -16,6 +16,13 @@
 // side by side as N columns of ONE MMA ([hi tokens | lo tokens], every column has its own scale), the epilogue adds the
 // two accumulator columns of a token.  e4m3 / MXFP8 activations enter as they are (one term).
 //
+// With at most 16 token rows per block (decode) bf16 activations take a second form: FOUR e2m1 terms, each the MXFP4
+// quantisation of what the terms before it left over (about 2^-14 of the group maximum after four), and the MMA is
+//   tcgen05.mma.kind::mxf4.block_scale.scale_vec::2X -- K = 64 per instruction and both operands packed, so a
+// weight tile stays 8 KB in shared memory (plain TMA copy, 64-byte swizzle) instead of the 16 KB of the byte-per-
+// element form, and a k step costs half the MMA instructions.  Twice the bytes in flight per SM and half the
+// instruction count are what a weight-streaming step is short of; the four terms are four groups of N columns.
+//
 // Data flow of one k step (128 k):
 //   weights     one TMA tensor copy: MB x (128 rows x 64 packed bytes) from the tile-contiguous layout of
 //               moe_weight_layout_to_b200mx, unpacked by the TMA unit (CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B) into the
@@ -40,8 +47,9 @@ namespace {
 
 constexpr int MX_THREADS = 320;               // warp 0 producer, 1 MMA, 2-5 epilogue, 6-9 scale loaders
 constexpr int MX_MAX_STAGES = 8;
-constexpr int MX_W_TILE = 128 * 128;           // one weight block of a stage in shared memory (unpacked)
-constexpr int MX_W_TILE_TX = 128 * 64;         // what its copy reports to the mbarrier: the packed bytes read
+constexpr int MX_W_TILE = 128 * 128;           // one weight block of a stage in shared memory (byte per element)
+constexpr int MX_W_TILE_TX = 128 * 64;         // what its copy reports to the mbarrier: the packed bytes read; also the
+                                               // size of a weight block that stays packed (four-term form)
 constexpr int MX_WS_TILE = 512;                // its scales
 constexpr int MX_SF_COLS = 16;                 // tensor-memory columns of scales per stage (MB x 4 + 4)
 constexpr int MX_SF_BASE = 512 - MX_MAX_STAGES * MX_SF_COLS;    // 384: accumulators live below
@@ -54,12 +62,37 @@ struct MxParams {
   int64_t chunk_bytes;
   int n_mma;                    // MMA N: token columns (hi and lo when split)
   int tb;                       // token rows per block (16, 32, 64 or 128)
-  int split;                    // bf16 source: columns [0, tb) hold hi, [tb, 2 tb) lo
+  int split;                    // terms of a token: 1, 2 (bf16 as hi + lo e4m3) or 4 (bf16 as e2m1 terms); term t of
+                                // token j is column t * tb + j
   int KT, NB;                   // 128-k steps, 128-row weight blocks
   int stages, stage_bytes;
   int acc_bufs;
   int n_groups;                 // ceil(NB / MB)
   int64_t grid_m;               // static bound on token blocks (dense problems: exact)
+};
+
+struct MxMaps {
+  CUtensorMap m[3];             // boxes of 1, 2 and 3 weight blocks
+};
+
+// The tiles of one CTA, in the order every role walks them.  A tile is one token block x up to MB consecutive weight
+// blocks; tile = (weight group, token block) with token blocks varying fastest, dealt out round robin, so that CTAs
+// running at the same time share a weight group (large problems: the group is read from HBM once).  (Equal contiguous
+// ranges of weight blocks per CTA, which leave no partly filled last wave, were measured 5-12 % slower at 16 and 64
+// tokens: they cut more tiles short of MB blocks, and a k step costs about the same whatever it carries.)
+struct MxSched {
+  int64_t useful_m, cur, end;
+  int NB, MB;
+  __device__ __forceinline__ MxSched(int64_t useful_m_, int NB_, int NG, int MB_)
+      : useful_m(useful_m_), cur(blockIdx.x), end(useful_m_ * NG), NB(NB_), MB(MB_) {}
+  __device__ __forceinline__ bool next(int64_t& pid_m, int& nb0, int& mb_live) {
+    if (cur >= end) return false;
+    pid_m = cur % useful_m;
+    nb0 = (int)(cur / useful_m) * MB;
+    mb_live = min(MB, NB - nb0);
+    cur += gridDim.x;
+    return true;
+  }
 };
 
 // ---- token block -> (expert, first row, rows) through the block schedule of the block size in use -----------
@@ -177,6 +210,74 @@ __global__ void __launch_bounds__(256) mx_pack_x_kernel(const GemmParams p, cons
   }
 }
 
+// ---- four e2m1 terms -----------------------------------------------------------------------------------------
+// Chunk of the four-term form: row r (r < 4 tb; term t of token j is row t * tb + j) is 64 bytes = 128 e2m1 values, low
+// nibble first, its 16-byte pieces XOR-swizzled with ((r >> 1) & 3) like a 64-byte-swizzled TMA tile; scales as above.
+__device__ __forceinline__ uint32_t f32_to_e2m1(float q) {           // round to nearest, ties to the even code; |q| <= 6
+  const float a = fabsf(q);
+  const uint32_t c = (uint32_t)(a > 0.25f) + (uint32_t)(a >= 0.75f) + (uint32_t)(a > 1.25f) + (uint32_t)(a >= 1.75f) +
+                     (uint32_t)(a > 2.5f) + (uint32_t)(a >= 3.5f) + (uint32_t)(a > 5.0f);
+  return c | ((__float_as_uint(q) >> 28) & 8u);
+}
+__device__ __forceinline__ float e2m1_to_f32(uint32_t c) {
+  const uint32_t m = c & 7u;
+  // 0, 0.5 | (1 + 0.5 (m & 1)) * 2^((m >> 1) - 1)
+  float v = m < 2u ? 0.5f * (float)m : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+  return (c & 8u) ? -v : v;
+}
+// e8m0 byte s with 2^(s-127) >= amax / 6, and the exact factors 2^(s-127), 2^(127-s)
+__device__ __forceinline__ void mx4_scale(float amax, uint32_t& sb, float& scale, float& inv) {
+  const float ds = __fdiv_rn(amax, 6.0f);
+  uint32_t u = (__float_as_uint(ds) + 0x007FFFFFu) & 0x7F800000u;
+  sb = u >> 23;
+  if (amax == 0.0f) sb = 127u;
+  sb = min(max(sb, 1u), 253u);
+  scale = __uint_as_float(sb << 23);
+  inv = __uint_as_float((254u - sb) << 23);
+}
+
+__global__ void __launch_bounds__(256) mx_pack_x4_kernel(const GemmParams p, const PackParams a) {
+  const int64_t slot = blockIdx.x;
+  const int kt = blockIdx.y;
+  int e; int64_t row0; int rows;
+  if (!mx_map_block(p, a.tb, slot, e, row0, rows)) return;
+  uint8_t* chunk = a.out + (slot * a.KT + kt) * a.chunk_bytes;
+  uint8_t* sc = chunk + (int64_t)a.n_mma * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k = kt * 128 + lane * 4;
+  const uint32_t g = (uint32_t)(lane >> 3), within = (uint32_t)(lane & 7) * 2u;     // a 32-group is one 16-byte piece
+  for (int r = warp; r < rows; r += 8) {
+    const int64_t m = row0 + r;
+    int64_t src = a.gather ? (int64_t)a.gather[m] : m;
+    if (src >= a.rows_x) src = -1;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (src >= 0 && k < a.K) {
+      const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)a.x + src * a.ld_x + k);
+      v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+      v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+      for (int o = 1; o <= 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      if (!(amax < 3.0e38f)) amax = t == 0 ? 3.0e38f : 0.0f;       // Inf / NaN in the group: keep the scales finite
+      uint32_t sb; float s, inv;
+      mx4_scale(amax, sb, s, inv);
+      uint32_t codes = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t c = f32_to_e2m1(v[i] * inv);
+        codes |= c << (4 * i);
+        v[i] -= e2m1_to_f32(c) * s;
+      }
+      const int rt = t * a.tb + r;
+      *reinterpret_cast<uint16_t*>(chunk + rt * 64 + ((g ^ (uint32_t)((rt >> 1) & 3)) << 4) + within) = (uint16_t)codes;
+      if ((lane & 7) == 0) sc[(rt & 31) * 16 + (rt >> 5) * 4 + (int)g] = (uint8_t)sb;
+    }
+  }
+}
+
 // ============================================================================================================
 // PTX pieces of the block-scaled path
 // ============================================================================================================
@@ -192,6 +293,29 @@ __device__ __forceinline__ void tma_tile_3d(uint32_t dst, const CUtensorMap* tma
 __device__ __forceinline__ uint32_t mx_idesc(int n, uint32_t sf) {
   return (sf << 4) | (5u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | (1u << 27) | (sf << 29);
 }
+// kind::mxf4: A and B e2m1 (code 1), packed, K-major, K = 64; sf selects the byte PAIR (0 or 2) of the scale words
+__device__ __forceinline__ uint32_t mx4_idesc(int n, uint32_t sf) {
+  return (sf << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | (1u << 27) | (sf << 29);
+}
+// shared-memory descriptor of a K-major operand with 64-byte rows and 64-byte swizzle (8-row groups 512 B apart)
+__device__ __forceinline__ uint64_t make_desc_sw64(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;
+  return d;
+}
+__device__ __forceinline__ void mma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
                                              uint32_t sfb, uint32_t accumulate) {
   asm volatile(
@@ -205,17 +329,20 @@ __device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t adesc, ui
 // ============================================================================================================
 // The GEMM kernel
 // ============================================================================================================
-template <typename TY, int MB>
+// F4: the four-term form (packed operands, kind::mxf4); otherwise byte-per-element operands, kind::mxf8f6f4
+template <typename TY, int MB, bool F4>
 __global__ void __launch_bounds__(MX_THREADS, 1)
-gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUtensorMap w_map) {
+gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxMaps w_maps) {
+  constexpr uint32_t W_TILE = F4 ? MX_W_TILE_TX : MX_W_TILE;       // bytes of a weight block in shared memory
+  constexpr uint32_t X_ROW = F4 ? 64u : 128u;                      // bytes of a token row of a k step
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int STAGES = q.stages;
   // per stage: [MB weight blocks][token rows + 1024 B scale area][MB x 512 B weight scales]
-  const uint32_t OFF_X = MB * MX_W_TILE;
-  const uint32_t OFF_XS = OFF_X + (uint32_t)q.n_mma * 128u;
+  const uint32_t OFF_X = MB * W_TILE;
+  const uint32_t OFF_XS = OFF_X + (uint32_t)q.n_mma * X_ROW;
   const uint32_t OFF_WS = OFF_XS + 1024u;
   const uint32_t ctl0 = sbase + (uint32_t)STAGES * (uint32_t)q.stage_bytes;
   auto BAR_FULL = [&](int s) { return ctl0 + 8u * (uint32_t)s; };
@@ -257,32 +384,29 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
   const int KT = q.KT, NB = q.NB, NG = q.n_groups;
   int64_t useful_m = q.grid_m;
   if (p.slice_sizes) useful_m = (int64_t)p.block_offs[p.E];
-  // item -> (token block, weight group): token blocks vary fastest, so that CTAs running at the same time share a
-  // weight group only when they hold blocks of the same expert
-  const int64_t n_items = useful_m * NG;
   const int acc_stride = MB * q.n_mma;              // accumulator columns of one buffer
+  MxSched sched(useful_m, NB, NG, MB);
+  int64_t pid_m;
+  int nb0, mb_live;
 
   if (warp == 0) {
     // ================================= producer =======================================================
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const int64_t pid_m = item % useful_m;
-        const int ng = (int)(item / useful_m);
+      while (ok && sched.next(pid_m, nb0, mb_live)) {
         int e; int64_t row0; int rows;
         mx_map_block(p, q.tb, pid_m, e, row0, rows);
-        const int nb0 = ng * MB;
-        const int mb_live = min(MB, NB - nb0);
         const uint8_t* xsrc = q.xq + pid_m * KT * q.chunk_bytes;
+        const CUtensorMap* w_map = &w_maps.m[mb_live - 1];
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(BAR_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 601);
           if (!ok) break;
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
           const int64_t tile = ((int64_t)e * KT + kt) * NB + nb0;
-          mbar_expect_tx(BAR_FULL(s), (uint32_t)(MB * MX_W_TILE_TX + mb_live * MX_WS_TILE) + (uint32_t)q.chunk_bytes);
-          tma_tile_3d(st, &w_map, 0, 0, (int)tile, BAR_FULL(s));
+          mbar_expect_tx(BAR_FULL(s), (uint32_t)(mb_live * (MX_W_TILE_TX + MX_WS_TILE)) + (uint32_t)q.chunk_bytes);
+          tma_tile_3d(st, w_map, 0, 0, (int)tile, BAR_FULL(s));
           bulk_g2s(st + OFF_WS, p.w_scale + tile * MX_WS_TILE, (uint32_t)(mb_live * MX_WS_TILE), BAR_FULL(s));
           bulk_g2s(st + OFF_X, xsrc + (int64_t)kt * q.chunk_bytes, (uint32_t)q.chunk_bytes, BAR_FULL(s));
         }
@@ -300,9 +424,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t it = 0, tc = 0;
       bool ok = true;
-      for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tc) {
-        const int ng = (int)(item / useful_m);
-        const int mb_live = min(MB, NB - ng * MB);
+      for (; ok && sched.next(pid_m, nb0, mb_live); ++tc) {
         const uint32_t ab = tc % (uint32_t)q.acc_bufs;
         ok = mbar_wait(BAR_ACC_EMPTY(ab), ((tc / (uint32_t)q.acc_bufs) & 1u) ^ 1u, ctl, 603);
         if (!ok) break;
@@ -316,16 +438,30 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
           tc_fence_after();
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
           const uint32_t sf = tmem_base + (uint32_t)(MX_SF_BASE + s * MX_SF_COLS);
-          const uint64_t bdesc = make_desc(st + OFF_X);
           // k group outermost: consecutive MMAs go to different accumulators
+          if constexpr (F4) {
+            const uint64_t bdesc = make_desc_sw64(st + OFF_X);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < 2; ++kk) {
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb) {
-              if (mb < mb_live)
-                mma_mxf8f6f4(d_tmem + (uint32_t)(mb * q.n_mma), make_desc(st + (uint32_t)mb * MX_W_TILE) + (uint64_t)(kk * 2),
-                             bdesc + (uint64_t)(kk * 2), mx_idesc(q.n_mma, (uint32_t)kk), sf + 4u * (uint32_t)mb, sf + 4u * MB,
-                             (kt | kk) ? 1u : 0u);
+              for (int mb = 0; mb < MB; ++mb) {
+                if (mb < mb_live)
+                  mma_mxf4(d_tmem + (uint32_t)(mb * q.n_mma), make_desc_sw64(st + (uint32_t)mb * W_TILE) + (uint64_t)(kk * 2),
+                           bdesc + (uint64_t)(kk * 2), mx4_idesc(q.n_mma, (uint32_t)(kk * 2)), sf + 4u * (uint32_t)mb, sf + 4u * MB,
+                           (kt | kk) ? 1u : 0u);
+              }
+            }
+          } else {
+            const uint64_t bdesc = make_desc(st + OFF_X);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+              for (int mb = 0; mb < MB; ++mb) {
+                if (mb < mb_live)
+                  mma_mxf8f6f4(d_tmem + (uint32_t)(mb * q.n_mma), make_desc(st + (uint32_t)mb * W_TILE) + (uint64_t)(kk * 2),
+                               bdesc + (uint64_t)(kk * 2), mx_idesc(q.n_mma, (uint32_t)kk), sf + 4u * (uint32_t)mb, sf + 4u * MB,
+                               (kt | kk) ? 1u : 0u);
+              }
             }
           }
           mma_commit(BAR_EMPTY(s));
@@ -346,8 +482,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
     const int qd = warp & 3;
     uint32_t it = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      const int mb_live = min(MB, NB - (int)(item / useful_m) * MB);
+    while (ok && sched.next(pid_m, nb0, mb_live)) {
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const int s = it % STAGES;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_FULL(s), (it / STAGES) & 1u, ctl, 607));
@@ -385,17 +520,14 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
     const bool swiglu = p.activation == MOE_ACT_SWIGLU;
     uint32_t tc = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++tc) {
-      const int64_t pid_m = item % useful_m;
-      const int ng = (int)(item / useful_m);
+    for (; ok && sched.next(pid_m, nb0, mb_live); ++tc) {
       int e; int64_t row0; int rows;
       mx_map_block(p, q.tb, pid_m, e, row0, rows);
-      const int mb_live = min(MB, NB - ng * MB);
       const uint32_t ab = tc % (uint32_t)q.acc_bufs;
       float bias_n[MB];
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb) {
-        const int n = (ng * MB + mb) * 128 + qd * 32 + lane;
+        const int n = (nb0 + mb) * 128 + qd * 32 + lane;
         bias_n[mb] = (p.bias && n < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + n) : 0.0f;
       }
       ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_ACC_FULL(ab), (tc / (uint32_t)q.acc_bufs) & 1u, ctl, 604));
@@ -417,13 +549,24 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
           if (mb < mb_live) {
-            const int n = (ng * MB + mb) * 128 + qd * 32 + lane;
+            const int n = (nb0 + mb) * 128 + qd * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + ab * (uint32_t)acc_stride +
                                    (uint32_t)(mb * q.n_mma + c0);
             uint32_t hi[16], lo[16];
             tmem_ld16(taddr, hi);
-            if (q.split) tmem_ld16(taddr + (uint32_t)q.tb, lo);
+            if (q.split > 1) tmem_ld16(taddr + (uint32_t)q.tb, lo);
             tmem_ld_wait();
+            if constexpr (F4) {                                   // terms 2 and 3
+              uint32_t t2[16], t3[16];
+              tmem_ld16(taddr + 2u * (uint32_t)q.tb, t2);
+              tmem_ld16(taddr + 3u * (uint32_t)q.tb, t3);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                hi[j] = __float_as_uint(__uint_as_float(hi[j]) + __uint_as_float(t3[j]));      // smallest terms first
+                lo[j] = __float_as_uint(__uint_as_float(lo[j]) + __uint_as_float(t2[j]));
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (j < jmax) {                                   // warp-uniform
@@ -431,7 +574,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
                 const float beta = __shfl_sync(0xFFFFFFFFu, beta_l, j);
                 const float gamma = __shfl_sync(0xFFFFFFFFu, gamma_l, j);
                 float a = __uint_as_float(hi[j]);
-                if (q.split) a += __uint_as_float(lo[j]);
+                if (q.split > 1) a += __uint_as_float(lo[j]);
                 a += bias_n[mb] * beta;
                 if (p.has_out_alpha) a *= p.out_alpha;
                 if (swiglu) {
@@ -464,7 +607,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ CUt
 
 // ---- host side -----------------------------------------------------------------------------------------------
 struct MxPlan {
-  int tb, n_mma, split, mb, KT, NB, n_groups, stages, stage_bytes, acc_bufs;
+  int tb, n_mma, split, f4, mb, KT, NB, n_groups, stages, stage_bytes, acc_bufs;
   int64_t grid_m, chunk_bytes, ws_bytes;
 };
 
@@ -476,8 +619,9 @@ int64_t blocks_bound(int64_t n_slices, int64_t n_rows, int64_t block) {
 
 MxPlan mx_plan(const MoeGemmArgs& a) {
   MxPlan pl;
-  pl.split = a.x_dtype == MOE_BF16 ? 1 : 0;
-  const int tb_max = pl.split ? 64 : 128;
+  const bool bf16 = a.x_dtype == MOE_BF16;
+  const bool pin_f4 = bf16 && a.kernel == MOE_GEMM_MX_F4, pin_f8 = a.kernel == MOE_GEMM_MX_F8;
+  const int tb_max = bf16 ? (pin_f4 ? 32 : 64) : 128;
   int tb = 16;
   if (a.tile_m == 16 || a.tile_m == 32 || a.tile_m == 64 || a.tile_m == 128) {
     tb = a.tile_m;
@@ -487,7 +631,10 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   }
   if (tb > tb_max) tb = tb_max;
   pl.tb = tb;
-  pl.n_mma = pl.split ? 2 * tb : (tb < 32 ? 32 : tb);     // a scale chunk serves 32 columns at a time
+  // bf16 tokens: four e2m1 terms for the smallest blocks (weight streaming decides there), else two e4m3 terms
+  pl.f4 = (bf16 && !pin_f8 && (pin_f4 || tb == 16)) ? 1 : 0;
+  pl.split = bf16 ? (pl.f4 ? 4 : 2) : 1;
+  pl.n_mma = pl.split > 1 ? pl.split * tb : (tb < 32 ? 32 : tb);     // a scale chunk serves 32 columns at a time
   pl.KT = (int)cdiv64(a.K, 128);
   pl.NB = (int)cdiv64(a.N, 128);
   pl.grid_m = a.slice_sizes ? blocks_bound(a.E, a.M, tb) : cdiv64(a.M, tb);
@@ -496,8 +643,8 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   const int64_t items3 = pl.grid_m * cdiv64(pl.NB, 3);
   pl.mb = (a.tile_n == 128) ? 1 : ((a.tile_n == 384 || items3 >= 2 * (int64_t)moe_sm_count()) ? 3 : 1);
   pl.n_groups = (int)cdiv64(pl.NB, pl.mb);
-  pl.chunk_bytes = (int64_t)pl.n_mma * 128 + 1024;
-  pl.stage_bytes = pl.mb * MX_W_TILE + (int)pl.chunk_bytes + 2048;
+  pl.chunk_bytes = (int64_t)pl.n_mma * (pl.f4 ? 64 : 128) + 1024;
+  pl.stage_bytes = pl.mb * (pl.f4 ? MX_W_TILE_TX : MX_W_TILE) + (int)pl.chunk_bytes + 2048;
   const int ctl_bytes = MX_CTL_BYTES;
   int st = (MX_SMEM_LIMIT - 1024 - ctl_bytes) / pl.stage_bytes;
   pl.stages = st > MX_MAX_STAGES ? MX_MAX_STAGES : st;
@@ -506,7 +653,7 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   return pl;
 }
 
-int make_w_map(const MoeGemmArgs& a, const MxPlan& pl, CUtensorMap* map) {
+int make_w_map(const MoeGemmArgs& a, const MxPlan& pl, int n_blocks, CUtensorMap* map) {
   static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   static std::mutex mu;
   {
@@ -522,14 +669,17 @@ int make_w_map(const MoeGemmArgs& a, const MxPlan& pl, CUtensorMap* map) {
       encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
     }
   }
-  // [tile][128 rows][128 e2m1 = 64 bytes]; the TMA unit writes 16 elements per 16 bytes of shared memory
+  // [tile][128 rows][128 e2m1 = 64 bytes].  Byte-per-element form: the TMA unit writes 16 elements per 16 bytes of
+  // shared memory (128-byte rows, 128-byte swizzle); packed form: the 64-byte rows as they are, 64-byte swizzle.
   const cuuint64_t tiles = (cuuint64_t)a.E * (cuuint64_t)pl.KT * (cuuint64_t)pl.NB;
-  const cuuint64_t dims[3] = {128, 128, tiles};
+  const cuuint64_t inner = pl.f4 ? 64 : 128;
+  const cuuint64_t dims[3] = {inner, 128, tiles};
   const cuuint64_t strides[2] = {64, 64 * 128};
-  const cuuint32_t box[3] = {128, 128, (cuuint32_t)pl.mb};
+  const cuuint32_t box[3] = {(cuuint32_t)inner, 128, (cuuint32_t)n_blocks};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void*>(a.w), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  const CUresult r = encode(map, pl.f4 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3,
+                            const_cast<void*>(a.w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            pl.f4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     moe_set_error("moe_grouped_gemm: cuTensorMapEncodeTiled (packed e2m1 weights) failed with code %d (%llu tiles)", (int)r,
@@ -539,17 +689,23 @@ int make_w_map(const MoeGemmArgs& a, const MxPlan& pl, CUtensorMap* map) {
   return MOE_OK;
 }
 
-template <typename TY, int MB>
-int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const CUtensorMap& w_map, int idle_sms, cudaStream_t st) {
+template <typename TY, int MB, bool F4>
+int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const MxMaps& w_map, int idle_sms, cudaStream_t st) {
   const int smem = pl.stages * pl.stage_bytes + MX_CTL_BYTES + 1024;
   const int64_t items = pl.grid_m * pl.n_groups;
   int sms = moe_sm_count() - idle_sms;
   if (sms < 1) sms = 1;
   const int grid = (int)(items < sms ? items : sms);
-  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_mx_kernel<TY, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  gemm_mx_kernel<TY, MB><<<grid, MX_THREADS, smem, st>>>(p, q, w_map);
+  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_mx_kernel<TY, MB, F4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  gemm_mx_kernel<TY, MB, F4><<<grid, MX_THREADS, smem, st>>>(p, q, w_map);
   MOE_CHECK_LAUNCH();
   return MOE_OK;
+}
+
+template <typename TY>
+int launch_mx_ty(const GemmParams& p, const MxParams& q, const MxPlan& pl, const MxMaps& w_map, int idle_sms, cudaStream_t st) {
+  if (pl.f4) return pl.mb == 3 ? launch_mx<TY, 3, true>(p, q, pl, w_map, idle_sms, st) : launch_mx<TY, 1, true>(p, q, pl, w_map, idle_sms, st);
+  return pl.mb == 3 ? launch_mx<TY, 3, false>(p, q, pl, w_map, idle_sms, st) : launch_mx<TY, 1, false>(p, q, pl, w_map, idle_sms, st);
 }
 
 }  // namespace
@@ -564,6 +720,7 @@ bool moe_gemm_mx_supported(const MoeGemmArgs& a, const char** why) {
   if ((uintptr_t)a.w % 32 != 0 || (uintptr_t)a.w_scale % 16 != 0) { *why = "weights are not 32-byte aligned"; return false; }
   if (a.K % 32 != 0) { *why = "K is not a multiple of 32"; return false; }
   if (a.x_scale && a.x_dtype != MOE_F8E4M3) { *why = "activation scales need e4m3 activations"; return false; }
+  if (a.kernel == MOE_GEMM_MX_F4 && a.x_dtype != MOE_BF16) { *why = "the four-term form is for bf16 activations"; return false; }
   if ((int64_t)a.E * cdiv64(a.K, 128) * cdiv64(a.N, 128) >= 2147483647LL) { *why = "too many weight tiles"; return false; }
   *why = "";
   return true;
@@ -597,7 +754,8 @@ int moe_gemm_mx_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
   pk.out = (uint8_t*)a.mx_workspace;
   const dim3 pgrid((unsigned)pl.grid_m, (unsigned)pl.KT);
   MOE_CHECK_ARG(pl.grid_m < 2147483647LL, "moe_grouped_gemm: too many token blocks");
-  if (pl.split) mx_pack_x_kernel<true><<<pgrid, 256, 0, st>>>(p, pk);
+  if (pl.f4) mx_pack_x4_kernel<<<pgrid, 256, 0, st>>>(p, pk);
+  else if (pl.split > 1) mx_pack_x_kernel<true><<<pgrid, 256, 0, st>>>(p, pk);
   else mx_pack_x_kernel<false><<<pgrid, 256, 0, st>>>(p, pk);
   MOE_CHECK_LAUNCH();
 
@@ -606,12 +764,11 @@ int moe_gemm_mx_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
   q.n_mma = pl.n_mma; q.tb = pl.tb; q.split = pl.split;
   q.KT = pl.KT; q.NB = pl.NB; q.stages = pl.stages; q.stage_bytes = pl.stage_bytes; q.acc_bufs = pl.acc_bufs;
   q.n_groups = pl.n_groups; q.grid_m = pl.grid_m;
-  CUtensorMap w_map;
-  if (int rc = make_w_map(a, pl, &w_map)) return rc;
+  MxMaps w_map;
+  for (int nb = 1; nb <= 3; ++nb)
+    if (int rc = make_w_map(a, pl, nb <= pl.mb ? nb : pl.mb, &w_map.m[nb - 1])) return rc;
   const int idle = a.idle_sms > 0 ? a.idle_sms : 0;
-  if (a.y_dtype == MOE_F8E4M3)
-    return pl.mb == 3 ? launch_mx<__nv_fp8_e4m3, 3>(p, q, pl, w_map, idle, st) : launch_mx<__nv_fp8_e4m3, 1>(p, q, pl, w_map, idle, st);
-  if (a.y_dtype == MOE_BF16)
-    return pl.mb == 3 ? launch_mx<__nv_bfloat16, 3>(p, q, pl, w_map, idle, st) : launch_mx<__nv_bfloat16, 1>(p, q, pl, w_map, idle, st);
-  return pl.mb == 3 ? launch_mx<float, 3>(p, q, pl, w_map, idle, st) : launch_mx<float, 1>(p, q, pl, w_map, idle, st);
+  if (a.y_dtype == MOE_F8E4M3) return launch_mx_ty<__nv_fp8_e4m3>(p, q, pl, w_map, idle, st);
+  if (a.y_dtype == MOE_BF16) return launch_mx_ty<__nv_bfloat16>(p, q, pl, w_map, idle, st);
+  return launch_mx_ty<float>(p, q, pl, w_map, idle, st);
 }

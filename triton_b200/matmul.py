@@ -115,6 +115,8 @@ _STATUS_TEXT = {
     603: "block-scaled kernel: the MMA thread waited for a free accumulator", 604: "block-scaled kernel: the epilogue waited for an accumulator",
     605: "block-scaled kernel: the final MMA drain", 606: "block-scaled kernel: the MMA thread waited for scales",
     607: "block-scaled kernel: a scale loader waited for a stage",
+    801: "router kernel: the producer waited for a free stage", 802: "router kernel: the MMA thread waited for a stage",
+    803: "router kernel: the final MMA drain", 804: "router kernel: the selection waited for the accumulator",
     901: "expert-parallel peer barrier: a rank did not arrive within the limit; the step after it read stale peer buffers",
 }
 
@@ -126,7 +128,7 @@ def status_message(code: int) -> str:
 
 def matmul_check_status(device=None):
     """Synchronise and raise if a bounded wait expired since the last check: a pipeline wait inside a tensor-core
-    kernel (codes 1xx-6xx) or an expert-parallel peer barrier (901).  Expert-parallel callers should poll this once
+    kernel (codes 1xx-8xx) or an expert-parallel peer barrier (901).  Expert-parallel callers should poll this once
     per step or batch: after a barrier time-out the step carries on with stale peer buffers and its result is wrong."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     w = _status_word(dev)
@@ -378,7 +380,7 @@ def matmul(a, b, bias,
             args.y_peers[i] = int(h)
     args.kernel = {"auto": _lib.MOE_GEMM_AUTO, "simt": _lib.MOE_GEMM_SIMT, "tcgen05": _lib.MOE_GEMM_TCGEN05,
                    "tcgen05-pair": _lib.MOE_GEMM_TCGEN05_PAIR, "stream": _lib.MOE_GEMM_STREAM,
-                   "mx": _lib.MOE_GEMM_MX}[kernel_choice]
+                   "mx": _lib.MOE_GEMM_MX, "mx-f8": _lib.MOE_GEMM_MX_F8, "mx-f4": _lib.MOE_GEMM_MX_F4}[kernel_choice]
     args.tile_m, args.tile_n = resolve_tile_m(), resolve_tile_n()
     args.idle_sms = get_idle_sms()
     args.status = _status_word(dev).data_ptr()

@@ -1,7 +1,7 @@
 """User-visible tuning overrides for `matmul` (triton_kernels/matmul_details/opt_flags.py:482-532).
 
 The constraint dictionary is context-local.  Keys understood here: ``kernel`` ("auto", "simt", "tcgen05", "tcgen05-pair",
-"stream", "mx"), ``block_m`` (token rows per tile: 16 / 32 / 64 / 128 for the block-scaled kernel, 128 / 256 for the bf16
+"stream", "mx", "mx-f8", "mx-f4"), ``block_m`` (token rows per tile: 16 / 32 / 64 / 128 for the block-scaled kernel, 128 / 256 for the bf16
 tensor-core kernel, whose 128-row tile spans only the rows present in steps of 16), ``block_n`` (128 / 256 / 384),
 ``idle_sms``.  Every other tile-shape key of the reference may be given only the value the CUDA kernels are built with
 (``block_k`` 64 or 128, ``split_k`` 1, ``is_persistent`` True, the rest None); anything else raises
@@ -82,7 +82,7 @@ def resolve_kernel_choice() -> str:
     c = get_opt_flags_constraints()
     for k, v in c.items():
         if k == "kernel":
-            if v not in ("auto", "simt", "tcgen05", "tcgen05-pair", "stream", "mx"):
+            if v not in ("auto", "simt", "tcgen05", "tcgen05-pair", "stream", "mx", "mx-f8", "mx-f4"):
                 raise InapplicableConstraint(f"unknown kernel {v!r}")
         elif k == "idle_sms":
             if v is not None and (not isinstance(v, int) or v < 0):
