@@ -192,6 +192,19 @@ def main(ref_root):
     asw = ta.swizzle_data(a)
     save("layout_bw2", {"value": v2, "value_shuffled_128_256": vs.contiguous(), "value_shuffled_64_128": vs2.contiguous(),
                         "act_scale": a, "act_scale_swizzled": asw.contiguous()})
+    # ---- router: dense product + top-k (bench/bench_mlp.py:70 followed by topk) -------------------------------------
+    for T, K, E, k in [(50, 96, 32, 4), (9, 64, 128, 2)]:
+        x = torch.randn(T, K, generator=g).bfloat16()
+        wg = (torch.randn(K, E, generator=g) / K ** 0.5).bfloat16()
+        bg = torch.randn(E, generator=g)
+        torch.arange = arange
+        try:
+            logits = ref_matmul.matmul_torch(x, wg, bg, None, None, None, None, ref_matmul.PrecisionConfig())
+        finally:
+            torch.arange = real_arange
+        sp = ref_topk.topk_torch(logits, k, apply_softmax=True)
+        save(f"router_T{T}_E{E}_k{k}", {"x": x, "wg": wg, "bg": bg, "k": k, "logits": logits, "vals": sp.vals, "indx": sp.indx,
+                                         "bitmatrix": sp.mask.storage.data.contiguous()})
     torch.histc = real_histc
 
 

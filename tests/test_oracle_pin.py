@@ -78,6 +78,17 @@ def test_routing_matches_reference_fixture(golden, name):
     assert torch.equal(row, g["row_sorted"])
 
 
+@pytest.mark.parametrize("name", ["router_T50_E32_k4", "router_T9_E128_k2"])
+def test_router_matches_reference_fixture(golden, name):
+    """`topk_torch(matmul_torch(x, wg, bg), k)` of the reference (bench/bench_mlp.py:70 + topk.py:144-185)."""
+    g = golden(name)
+    logits, vals, indx, bm = oracle.router_topk_oracle(g["x"], g["wg"], g["bg"], int(g["k"]), True)
+    assert torch.equal(logits, g["logits"])
+    assert torch.equal(indx, g["indx"].int())
+    assert torch.equal(bm, g["bitmatrix"])
+    assert torch.equal(vals.float(), g["vals"].float())
+
+
 def test_bitmatrix_docstring_example():
     # reference tensor_details/bitmatrix.py:10-19
     rows = [[2, 4, 5], [1, 5], [0, 1, 2, 6], [2, 4]]

@@ -92,3 +92,20 @@ def test_router_topk_falls_back_for_other_shapes(device):
     assert sp.indx.shape == (T, k)
     agree = (sp.indx.cpu().int() == indx).all(dim=1).float().mean().item()
     assert agree > 0.95
+
+
+@pytest.mark.parametrize("name", ["router_T50_E32_k4", "router_T9_E128_k2"])
+def test_router_topk_against_reference_fixture(golden, name, device):
+    """Fixtures recorded from the reference's own `matmul_torch` + `topk_torch`."""
+    g = golden(name)
+    k = int(g["k"])
+    sp, logits = tb.router_topk(g["x"].to(device), g["wg"].to(device), g["bg"].to(device), k, return_logits=True)
+    tb.matmul_check_status()
+    ref = g["logits"].float()
+    diff = (logits.cpu() - ref).abs()
+    assert (diff <= (ref.abs() * 2.0 ** -7).clamp_min(1e-5)).all()
+    same = diff.max(dim=1).values == 0           # rows whose logits came out bit-identical must select identically
+    assert same.float().mean().item() > 0.9
+    assert torch.equal(sp.indx.cpu().int()[same], g["indx"].int()[same])
+    assert torch.equal(sp.mask.storage.data.cpu()[: ref.shape[0]][same], g["bitmatrix"][same])
+    assert (sp.vals.cpu().float()[same] - g["vals"].float()[same]).abs().max().item() <= 2.0 ** -8
