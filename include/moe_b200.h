@@ -91,7 +91,8 @@ int moe_bitmatrix_metadata(const int16_t* indx, int64_t ld_indx, int64_t T, int 
  * composes, tests/test_distributed.py:203-210) with the expert histogram taken in the top-k pass and the ragged
  * metadata computed by the block that scans the histogram.  Every one of the T rows is valid (no device-side row
  * bound, no provided indices); n_expts <= 256, otherwise MOE_ERR_UNSUPPORTED and the caller uses the separate entry
- * points.  Outputs and the workspace (moe_bitmatrix_metadata_workspace bytes) as for those entry points.           */
+ * points.  Outputs as for those entry points; workspace of moe_route_workspace(T, n_expts, k) bytes.               */
+size_t moe_route_workspace(int64_t T, int E, int k);
 int moe_route(const void* logits, int dtype, int64_t T, int E, int k, int apply_softmax, int64_t ld_logits,
               void* vals, int64_t ld_vals, int16_t* indx, int64_t ld_indx,
               uint32_t* bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,

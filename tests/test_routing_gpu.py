@@ -152,7 +152,7 @@ def test_routing_full_size(device):
 
 
 @pytest.mark.parametrize("T, E, k", [(1, 128, 4), (7, 13, 2), (255, 32, 4), (256, 128, 4), (257, 200, 8), (4099, 256, 4),
-                                     (16384, 128, 4)])
+                                     (16384, 128, 4), (129, 48, 3), (1000, 128, 6), (300, 64, 16), (2500, 96, 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_fused_route_equals_separate_entry_points(T, E, k, dtype, device, monkeypatch):
     """`route` (three launches: top-k + histogram, scan + ragged metadata, rank) returns exactly what the five-launch

@@ -64,6 +64,7 @@ PROTOTYPES = {
     "moe_topk_fwd": (i32, [vp, i32, i64, i32, i32, i32, i64, vp, i64, vp, i64, vp, i64, i64, vp, i32, vp]),
     "moe_bitmatrix_metadata_workspace": (sz, [i64, i32, i32]),
     "moe_bitmatrix_metadata": (i32, [vp, i64, i64, i32, i32, vp, vp, vp, vp, vp, sz, vp]),
+    "moe_route_workspace": (sz, [i64, i32, i32]),
     "moe_route": (i32, [vp, i32, i64, i32, i32, i32, i64, vp, i64, vp, i64, vp, i64, i64, vp, vp, vp, vp, vp, i64, vp, i64,
                         i64, vp, sz, vp]),
     "moe_router_topk_workspace_bytes": (sz, [i64, i64, i32]),

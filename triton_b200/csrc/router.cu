@@ -14,6 +14,7 @@
 // zero, as it found them.
 // Every mbarrier wait is bounded.
 #include "gemm_tc_common.cuh"
+#include "topk_select.cuh"
 
 namespace {
 
@@ -38,59 +39,13 @@ struct RouterParams {
   int32_t* status;
 };
 
-// order-preserving map float -> uint32 (larger float <=> larger key), as the stand-alone top-k kernel uses it
-__device__ __forceinline__ uint32_t rt_float_key(float f) {
-  const uint32_t b = __float_as_uint(f);
-  return b ^ ((b & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
-}
-__device__ __forceinline__ float rt_key_float(uint32_t k) {
-  return __uint_as_float(k ^ ((k & 0x80000000u) ? 0x80000000u : 0xFFFFFFFFu));
-}
-
-// The K best (value key, expert) pairs, best first.  An insertion compares the candidate with all K places at once
-// (independent compares, then two selects per place) instead of bubbling it down: a thread walks its row alone, so the
-// length of the dependent chain is what the selection costs.  `push` takes experts in ascending order and keeps the
-// earlier of two equal values ahead with a strict compare; `push_any` takes them in any order and compares the
-// expert index too.
-template <int K>
-struct TopK {
-  uint32_t key[K];
-  int idx[K];
-  __device__ __forceinline__ TopK() {
-#pragma unroll
-    for (int i = 0; i < K; ++i) { key[i] = 0u; idx[i] = 0x7FFFFFFF; }
-  }
-  __device__ __forceinline__ void place(uint32_t c, int ci, const bool (&gt)[K]) {
-#pragma unroll
-    for (int i = K - 1; i > 0; --i) {               // descending: place i - 1 still holds its old entry
-      key[i] = gt[i] ? (gt[i - 1] ? key[i - 1] : c) : key[i];
-      idx[i] = gt[i] ? (gt[i - 1] ? idx[i - 1] : ci) : idx[i];
-    }
-    key[0] = gt[0] ? c : key[0];
-    idx[0] = gt[0] ? ci : idx[0];
-  }
-  __device__ __forceinline__ void push(float v, int e) {
-    const uint32_t c = rt_float_key(v);
-    bool gt[K];
-#pragma unroll
-    for (int i = 0; i < K; ++i) gt[i] = c > key[i];
-    place(c, e, gt);
-  }
-  __device__ __forceinline__ void push_any(uint32_t c, int ci) {
-    bool gt[K];
-#pragma unroll
-    for (int i = 0; i < K; ++i) gt[i] = c > key[i] || (c == key[i] && ci < idx[i]);
-    place(c, ci, gt);
-  }
-};
-
 template <int K>
 __device__ __forceinline__ void rt_store_row(const RouterParams& p, int64_t row, const TopK<K>& tk) {
   float v[K];
   int e[K];
 #pragma unroll
   for (int i = 0; i < K; ++i) {
-    v[i] = rt_key_float(tk.key[i]);
+    v[i] = sel_key_float(tk.key[i]);
     e[i] = tk.idx[i];
   }
   if (p.apply_softmax) {
@@ -315,17 +270,7 @@ router_topk_kernel(const RouterParams p, const __grid_constant__ CUtensorMap x_m
 #pragma unroll
         for (int i = 0; i < K; ++i) tk.push_any(sub[u].key[i], sub[u].idx[i]);
       }
-      for (int m = 1; m < P; m <<= 1) {
-        uint32_t ok_[K];
-        int oi[K];
-#pragma unroll
-        for (int i = 0; i < K; ++i) {
-          ok_[i] = __shfl_xor_sync(0xFFFFFFFFu, tk.key[i], m);
-          oi[i] = __shfl_xor_sync(0xFFFFFFFFu, tk.idx[i], m);
-        }
-#pragma unroll
-        for (int i = 0; i < K; ++i) tk.push_any(ok_[i], oi[i]);
-      }
+      tk.merge_lanes(P);
       if (live && part == 0) rt_store_row<K>(p, row, tk);
     }
   }

@@ -8,15 +8,14 @@ from .tensor_details.ragged_tensor import _empty_aligned
 from .topk import topk
 
 
-FUSED_MAX_TOKENS = 2048
+FUSED_MAX_TOKENS = 1 << 22
 
 
 def route(logits, n_expts_act, apply_softmax=True):
     """Top-k, expert histogram, expert-major sort and ragged metadata of one batch of logits in three launches
     (`moe_route`): -> (ragged_metadata, sparse_logits), the same objects `topk` + `make_ragged_tensor_metadata` return.
-    Used for batches of up to FUSED_MAX_TOKENS tokens, where a step is bound by its launch count; larger batches (and
-    more than 256 experts, or logits that are not a plain 2-D tensor) take the five-launch composition, whose top-k
-    kernel spreads one token row per warp over the whole GPU and is faster there."""
+    More than 256 experts, more than FUSED_MAX_TOKENS tokens, or logits that are not a plain 2-D tensor take the
+    five-launch composition of the separate entry points."""
     if not (isinstance(logits, torch.Tensor) and logits.ndim == 2 and logits.shape[1] <= 256
             and 0 < logits.shape[0] <= FUSED_MAX_TOKENS and logits.stride(1) == 1):
         sparse = topk(logits, n_expts_act, apply_softmax=apply_softmax)
@@ -38,7 +37,7 @@ def route(logits, n_expts_act, apply_softmax=True):
     offs = _empty_aligned((5, E + 1), dev)
     sched = _empty_aligned((4, mnb), dev)
     slice_offs, block_offs = offs[0], offs[1:]
-    ws_bytes = lib.moe_bitmatrix_metadata_workspace(T, E, k)
+    ws_bytes = lib.moe_route_workspace(T, E, k)
     ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
     _lib.check(lib.moe_route(_lib.ptr(logits), _lib.dtype_code(logits.dtype), T, E, k, int(bool(apply_softmax)), logits.stride(0),
                              _lib.ptr(vals), vals.stride(0), _lib.ptr(indx), indx.stride(0), _lib.ptr(bm), bm.stride(0),
