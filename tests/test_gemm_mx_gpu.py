@@ -270,3 +270,4 @@ def test_layer_with_e4m3_activations_against_oracle(tokens, device):
     got = z[rows.to(device)].cpu()
     oracle.assert_close_oracle(ref, got, maxtol=MAXTOL_MX4, rmstol=None, what="fp8 layer")
     assert oracle.rel_l2(ref, got) < 1e-2
+

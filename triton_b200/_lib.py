@@ -150,3 +150,26 @@ def ptr(t):
 
 def stream():
     return torch.cuda.current_stream().cuda_stream
+
+
+_zero_scratch = {}
+ZERO_SCRATCH_CAP = 160 << 20
+
+
+def zero_scratch(device, nbytes):
+    """A device buffer that is all zero between calls, for the kernels that keep partial sums of K slices in global
+    memory (they want it zero and leave it zero).  One buffer per device, cleared when it is allocated and grown on demand
+    up to ZERO_SCRATCH_CAP; calls that use it must not overlap on the GPU (one stream, or the caller's own ordering).
+    -> tensor, or None when there is none of that size and one cannot be made now: during CUDA-graph capture (the buffer
+    would belong to the graph), or above the cap.  Callers then take their form without K slices."""
+    import torch
+    dev = torch.device(device)
+    t = _zero_scratch.get(dev.index)
+    if t is not None and t.numel() >= nbytes:
+        return t
+    if nbytes > ZERO_SCRATCH_CAP or torch.cuda.is_current_stream_capturing():
+        return None
+    grow = max(int(nbytes), 32 << 20)
+    t = torch.zeros(grow, dtype=torch.uint8, device=dev)
+    _zero_scratch[dev.index] = t
+    return t

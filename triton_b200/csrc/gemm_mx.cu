@@ -35,6 +35,7 @@
 // wait is bounded.
 #include "gemm_tc_common.cuh"
 #include <cuda_fp8.h>
+#include <utility>
 
 // e4m3 output (the next GEMM's activations): round to nearest, saturating at +-448 like the MMA's own conversions
 template <> __device__ __forceinline__ __nv_fp8_e4m3 from_f32<__nv_fp8_e4m3>(float v) {
@@ -79,7 +80,10 @@ struct MxMaps {
 // blocks; tile = (weight group, token block) with token blocks varying fastest, dealt out round robin, so that CTAs
 // running at the same time share a weight group (large problems: the group is read from HBM once).  (Equal contiguous
 // ranges of weight blocks per CTA, which leave no partly filled last wave, were measured 5-12 % slower at 16 and 64
-// tokens: they cut more tiles short of MB blocks, and a k step costs about the same whatever it carries.)
+// tokens: they cut more tiles short of MB blocks, and a k step costs about the same whatever it carries.  Slices of K per
+// tile with fp32 partial sums in global memory -- red.global.add, the slice that arrives last runs the epilogue -- were
+// correct and 20-35 % slower at 4 to 64 tokens: 48 scalar reductions per thread and slice, their fence and the counter
+// round trip take longer than a slice of a few k steps, and the epilogue warps become the bottleneck.)
 struct MxSched {
   int64_t useful_m, cur, end;
   int NB, MB;
@@ -112,6 +116,16 @@ __device__ __forceinline__ bool mx_map_block(const GemmParams& p, int tb, int64_
   rows = min(tb, p.slice_sizes[e] - blk * tb);
   return rows > 0;
 }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------------
+// The pack kernel and the GEMM are launched with the programmatic-stream-serialization attribute: the next kernel of the
+// stream may start while this one still runs, and whatever it reads from a predecessor comes after its own
+// griddepcontrol.wait, which returns once the predecessors have completed and their writes are visible.  A decode step is
+// short launches back to back; this way a kernel's launch and prologue overlap the tail of its predecessor.  (Inside a
+// replayed CUDA graph the gain is within the noise: launches are back to back there anyway.  Requesting the first weight
+// tiles ahead of the wait changed nothing either.)
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ============================================================================================================
 // Pack kernel: token rows -> per (token block, k step) chunks in the operand layout of the MMA.
@@ -152,6 +166,8 @@ __device__ __forceinline__ void mx8_scale(float amax, uint32_t& sb, float& scale
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(256) mx_pack_x_kernel(const GemmParams p, const PackParams a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t slot = blockIdx.x;
   const int kt = blockIdx.y;
   int e; int64_t row0; int rows;
@@ -237,6 +253,8 @@ __device__ __forceinline__ void mx4_scale(float amax, uint32_t& sb, float& scale
 }
 
 __global__ void __launch_bounds__(256) mx_pack_x4_kernel(const GemmParams p, const PackParams a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t slot = blockIdx.x;
   const int kt = blockIdx.y;
   int e; int64_t row0; int rows;
@@ -380,6 +398,8 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int KT = q.KT, NB = q.NB, NG = q.n_groups;
   int64_t useful_m = q.grid_m;
@@ -641,7 +661,7 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   // three weight blocks per CTA tile share one token tile (fewer token bytes per weight byte); one block when there
   // would be too few tiles to fill the SMs
   const int64_t items3 = pl.grid_m * cdiv64(pl.NB, 3);
-  pl.mb = (a.tile_n == 128) ? 1 : ((a.tile_n == 384 || items3 >= 2 * (int64_t)moe_sm_count()) ? 3 : 1);
+  pl.mb = (a.tile_n == 128) ? 1 : ((a.tile_n == 384 || items3 >= (int64_t)moe_sm_count()) ? 3 : 1);
   pl.n_groups = (int)cdiv64(pl.NB, pl.mb);
   pl.chunk_bytes = (int64_t)pl.n_mma * (pl.f4 ? 64 : 128) + 1024;
   pl.stage_bytes = pl.mb * (pl.f4 ? MX_W_TILE_TX : MX_W_TILE) + (int)pl.chunk_bytes + 2048;
@@ -689,6 +709,22 @@ int make_w_map(const MoeGemmArgs& a, const MxPlan& pl, int n_blocks, CUtensorMap
   return MOE_OK;
 }
 
+// launch with the programmatic-stream-serialization attribute (see pdl_wait above)
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <typename TY, int MB, bool F4>
 int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const MxMaps& w_map, int idle_sms, cudaStream_t st) {
   const int smem = pl.stages * pl.stage_bytes + MX_CTL_BYTES + 1024;
@@ -697,7 +733,7 @@ int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const Mx
   if (sms < 1) sms = 1;
   const int grid = (int)(items < sms ? items : sms);
   MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_mx_kernel<TY, MB, F4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  gemm_mx_kernel<TY, MB, F4><<<grid, MX_THREADS, smem, st>>>(p, q, w_map);
+  MOE_CHECK_CUDA(launch_pdl(gemm_mx_kernel<TY, MB, F4>, dim3(grid), dim3(MX_THREADS), (size_t)smem, st, p, q, w_map));
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }
@@ -754,9 +790,9 @@ int moe_gemm_mx_launch(const GemmParams& p_in, const MoeGemmArgs& a, cudaStream_
   pk.out = (uint8_t*)a.mx_workspace;
   const dim3 pgrid((unsigned)pl.grid_m, (unsigned)pl.KT);
   MOE_CHECK_ARG(pl.grid_m < 2147483647LL, "moe_grouped_gemm: too many token blocks");
-  if (pl.f4) mx_pack_x4_kernel<<<pgrid, 256, 0, st>>>(p, pk);
-  else if (pl.split > 1) mx_pack_x_kernel<true><<<pgrid, 256, 0, st>>>(p, pk);
-  else mx_pack_x_kernel<false><<<pgrid, 256, 0, st>>>(p, pk);
+  if (pl.f4) MOE_CHECK_CUDA(launch_pdl(mx_pack_x4_kernel, pgrid, dim3(256), 0, st, p, pk));
+  else if (pl.split > 1) MOE_CHECK_CUDA(launch_pdl(mx_pack_x_kernel<true>, pgrid, dim3(256), 0, st, p, pk));
+  else MOE_CHECK_CUDA(launch_pdl(mx_pack_x_kernel<false>, pgrid, dim3(256), 0, st, p, pk));
   MOE_CHECK_LAUNCH();
 
   MxParams q;

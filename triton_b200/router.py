@@ -11,20 +11,6 @@ from .tensor import BIT, SparseMatrix, wrap_torch_tensor
 from .topk import topk
 
 
-_ws_cache = {}
-
-
-def _workspace(dev, nbytes):
-    """Scratch for the K slices of small batches.  The kernel wants it zero and leaves it zero, so it is cleared when it
-    is allocated and then reused: one buffer per (device, stream), grown on demand."""
-    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
-    ws = _ws_cache.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=dev)
-        _ws_cache[key] = ws
-    return ws
-
-
 def prepare_router_weight(wg: torch.Tensor) -> torch.Tensor:
     """-> Wg as the kernel reads it: logical shape [K, E] kept, memory [E, K] with K contiguous (stride(0) == 1).
     A weight that already has that memory order is returned as it is; do this once per layer, not per step."""
@@ -41,6 +27,11 @@ def router_topk_supported(x, wg, k) -> bool:
             and wg.data_ptr() % 16 == 0)
 
 
+def _two_steps(logits, k, apply_softmax, return_logits):
+    sp = topk(logits, k, apply_softmax=apply_softmax)
+    return (sp, logits.float()) if return_logits else sp
+
+
 def router_topk(x: torch.Tensor, wg: torch.Tensor, bg, k: int, apply_softmax: bool = True, logits_dtype=None,
                 return_logits: bool = False):
     """SparseMatrix of `topk(x @ wg + bg, k, apply_softmax)` (and the fp32 logits when `return_logits`).
@@ -55,8 +46,7 @@ def router_topk(x: torch.Tensor, wg: torch.Tensor, bg, k: int, apply_softmax: bo
     wg = prepare_router_weight(wg)
     if not router_topk_supported(x, wg, k):
         logits = (x.float() @ wg.float() + (0 if bg is None else bg.float())).to(logits_dtype)
-        sp = topk(logits, k, apply_softmax=apply_softmax)
-        return (sp, logits.float()) if return_logits else sp
+        return _two_steps(logits, k, apply_softmax, return_logits)
     lib = _lib.load()
     T, K = x.shape
     E = wg.shape[1]
@@ -68,7 +58,11 @@ def router_topk(x: torch.Tensor, wg: torch.Tensor, bg, k: int, apply_softmax: bo
     bm = bm_store.transpose(0, 1)[:T]
     logits = torch.empty((T, E), dtype=torch.float32, device=dev) if return_logits else None
     ws_bytes = lib.moe_router_topk_workspace_bytes(T, K, E)
-    ws = _workspace(dev, ws_bytes)
+    ws = _lib.zero_scratch(dev, ws_bytes) if ws_bytes > 0 else None
+    if ws_bytes > 0 and ws is None:
+        # no zeroed scratch to be had now (first use inside a graph capture): the two steps apart
+        logits = torch.addmm(bg.to(x.dtype), x, wg) if bg is not None else x @ wg
+        return _two_steps(logits.to(logits_dtype), k, apply_softmax, return_logits)
     if bg is not None and bg.dtype not in (torch.float32, torch.bfloat16):
         bg = bg.float()
     if T > 0:
@@ -76,7 +70,8 @@ def router_topk(x: torch.Tensor, wg: torch.Tensor, bg, k: int, apply_softmax: bo
                                        _lib.dtype_code(bg.dtype) if bg is not None else 0, E, k, int(bool(apply_softmax)),
                                        int(logits_dtype == torch.bfloat16), _lib.ptr(logits), E, _lib.ptr(vals),
                                        _lib.dtype_code(vals.dtype), vals.stride(0), _lib.ptr(indx), indx.stride(0), _lib.ptr(bm),
-                                       bm.stride(0), bm.stride(1), _lib.ptr(ws), ws_bytes, _status_word(dev).data_ptr(),
+                                       bm.stride(0), bm.stride(1), _lib.ptr(ws), ws_bytes if ws is not None else 0,
+                                       _status_word(dev).data_ptr(),
                                        _lib.stream()), "moe_router_topk")
     bitmatrix = wrap_torch_tensor(bm, dtype=BIT, shape=[T, E], shape_max=[T, None])
     sp = SparseMatrix(indx=indx, vals=vals, mask=bitmatrix)
