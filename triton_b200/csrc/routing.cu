@@ -119,20 +119,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) topk_kernel(
 // four lanes share the bitmatrix words.  With HIST the block (256 rows) also counts its picks per expert into
 // partial[block][e], the first pass of the expert sort.  The warp-per-row kernel above spends its time in k rounds of
 // 64-bit warp reductions per row: 19.6 us for 16384 x 128 logits against about 5 us here.
-template <typename T, int K, bool HIST>
-__global__ void __launch_bounds__(HIST ? 1024 : 256) topk_quad_kernel(
-    const T* __restrict__ logits, int64_t ld_logits, int64_t T_rows, int E, int apply_softmax, T* __restrict__ vals,
-    int64_t ld_vals, int16_t* __restrict__ indx, int64_t ld_indx, uint32_t* __restrict__ bitmatrix, int64_t bm_stride_row,
-    int64_t bm_stride_word, int32_t* __restrict__ partial) {
-  extern __shared__ int32_t s_hist[];                     // [E] with HIST
-  if constexpr (HIST) {
-    for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
-    __syncthreads();
-  }
-  const int part = threadIdx.x & 3;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 2) + (threadIdx.x >> 2);
-  const bool live = row < T_rows;
-  const T* x = logits + (live ? row : 0) * ld_logits;      // rows past the end walk row 0 and store nothing
+template <typename T, int K>
+__device__ __forceinline__ TopK<K> quad_select(const T* __restrict__ x, int E, int part) {
   constexpr int NL = K <= 4 ? 2 : 1;
   TopK<K> sub[NL];
   for (int c0 = part; c0 * 4 < E; c0 += 4 * NL) {
@@ -158,37 +146,64 @@ __global__ void __launch_bounds__(HIST ? 1024 : 256) topk_quad_kernel(
 #pragma unroll
     for (int i = 0; i < K; ++i) tk.push_any(sub[u].key[i], sub[u].idx[i]);
   tk.merge_lanes(4);
-  if (live) {
-    if (part == 0) {
-      float v[K];
+  return tk;
+}
+
+// values (softmax over the picks), indices, bitmatrix words of one row; `hist` (shared memory, may be NULL) counts the picks
+template <typename T, int K>
+__device__ __forceinline__ void quad_store(const TopK<K>& tk, int part, int64_t row, int E, int apply_softmax, T* __restrict__ vals,
+                                           int64_t ld_vals, int16_t* __restrict__ indx, int64_t ld_indx,
+                                           uint32_t* __restrict__ bitmatrix, int64_t bm_stride_row, int64_t bm_stride_word,
+                                           int32_t* hist) {
+  if (part == 0) {
+    float v[K];
 #pragma unroll
-      for (int i = 0; i < K; ++i) v[i] = sel_key_float(tk.key[i]);
-      if (apply_softmax) {
-        float mx = -INFINITY;
+    for (int i = 0; i < K; ++i) v[i] = sel_key_float(tk.key[i]);
+    if (apply_softmax) {
+      float mx = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < K; ++i) mx = fmaxf(mx, v[i]);
-        float sum = 0.0f;
+      for (int i = 0; i < K; ++i) mx = fmaxf(mx, v[i]);
+      float sum = 0.0f;
 #pragma unroll
-        for (int i = 0; i < K; ++i) sum += expf(v[i] - mx);
+      for (int i = 0; i < K; ++i) sum += expf(v[i] - mx);
 #pragma unroll
-        for (int i = 0; i < K; ++i) v[i] = __fdiv_rn(expf(v[i] - mx), sum);
-      }
-#pragma unroll
-      for (int i = 0; i < K; ++i) {
-        vals[row * ld_vals + i] = from_f32<T>(v[i]);
-        indx[row * ld_indx + i] = (int16_t)tk.idx[i];
-        if constexpr (HIST) atomicAdd(&s_hist[tk.idx[i]], 1);
-      }
+      for (int i = 0; i < K; ++i) v[i] = __fdiv_rn(expf(v[i] - mx), sum);
     }
-    const int words = (E + 31) >> 5;
-    for (int w = part; w < words; w += 4) {
-      uint32_t bits = 0;
 #pragma unroll
-      for (int i = 0; i < K; ++i)
-        if ((tk.idx[i] >> 5) == w) bits |= 1u << (tk.idx[i] & 31);
-      bitmatrix[row * bm_stride_row + (int64_t)w * bm_stride_word] = bits;
+    for (int i = 0; i < K; ++i) {
+      vals[row * ld_vals + i] = from_f32<T>(v[i]);
+      indx[row * ld_indx + i] = (int16_t)tk.idx[i];
+      if (hist) atomicAdd(&hist[tk.idx[i]], 1);
     }
   }
+  const int words = (E + 31) >> 5;
+  for (int w = part; w < words; w += 4) {
+    uint32_t bits = 0;
+#pragma unroll
+    for (int i = 0; i < K; ++i)
+      if ((tk.idx[i] >> 5) == w) bits |= 1u << (tk.idx[i] & 31);
+    bitmatrix[row * bm_stride_row + (int64_t)w * bm_stride_word] = bits;
+  }
+}
+
+template <typename T, int K, bool HIST>
+__global__ void __launch_bounds__(HIST ? 1024 : 256) topk_quad_kernel(
+    const T* __restrict__ logits, int64_t ld_logits, int64_t T_rows, int E, int apply_softmax, T* __restrict__ vals,
+    int64_t ld_vals, int16_t* __restrict__ indx, int64_t ld_indx, uint32_t* __restrict__ bitmatrix, int64_t bm_stride_row,
+    int64_t bm_stride_word, int32_t* __restrict__ partial) {
+  extern __shared__ int32_t s_hist[];                     // [E] with HIST
+  if constexpr (HIST) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+    __syncthreads();
+  }
+  const int part = threadIdx.x & 3;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 2) + (threadIdx.x >> 2);
+  const bool live = row < T_rows;
+  const T* x = logits + (live ? row : 0) * ld_logits;      // rows past the end walk row 0 and store nothing
+  const TopK<K> tk = quad_select<T, K>(x, E, part);
+  if (live)
+    quad_store<T, K>(tk, part, row, E, apply_softmax, vals, ld_vals, indx, ld_indx, bitmatrix, bm_stride_row, bm_stride_word,
+                     HIST ? s_hist : nullptr);
   if constexpr (HIST) {
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) partial[(int64_t)blockIdx.x * E + e] = s_hist[e];
@@ -299,18 +314,16 @@ __global__ void __launch_bounds__(1024) bm_scan_kernel(int32_t* __restrict__ par
   }
 }
 
-__global__ void __launch_bounds__(256) bm_rank_kernel(const int16_t* __restrict__ indx, int64_t ld_indx, int64_t T_rows,
-                                                      int E, int k, const int32_t* __restrict__ n_rows_dev,
-                                                      const int32_t* __restrict__ partial,
-                                                      const int32_t* __restrict__ col_offs,
-                                                      int32_t* __restrict__ col_sorted, int32_t* __restrict__ row_sorted) {
-  extern __shared__ int32_t s_cnt[];  // [warps][E]; a block covers blockDim.x tokens, the blocks of `partial`
+// Positions of the entries of one block of blockDim.x tokens starting at token `tok_base`: `base[e]` is where the
+// block's entries of expert e start (expert offset + entries of earlier blocks); s_cnt holds [warps][E] counters.
+__device__ __forceinline__ void rank_block(const int16_t* __restrict__ indx, int64_t ld_indx, int64_t T_rows, int E, int k,
+                                           int64_t n_rows, const int32_t* base_a, const int32_t* base_b, int64_t tok_base,
+                                           int32_t* __restrict__ col_sorted, int32_t* __restrict__ row_sorted, int32_t* s_cnt) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const int64_t n_rows = n_rows_dev ? min((int64_t)*n_rows_dev, T_rows) : T_rows;
   int32_t* my = s_cnt + (int64_t)warp * E;
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_cnt[i] = 0;
   __syncthreads();
-  const int64_t tok0 = (int64_t)blockIdx.x * blockDim.x + warp * 32;
+  const int64_t tok0 = tok_base + warp * 32;
   const int n_ent = 32 * k;
   // count the entries of this warp's 32 tokens
   for (int j = lane; j < n_ent; j += 32) {
@@ -320,7 +333,7 @@ __global__ void __launch_bounds__(256) bm_rank_kernel(const int16_t* __restrict_
   __syncthreads();
   // turn the per-warp counts into starting offsets: base + counts of the warps before this one
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run = partial[(int64_t)blockIdx.x * E + e] + col_offs[e];
+    int run = (base_a ? base_a[e] : 0) + base_b[e];
     for (int w = 0; w < nwarps; ++w) {
       int v = s_cnt[w * E + e];
       s_cnt[w * E + e] = run;
@@ -348,6 +361,17 @@ __global__ void __launch_bounds__(256) bm_rank_kernel(const int16_t* __restrict_
       col_sorted[pos] = (int32_t)flat;
     }
   }
+}
+
+__global__ void __launch_bounds__(256) bm_rank_kernel(const int16_t* __restrict__ indx, int64_t ld_indx, int64_t T_rows,
+                                                      int E, int k, const int32_t* __restrict__ n_rows_dev,
+                                                      const int32_t* __restrict__ partial,
+                                                      const int32_t* __restrict__ col_offs,
+                                                      int32_t* __restrict__ col_sorted, int32_t* __restrict__ row_sorted) {
+  extern __shared__ int32_t s_cnt[];  // [warps][E]; a block covers blockDim.x tokens, the blocks of `partial`
+  const int64_t n_rows = n_rows_dev ? min((int64_t)*n_rows_dev, T_rows) : T_rows;
+  rank_block(indx, ld_indx, T_rows, E, k, n_rows, partial + (int64_t)blockIdx.x * E, col_offs, (int64_t)blockIdx.x * blockDim.x,
+             col_sorted, row_sorted, s_cnt);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -563,7 +587,8 @@ extern "C" __attribute__((visibility("default"))) int moe_ragged_metadata_remap(
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// moe_route: the whole routing step in three launches (the standalone entry points above take five).
+// moe_route: the whole routing step in three launches (the standalone entry points above take five); batches of up to
+// 256 tokens in one (route_small_kernel, at the end of this section).
 //   A  topk_quad_kernel<HIST>   top-k + softmax + bitmatrix row of every token, and the expert histogram of each block
 //      (route_topk_hist_kernel  of 128 tokens (partial[blk][e]) in the same pass over the logits;
 //       for other k)
@@ -660,6 +685,42 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_topk_hist_kernel(
   for (int e = threadIdx.x; e < E; e += blockDim.x) partial[(int64_t)blockIdx.x * E + e] = s_hist[e];
 }
 
+// One row of the ragged metadata from the slice sizes in shared memory (s_size[0..E), s_size[E] = 0): row 0 =
+// slice_offs (= expert offsets, also written to col_offs when given), rows 1..4 = block_offs and block schedule of the
+// block sizes 16..128.  All threads of the block call it.
+__device__ void ragged_row(int row, const int32_t* s_size, int E, int32_t* s_nb, int32_t* s_offs, int32_t* s_warp,
+                           int32_t* __restrict__ slice_offs, int32_t* __restrict__ col_offs, int32_t* __restrict__ block_offs,
+                           int64_t ld_block_offs, int32_t* __restrict__ block_sched, int64_t ld_sched, int64_t n_sched) {
+  const int log2bs = row == 0 ? 0 : row + 3;
+  for (int i = threadIdx.x; i <= E; i += blockDim.x)
+    s_nb[i] = (i < E) ? (int32_t)(((int64_t)s_size[i] + ((1 << log2bs) - 1)) >> log2bs) : 0;
+  __syncthreads();
+  block_exclusive_scan(s_nb, s_offs, E + 1, s_warp);
+  __syncthreads();
+  int32_t* dst = row == 0 ? slice_offs : block_offs + (int64_t)(row - 1) * ld_block_offs;
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) {
+    dst[i] = s_offs[i];
+    if (row == 0 && i < E && col_offs) col_offs[i] = s_offs[i];
+  }
+  if (row > 0) {
+    const int32_t tot = s_offs[E];
+    int32_t* sched = block_sched + (int64_t)(row - 1) * ld_sched;
+    for (int64_t p = threadIdx.x; p < n_sched; p += blockDim.x) {
+      int32_t v = -1;
+      if (p < tot) {
+        int lo = 0, hi = E;  // largest e with offs[e] <= p
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (s_offs[mid] <= p) lo = mid; else hi = mid;
+        }
+        v = (int32_t)(((uint32_t)(p - s_offs[lo]) << 16) | (uint32_t)lo);
+      }
+      sched[p] = v;
+    }
+  }
+  __syncthreads();
+}
+
 // Six blocks of 1024 threads.  n_experts <= 1024.
 __global__ void __launch_bounds__(1024) route_scan_ragged_kernel(const int32_t* __restrict__ partial_in,
                                                                  int32_t* __restrict__ partial_out, int64_t n_blocks, int E,
@@ -734,38 +795,53 @@ __global__ void __launch_bounds__(1024) route_scan_ragged_kernel(const int32_t* 
   __syncthreads();
   if (role == 0) return;
   // ---- 2. expert offsets, then the ragged metadata: row 0 = slice_offs (= col_offs), rows 1..4 = block sizes 16..128 --
-  {
-    const int row = role - 1;
-    const int log2bs = row == 0 ? 0 : row + 3;
-    for (int i = threadIdx.x; i <= E; i += blockDim.x)
-      s_nb[i] = (i < E) ? (int32_t)(((int64_t)s_size[i] + ((1 << log2bs) - 1)) >> log2bs) : 0;
-    __syncthreads();
-    block_exclusive_scan(s_nb, s_offs, E + 1, s_warp);
-    __syncthreads();
-    int32_t* dst = row == 0 ? slice_offs : block_offs + (int64_t)(row - 1) * ld_block_offs;
-    for (int i = threadIdx.x; i <= E; i += blockDim.x) {
-      dst[i] = s_offs[i];
-      if (row == 0 && i < E) col_offs[i] = s_offs[i];
-    }
-    if (row > 0) {
-      const int32_t tot = s_offs[E];
-      int32_t* sched = block_sched + (int64_t)(row - 1) * ld_sched;
-      for (int64_t p = threadIdx.x; p < n_sched; p += blockDim.x) {
-        int32_t v = -1;
-        if (p < tot) {
-          int lo = 0, hi = E;  // largest e with offs[e] <= p
-          while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (s_offs[mid] <= p) lo = mid; else hi = mid;
-          }
-          v = (int32_t)(((uint32_t)(p - s_offs[lo]) << 16) | (uint32_t)lo);
-        }
-        sched[p] = v;
-      }
-    }
-    __syncthreads();
-  }
+  ragged_row(role - 1, s_size, E, s_nb, s_offs, s_warp, slice_offs, col_offs, block_offs, ld_block_offs, block_sched, ld_sched,
+             n_sched);
 }
+
+// The whole routing step of a small batch (at most 256 tokens, at most 256 experts, k in {1, 2, 4, 8, 16}) in ONE launch
+// of one block of 1024 threads: top-k with four lanes per row, the expert histogram in shared memory, the expert offsets,
+// the positions of the entries and the five rows of the ragged metadata, with block barriers where the three-launch
+// form has kernel boundaries.  A decode step is bound by its launch count: this takes two launches off it.
+template <typename T, int K>
+__global__ void __launch_bounds__(1024) route_small_kernel(
+    const T* __restrict__ logits, int64_t ld_logits, int64_t T_rows, int E, int apply_softmax, T* __restrict__ vals,
+    int64_t ld_vals, int16_t* __restrict__ indx, int64_t ld_indx, uint32_t* __restrict__ bitmatrix, int64_t bm_stride_row,
+    int64_t bm_stride_word, int32_t* __restrict__ col_sum, int32_t* __restrict__ col_sorted, int32_t* __restrict__ row_sorted,
+    int32_t* __restrict__ slice_offs, int32_t* __restrict__ block_offs, int64_t ld_block_offs, int32_t* __restrict__ block_sched,
+    int64_t ld_sched, int64_t n_sched) {
+  extern __shared__ int32_t s_mem[];            // [E + 1] sizes, [E + 1] scan input, [E + 1] offsets, [E] expert offsets, [32][E] counters
+  __shared__ int32_t s_warp[33];
+  int32_t* s_size = s_mem;
+  int32_t* s_nb = s_size + (E + 1);
+  int32_t* s_offs = s_nb + (E + 1);
+  int32_t* s_col = s_offs + (E + 1);
+  int32_t* s_cnt = s_col + E;
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) s_size[e] = 0;
+  __syncthreads();
+  {
+    const int part = threadIdx.x & 3;
+    const int64_t row = threadIdx.x >> 2;
+    const bool live = row < T_rows;
+    const T* x = logits + (live ? row : 0) * ld_logits;
+    const TopK<K> tk = quad_select<T, K>(x, E, part);
+    if (live)
+      quad_store<T, K>(tk, part, row, E, apply_softmax, vals, ld_vals, indx, ld_indx, bitmatrix, bm_stride_row, bm_stride_word,
+                       s_size);
+  }
+  __syncthreads();                               // the picks are in global memory and counted
+  for (int e = threadIdx.x; e < E; e += blockDim.x) col_sum[e] = s_size[e];
+  // row 0 first: the expert offsets the positions need (kept in shared memory: ragged_row reuses s_offs)
+  ragged_row(0, s_size, E, s_nb, s_offs, s_warp, slice_offs, nullptr, block_offs, ld_block_offs, block_sched, ld_sched, n_sched);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_col[e] = s_offs[e];
+  __syncthreads();
+  rank_block(indx, ld_indx, T_rows, E, K, T_rows, nullptr, s_col, 0, col_sorted, row_sorted, s_cnt);
+  __syncthreads();
+  for (int row = 1; row < 5; ++row)
+    ragged_row(row, s_size, E, s_nb, s_offs, s_warp, slice_offs, nullptr, block_offs, ld_block_offs, block_sched, ld_sched, n_sched);
+}
+
+constexpr int kRouteSmallTokens = 256;
 
 }  // namespace
 
@@ -792,6 +868,26 @@ extern "C" __attribute__((visibility("default"))) int moe_route(
   MOE_CHECK_ARG(workspace_bytes >= moe_route_workspace(T, E, k), "moe_route: workspace too small (%zu < %zu)", workspace_bytes,
                 moe_route_workspace(T, E, k));
   cudaStream_t st = (cudaStream_t)stream;
+  if (T <= kRouteSmallTokens && (k == 1 || k == 2 || k == 4 || k == 8 || k == 16)) {
+    const size_t smem_s = (size_t)(3 * (E + 1) + E + 32 * E) * sizeof(int32_t);
+#define MOE_ROUTE_SMALL(KK)                                                                                              \
+  MOE_DISPATCH_FLOAT(dtype, Tv, {                                                                                         \
+    route_small_kernel<Tv, KK><<<1, 1024, smem_s, st>>>((const Tv*)logits, ld_logits, T, E, apply_softmax, (Tv*)vals, ld_vals, \
+                                                         indx, ld_indx, bitmatrix, bm_stride_row, bm_stride_word, col_sum,  \
+                                                         col_sorted, row_sorted, slice_offs, block_offs, ld_block_offs,     \
+                                                         block_sched, ld_sched, n_sched);                                   \
+  })
+    switch (k) {
+      case 1: MOE_ROUTE_SMALL(1); break;
+      case 2: MOE_ROUTE_SMALL(2); break;
+      case 4: MOE_ROUTE_SMALL(4); break;
+      case 8: MOE_ROUTE_SMALL(8); break;
+      default: MOE_ROUTE_SMALL(16); break;
+    }
+#undef MOE_ROUTE_SMALL
+    MOE_CHECK_LAUNCH();
+    return MOE_OK;
+  }
   const int64_t nb = cdiv64(T, kRouteTokPerBlock);
   int32_t* partial = (int32_t*)workspace;          // counts per block of tokens, their running offsets, expert offsets
   int32_t* scanned = partial + nb * E;
