@@ -243,7 +243,10 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t c) {
 }
 // e8m0 byte s with 2^(s-127) >= amax / 6, and the exact factors 2^(s-127), 2^(127-s)
 __device__ __forceinline__ void mx4_scale(float amax, uint32_t& sb, float& scale, float& inv) {
-  const float ds = __fdiv_rn(amax, 6.0f);
+  // amax / 6 rounded UP to a power of two; the product with a constant just above 1/6 is never below the quotient, so
+  // every value of the group still fits (it doubles the scale where amax is within an ulp of 6 * 2^e, which costs nothing
+  // that matters here) and the division is off the chain
+  const float ds = amax * 0.16666668f;
   uint32_t u = (__float_as_uint(ds) + 0x007FFFFFu) & 0x7F800000u;
   sb = u >> 23;
   if (amax == 0.0f) sb = 127u;
@@ -252,6 +255,9 @@ __device__ __forceinline__ void mx4_scale(float amax, uint32_t& sb, float& scale
   inv = __uint_as_float((254u - sb) << 23);
 }
 
+// (A warp per (token block, k step, four rows) with the rows' chains side by side, and dead warps grouped into whole
+// CTAs, was tried in place of the loop over rows below: 2.3 x slower.  A row's four-term chain is latency, and four of
+// them in one warp add up where eight warps of a CTA overlap them.)
 __global__ void __launch_bounds__(256) mx_pack_x4_kernel(const GemmParams p, const PackParams a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -276,9 +282,10 @@ __global__ void __launch_bounds__(256) mx_pack_x4_kernel(const GemmParams p, con
     }
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
+      // maximum of the 32-group: the 8 lanes that hold it reduce the bit patterns of their |values| (non-negative floats
+      // order like unsigned integers; NaN patterns rank above Inf and are caught below)
       float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-#pragma unroll
-      for (int o = 1; o <= 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+      amax = __uint_as_float(__reduce_max_sync(0xFFu << (lane & 24), __float_as_uint(amax)));
       if (!(amax < 3.0e38f)) amax = t == 0 ? 3.0e38f : 0.0f;       // Inf / NaN in the group: keep the scales finite
       uint32_t sb; float s, inv;
       mx4_scale(amax, sb, s, inv);

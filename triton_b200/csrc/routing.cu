@@ -588,7 +588,7 @@ extern "C" __attribute__((visibility("default"))) int moe_ragged_metadata_remap(
 
 // ---------------------------------------------------------------------------------------------------------
 // moe_route: the whole routing step in three launches (the standalone entry points above take five); batches of up to
-// 256 tokens in one (route_small_kernel, at the end of this section).
+// 256 tokens in one launch of five independent blocks (route_small_kernel, at the end of this section).
 //   A  topk_quad_kernel<HIST>   top-k + softmax + bitmatrix row of every token, and the expert histogram of each block
 //      (route_topk_hist_kernel  of 128 tokens (partial[blk][e]) in the same pass over the logits;
 //       for other k)
@@ -800,9 +800,11 @@ __global__ void __launch_bounds__(1024) route_scan_ragged_kernel(const int32_t* 
 }
 
 // The whole routing step of a small batch (at most 256 tokens, at most 256 experts, k in {1, 2, 4, 8, 16}) in ONE launch
-// of one block of 1024 threads: top-k with four lanes per row, the expert histogram in shared memory, the expert offsets,
-// the positions of the entries and the five rows of the ragged metadata, with block barriers where the three-launch
-// form has kernel boundaries.  A decode step is bound by its launch count: this takes two launches off it.
+// of five blocks of 1024 threads that do not wait on one another: every block selects the top-k of every row for itself
+// (four lanes per row; 128 KB of logits at most) and counts the picks; block 0 stores the selection, the expert offsets
+// (ragged row 0) and the positions of the entries, blocks 1..4 each build the block_offs row and the schedule of one
+// block size.  Repeating the selection five times costs less than what it replaces: a chain of kernel boundaries
+// (three launches) or of block barriers (one block doing all five rows took 20 us at 64 tokens).
 template <typename T, int K>
 __global__ void __launch_bounds__(1024) route_small_kernel(
     const T* __restrict__ logits, int64_t ld_logits, int64_t T_rows, int E, int apply_softmax, T* __restrict__ vals,
@@ -817,6 +819,7 @@ __global__ void __launch_bounds__(1024) route_small_kernel(
   int32_t* s_offs = s_nb + (E + 1);
   int32_t* s_col = s_offs + (E + 1);
   int32_t* s_cnt = s_col + E;
+  const int role = blockIdx.x;
   for (int e = threadIdx.x; e <= E; e += blockDim.x) s_size[e] = 0;
   __syncthreads();
   {
@@ -825,20 +828,26 @@ __global__ void __launch_bounds__(1024) route_small_kernel(
     const bool live = row < T_rows;
     const T* x = logits + (live ? row : 0) * ld_logits;
     const TopK<K> tk = quad_select<T, K>(x, E, part);
-    if (live)
-      quad_store<T, K>(tk, part, row, E, apply_softmax, vals, ld_vals, indx, ld_indx, bitmatrix, bm_stride_row, bm_stride_word,
-                       s_size);
+    if (live) {
+      if (role == 0) {
+        quad_store<T, K>(tk, part, row, E, apply_softmax, vals, ld_vals, indx, ld_indx, bitmatrix, bm_stride_row,
+                         bm_stride_word, s_size);
+      } else if (part == 0) {
+#pragma unroll
+        for (int i = 0; i < K; ++i) atomicAdd(&s_size[tk.idx[i]], 1);
+      }
+    }
   }
-  __syncthreads();                               // the picks are in global memory and counted
+  __syncthreads();                               // the picks are counted (block 0: and in global memory)
+  if (role > 0) {
+    ragged_row(role, s_size, E, s_nb, s_offs, s_warp, slice_offs, nullptr, block_offs, ld_block_offs, block_sched, ld_sched, n_sched);
+    return;
+  }
   for (int e = threadIdx.x; e < E; e += blockDim.x) col_sum[e] = s_size[e];
-  // row 0 first: the expert offsets the positions need (kept in shared memory: ragged_row reuses s_offs)
   ragged_row(0, s_size, E, s_nb, s_offs, s_warp, slice_offs, nullptr, block_offs, ld_block_offs, block_sched, ld_sched, n_sched);
   for (int e = threadIdx.x; e < E; e += blockDim.x) s_col[e] = s_offs[e];
   __syncthreads();
   rank_block(indx, ld_indx, T_rows, E, K, T_rows, nullptr, s_col, 0, col_sorted, row_sorted, s_cnt);
-  __syncthreads();
-  for (int row = 1; row < 5; ++row)
-    ragged_row(row, s_size, E, s_nb, s_offs, s_warp, slice_offs, nullptr, block_offs, ld_block_offs, block_sched, ld_sched, n_sched);
 }
 
 constexpr int kRouteSmallTokens = 256;
@@ -872,7 +881,7 @@ extern "C" __attribute__((visibility("default"))) int moe_route(
     const size_t smem_s = (size_t)(3 * (E + 1) + E + 32 * E) * sizeof(int32_t);
 #define MOE_ROUTE_SMALL(KK)                                                                                              \
   MOE_DISPATCH_FLOAT(dtype, Tv, {                                                                                         \
-    route_small_kernel<Tv, KK><<<1, 1024, smem_s, st>>>((const Tv*)logits, ld_logits, T, E, apply_softmax, (Tv*)vals, ld_vals, \
+    route_small_kernel<Tv, KK><<<5, 1024, smem_s, st>>>((const Tv*)logits, ld_logits, T, E, apply_softmax, (Tv*)vals, ld_vals, \
                                                          indx, ld_indx, bitmatrix, bm_stride_row, bm_stride_word, col_sum,  \
                                                          col_sorted, row_sorted, slice_offs, block_offs, ld_block_offs,     \
                                                          block_sched, ld_sched, n_sched);                                   \
