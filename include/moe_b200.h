@@ -86,10 +86,10 @@ int moe_bitmatrix_metadata(const int16_t* indx, int64_t ld_indx, int64_t T, int 
                            const int32_t* n_rows_dev, int32_t* col_sum, int32_t* col_sorted,
                            int32_t* row_sorted, void* workspace, size_t workspace_bytes, void* stream);
 
-/* The whole routing step of a layer in three launches: moe_topk_fwd + moe_bitmatrix_metadata + moe_ragged_metadata
- * (topk.py:106-141 -> tensor.py:202-209 -> ragged_tensor.py:183-210 of the reference, what its test helper `routing`
- * composes, tests/test_distributed.py:203-210) with the expert histogram taken in the top-k pass and the ragged
- * metadata computed by the block that scans the histogram.  Every one of the T rows is valid (no device-side row
+/* The whole routing step of a layer in three launches (one for up to 256 tokens): moe_topk_fwd +
+ * moe_bitmatrix_metadata + moe_ragged_metadata (topk.py:106-141 -> tensor.py:202-209 -> ragged_tensor.py:183-210 of the
+ * reference, what its test helper `routing` composes, tests/test_distributed.py:203-210) with the expert histogram taken
+ * in the top-k pass and the ragged metadata built beside the scan of the histograms.  Every one of the T rows is valid (no device-side row
  * bound, no provided indices); n_expts <= 256, otherwise MOE_ERR_UNSUPPORTED and the caller uses the separate entry
  * points.  Outputs as for those entry points; workspace of moe_route_workspace(T, n_expts, k) bytes.               */
 size_t moe_route_workspace(int64_t T, int E, int k);
@@ -240,8 +240,9 @@ typedef struct {
                                                       TMA instead of gathering 16 bytes at a time.  NULL: gather in-kernel. */
   /* block-scaled kernel (w_kind MOE_W_MX4_B200MX; matmul.py:130-132, 311-336 of the reference: a_mx_scale / fp8
      activations against MXFP4 weights).  x_dtype MOE_F8E4M3 takes e4m3 rows as they are, with x_scale (e8m0,
-     [rows_x, K / 32], row pitch ld_x_scale bytes) for MXFP8 or NULL for unit scales; x_dtype MOE_BF16 is split into
-     two e4m3 terms inside the library.  mx_workspace holds the re-laid-out token blocks:
+     [rows_x, K / 32], row pitch ld_x_scale bytes) for MXFP8 or NULL for unit scales; x_dtype MOE_BF16 is split inside
+     the library into two e4m3 terms (kind::mxf8f6f4) or, for token blocks of 16 rows, four e2m1 terms (kind::mxf4);
+     MOE_GEMM_MX_F8 / MOE_GEMM_MX_F4 pin the form.  mx_workspace holds the re-laid-out token blocks:
      moe_gemm_mx_workspace_bytes(args) bytes, 1024-byte aligned.  For this kernel tile_m is the token block
      (0 auto, 16, 32, 64, 128) and tile_n 128 / 384 pins one / three weight blocks per CTA tile.                 */
   const uint8_t* x_scale; int64_t ld_x_scale;
