@@ -271,3 +271,28 @@ def test_layer_with_e4m3_activations_against_oracle(tokens, device):
     oracle.assert_close_oracle(ref, got, maxtol=MAXTOL_MX4, rmstol=None, what="fp8 layer")
     assert oracle.rel_l2(ref, got) < 1e-2
 
+
+@pytest.mark.parametrize("K", [384, 640, 2880])
+@pytest.mark.parametrize("sizes", [[3, 0, 1, 16, 0, 7], [1], [16, 16, 5, 2], [20, 1, 0, 33]])
+@pytest.mark.parametrize("act", [False, True])
+def test_block_scaled_few_tiles_k_step_stages(K, sizes, act, device):
+    """Decode-sized calls with so few tiles that a CTA gets single weight blocks: the kernel then puts three k steps of
+    one block into a stage (K = 384: exactly one stage; 640: a full and a partial one; 2880: seven and a partial one)."""
+    g = torch.Generator().manual_seed(K + len(sizes) * 7 + int(act))
+    E, N = len(sizes), 640
+    sizes_t = torch.tensor(sizes, dtype=torch.int32)
+    M = int(sizes_t.sum())
+    wq, ws, wdeq = quantised_weights(E, K, N, g)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    bias = torch.randn(E, N, generator=g) * 0.1
+    gammas = torch.rand(M, generator=g)
+    scatter = torch.randperm(M, generator=g).int()
+    a = (1.702, 7.0) if act else None
+    ref = oracle.matmul_oracle(x.float(), wdeq, bias, sizes_t, None, None, gammas=None if act else gammas, out_dtype=torch.float32)
+    if act:
+        ref = oracle.swiglu_oracle(ref, *a) * gammas[:, None]
+    out = torch.zeros_like(ref)
+    out[scatter.long()] = ref
+    y = run_mx(x, wq, ws, sizes_t, device, bias=bias, scatter=scatter, gammas=gammas, act=a, out_dtype=torch.float32,
+               kernel="mx-f4", block_m=16)
+    assert oracle.rel_l2(out, y) < 5e-4

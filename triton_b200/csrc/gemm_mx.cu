@@ -355,20 +355,28 @@ __device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t adesc, ui
 // The GEMM kernel
 // ============================================================================================================
 // F4: the four-term form (packed operands, kind::mxf4); otherwise byte-per-element operands, kind::mxf8f6f4
-template <typename TY, int MB, bool F4>
+// KM (four-term form, MB = 3): the three weight tiles of a stage are three consecutive K STEPS of ONE weight block instead of
+// one k step of three blocks -- for steps with so few tiles that a CTA gets single weight blocks (one to four tokens: 60
+// to 165 three-block tiles for 148 SMs).  A stage of one 8 KB tile cannot keep a per-SM copy pipeline busy (a ring of
+// 8 KB stages streams 3.3 TB/s over the GPU however many are in flight, 24 KB stages 7.1 TB/s).
+template <typename TY, int MB, bool F4, bool KM = false>
 __global__ void __launch_bounds__(MX_THREADS, 1)
 gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxMaps w_maps) {
+  static_assert(!KM || (F4 && MB == 3), "the k-step form is built for the four-term kernel with three tiles per stage");
   constexpr uint32_t W_TILE = F4 ? MX_W_TILE_TX : MX_W_TILE;       // bytes of a weight block in shared memory
   constexpr uint32_t X_ROW = F4 ? 64u : 128u;                      // bytes of a token row of a k step
+  constexpr int NACC = KM ? 1 : MB;                                // accumulators (weight blocks) of a tile
+  constexpr int SF_COLS = KM ? 24 : MX_SF_COLS;                    // scale columns of a stage: KM has three token chunks
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int STAGES = q.stages;
-  // per stage: [MB weight blocks][token rows + 1024 B scale area][MB x 512 B weight scales]
+  // per stage: [MB weight tiles][token rows + 1024 B scale area (KM: three such chunks)][MB x 512 B weight scales]
   const uint32_t OFF_X = MB * W_TILE;
   const uint32_t OFF_XS = OFF_X + (uint32_t)q.n_mma * X_ROW;
-  const uint32_t OFF_WS = OFF_XS + 1024u;
+  const uint32_t OFF_WS = KM ? OFF_X + 3u * (uint32_t)q.chunk_bytes : OFF_XS + 1024u;
+  const uint32_t SF_BASE = KM ? 512u - (uint32_t)(MX_MAX_STAGES > 5 ? 5 : MX_MAX_STAGES) * 24u : (uint32_t)MX_SF_BASE;
   const uint32_t ctl0 = sbase + (uint32_t)STAGES * (uint32_t)q.stage_bytes;
   auto BAR_FULL = [&](int s) { return ctl0 + 8u * (uint32_t)s; };
   auto BAR_EMPTY = [&](int s) { return ctl0 + 8u * (uint32_t)(MX_MAX_STAGES + s); };
@@ -411,8 +419,9 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
   const int KT = q.KT, NB = q.NB, NG = q.n_groups;
   int64_t useful_m = q.grid_m;
   if (p.slice_sizes) useful_m = (int64_t)p.block_offs[p.E];
-  const int acc_stride = MB * q.n_mma;              // accumulator columns of one buffer
-  MxSched sched(useful_m, NB, NG, MB);
+  const int acc_stride = NACC * q.n_mma;            // accumulator columns of one buffer
+  MxSched sched(useful_m, NB, NG, NACC);
+  const int KS = KM ? (KT + 2) / 3 : KT;            // stages of a tile
   int64_t pid_m;
   int nb0, mb_live;
 
@@ -426,16 +435,27 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
         mx_map_block(p, q.tb, pid_m, e, row0, rows);
         const uint8_t* xsrc = q.xq + pid_m * KT * q.chunk_bytes;
         const CUtensorMap* w_map = &w_maps.m[mb_live - 1];
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        for (int kt = 0; kt < KS; ++kt, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(BAR_EMPTY(s), ((it / STAGES) & 1u) ^ 1u, ctl, 601);
           if (!ok) break;
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
-          const int64_t tile = ((int64_t)e * KT + kt) * NB + nb0;
-          mbar_expect_tx(BAR_FULL(s), (uint32_t)(mb_live * (MX_W_TILE_TX + MX_WS_TILE)) + (uint32_t)q.chunk_bytes);
-          tma_tile_3d(st, w_map, 0, 0, (int)tile, BAR_FULL(s));
-          bulk_g2s(st + OFF_WS, p.w_scale + tile * MX_WS_TILE, (uint32_t)(mb_live * MX_WS_TILE), BAR_FULL(s));
-          bulk_g2s(st + OFF_X, xsrc + (int64_t)kt * q.chunk_bytes, (uint32_t)q.chunk_bytes, BAR_FULL(s));
+          if constexpr (KM) {
+            const int k_live = min(3, KT - 3 * kt);
+            mbar_expect_tx(BAR_FULL(s), (uint32_t)k_live * ((uint32_t)(MX_W_TILE_TX + MX_WS_TILE) + (uint32_t)q.chunk_bytes));
+            for (int i = 0; i < k_live; ++i) {
+              const int64_t tile = ((int64_t)e * KT + 3 * kt + i) * NB + nb0;
+              tma_tile_3d(st + (uint32_t)i * W_TILE, &w_maps.m[0], 0, 0, (int)tile, BAR_FULL(s));
+              bulk_g2s(st + OFF_WS + (uint32_t)i * MX_WS_TILE, p.w_scale + tile * MX_WS_TILE, (uint32_t)MX_WS_TILE, BAR_FULL(s));
+            }
+            bulk_g2s(st + OFF_X, xsrc + (int64_t)(3 * kt) * q.chunk_bytes, (uint32_t)k_live * (uint32_t)q.chunk_bytes, BAR_FULL(s));
+          } else {
+            const int64_t tile = ((int64_t)e * KT + kt) * NB + nb0;
+            mbar_expect_tx(BAR_FULL(s), (uint32_t)(mb_live * (MX_W_TILE_TX + MX_WS_TILE)) + (uint32_t)q.chunk_bytes);
+            tma_tile_3d(st, w_map, 0, 0, (int)tile, BAR_FULL(s));
+            bulk_g2s(st + OFF_WS, p.w_scale + tile * MX_WS_TILE, (uint32_t)(mb_live * MX_WS_TILE), BAR_FULL(s));
+            bulk_g2s(st + OFF_X, xsrc + (int64_t)kt * q.chunk_bytes, (uint32_t)q.chunk_bytes, BAR_FULL(s));
+          }
         }
       }
       if (!ok) {
@@ -457,16 +477,29 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * (uint32_t)acc_stride;
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        for (int kt = 0; kt < KS; ++kt, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(BAR_FULL(s), (it / STAGES) & 1u, ctl, 602);
           ok = ok && mbar_wait(BAR_SF(s), (it / STAGES) & 1u, ctl, 606);
           if (!ok) break;
           tc_fence_after();
           const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
-          const uint32_t sf = tmem_base + (uint32_t)(MX_SF_BASE + s * MX_SF_COLS);
+          const uint32_t sf = tmem_base + SF_BASE + (uint32_t)(s * SF_COLS);
           // k group outermost: consecutive MMAs go to different accumulators
-          if constexpr (F4) {
+          if constexpr (KM) {
+            const int k_live = min(3, KT - 3 * kt);
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+              if (i < k_live) {
+                const uint64_t adesc = make_desc_sw64(st + (uint32_t)i * W_TILE);
+                const uint64_t bdesc = make_desc_sw64(st + OFF_X + (uint32_t)i * (uint32_t)q.chunk_bytes);
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk)
+                  mma_mxf4(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), mx4_idesc(q.n_mma, (uint32_t)(kk * 2)),
+                           sf + 4u * (uint32_t)i, sf + 12u + 4u * (uint32_t)i, (kt | i | kk) ? 1u : 0u);
+              }
+            }
+          } else if constexpr (F4) {
             const uint64_t bdesc = make_desc_sw64(st + OFF_X);
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
@@ -510,12 +543,36 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
     uint32_t it = 0;
     bool ok = true;
     while (ok && sched.next(pid_m, nb0, mb_live)) {
-      for (int kt = 0; kt < KT; ++kt, ++it) {
+      for (int kt = 0; kt < KS; ++kt, ++it) {
         const int s = it % STAGES;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(BAR_FULL(s), (it / STAGES) & 1u, ctl, 607));
         if (!ok) break;
         const uint32_t st = sbase + (uint32_t)s * (uint32_t)q.stage_bytes;
-        const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(MX_SF_BASE + s * MX_SF_COLS);
+        const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + SF_BASE + (uint32_t)(s * SF_COLS);
+        if constexpr (KM) {
+          // columns 0..11: the weight scales of the three k steps, 12..23: the token scales of the three chunks
+          const int k_live = min(3, KT - 3 * kt);
+          uint4 w[3], x[3];
+#pragma unroll
+          for (int i = 0; i < 3; ++i) {
+            w[i] = i < k_live ? lds128(st + OFF_WS + (uint32_t)i * MX_WS_TILE + (uint32_t)lane * 16u) : make_uint4(0, 0, 0, 0);
+            x[i] = i < k_live ? lds128(st + OFF_X + (uint32_t)i * (uint32_t)q.chunk_bytes + (uint32_t)q.n_mma * X_ROW + (uint32_t)lane * 16u)
+                              : make_uint4(0, 0, 0, 0);
+          }
+          asm volatile(
+              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+              "r"(w[0].x), "r"(w[0].y), "r"(w[0].z), "r"(w[0].w), "r"(w[1].x), "r"(w[1].y), "r"(w[1].z), "r"(w[1].w),
+              "r"(w[2].x), "r"(w[2].y), "r"(w[2].z), "r"(w[2].w), "r"(x[0].x), "r"(x[0].y), "r"(x[0].z), "r"(x[0].w)
+              : "memory");
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr + 16u), "r"(x[1].x),
+                       "r"(x[1].y), "r"(x[1].z), "r"(x[1].w), "r"(x[2].x), "r"(x[2].y), "r"(x[2].z), "r"(x[2].w)
+                       : "memory");
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_SF(s));
+          continue;
+        }
         uint4 v[MB + 1];
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
@@ -551,9 +608,9 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
       int e; int64_t row0; int rows;
       mx_map_block(p, q.tb, pid_m, e, row0, rows);
       const uint32_t ab = tc % (uint32_t)q.acc_bufs;
-      float bias_n[MB];
+      float bias_n[NACC];
 #pragma unroll
-      for (int mb = 0; mb < MB; ++mb) {
+      for (int mb = 0; mb < NACC; ++mb) {
         const int n = (nb0 + mb) * 128 + qd * 32 + lane;
         bias_n[mb] = (p.bias && n < p.N) ? load_bias(p.bias, p.bias_dtype, (int64_t)e * p.ld_bias + n) : 0.0f;
       }
@@ -574,7 +631,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
         }
         const int jmax = min(16, rows - c0);
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
+        for (int mb = 0; mb < NACC; ++mb) {
           if (mb < mb_live) {
             const int n = (nb0 + mb) * 128 + qd * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(qd * 32) << 16) + ab * (uint32_t)acc_stride +
@@ -634,7 +691,7 @@ gemm_mx_kernel(const GemmParams p, const MxParams q, const __grid_constant__ MxM
 
 // ---- host side -----------------------------------------------------------------------------------------------
 struct MxPlan {
-  int tb, n_mma, split, f4, mb, KT, NB, n_groups, stages, stage_bytes, acc_bufs;
+  int tb, n_mma, split, f4, km, mb, KT, NB, n_groups, stages, stage_bytes, acc_bufs;
   int64_t grid_m, chunk_bytes, ws_bytes;
 };
 
@@ -669,13 +726,24 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   // would be too few tiles to fill the SMs
   const int64_t items3 = pl.grid_m * cdiv64(pl.NB, 3);
   pl.mb = (a.tile_n == 128) ? 1 : ((a.tile_n == 384 || items3 >= (int64_t)moe_sm_count()) ? 3 : 1);
+  // too few tiles for three blocks each, four-term form: single weight blocks, three k steps of one block per stage
+  // (a stage of one 8 KB tile does not keep a copy pipeline busy)
+  pl.km = (pl.f4 && tb == 16 && pl.mb == 1 && a.tile_n == 0 && pl.KT >= 3) ? 1 : 0;
   pl.n_groups = (int)cdiv64(pl.NB, pl.mb);
   pl.chunk_bytes = (int64_t)pl.n_mma * (pl.f4 ? 64 : 128) + 1024;
-  pl.stage_bytes = pl.mb * (pl.f4 ? MX_W_TILE_TX : MX_W_TILE) + (int)pl.chunk_bytes + 2048;
   const int ctl_bytes = MX_CTL_BYTES;
-  int st = (MX_SMEM_LIMIT - 1024 - ctl_bytes) / pl.stage_bytes;
-  pl.stages = st > MX_MAX_STAGES ? MX_MAX_STAGES : st;
-  pl.acc_bufs = (2 * pl.mb * pl.n_mma <= MX_SF_BASE) ? 2 : 1;
+  if (pl.km) {
+    pl.mb = 3;                                       // tiles of a stage; n_groups stays the number of weight blocks
+    pl.stage_bytes = 3 * MX_W_TILE_TX + 3 * (int)pl.chunk_bytes + 2048;
+    int st = (MX_SMEM_LIMIT - 1024 - ctl_bytes) / pl.stage_bytes;
+    pl.stages = st > 5 ? 5 : st;
+    pl.acc_bufs = 2;
+  } else {
+    pl.stage_bytes = pl.mb * (pl.f4 ? MX_W_TILE_TX : MX_W_TILE) + (int)pl.chunk_bytes + 2048;
+    int st = (MX_SMEM_LIMIT - 1024 - ctl_bytes) / pl.stage_bytes;
+    pl.stages = st > MX_MAX_STAGES ? MX_MAX_STAGES : st;
+    pl.acc_bufs = (2 * pl.mb * pl.n_mma <= MX_SF_BASE) ? 2 : 1;
+  }
   pl.ws_bytes = pl.grid_m * pl.KT * pl.chunk_bytes;
   return pl;
 }
@@ -732,21 +800,22 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-template <typename TY, int MB, bool F4>
+template <typename TY, int MB, bool F4, bool KM = false>
 int launch_mx(const GemmParams& p, const MxParams& q, const MxPlan& pl, const MxMaps& w_map, int idle_sms, cudaStream_t st) {
   const int smem = pl.stages * pl.stage_bytes + MX_CTL_BYTES + 1024;
   const int64_t items = pl.grid_m * pl.n_groups;
   int sms = moe_sm_count() - idle_sms;
   if (sms < 1) sms = 1;
   const int grid = (int)(items < sms ? items : sms);
-  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_mx_kernel<TY, MB, F4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  MOE_CHECK_CUDA(launch_pdl(gemm_mx_kernel<TY, MB, F4>, dim3(grid), dim3(MX_THREADS), (size_t)smem, st, p, q, w_map));
+  MOE_CHECK_CUDA(cudaFuncSetAttribute(gemm_mx_kernel<TY, MB, F4, KM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  MOE_CHECK_CUDA(launch_pdl(gemm_mx_kernel<TY, MB, F4, KM>, dim3(grid), dim3(MX_THREADS), (size_t)smem, st, p, q, w_map));
   MOE_CHECK_LAUNCH();
   return MOE_OK;
 }
 
 template <typename TY>
 int launch_mx_ty(const GemmParams& p, const MxParams& q, const MxPlan& pl, const MxMaps& w_map, int idle_sms, cudaStream_t st) {
+  if (pl.km) return launch_mx<TY, 3, true, true>(p, q, pl, w_map, idle_sms, st);
   if (pl.f4) return pl.mb == 3 ? launch_mx<TY, 3, true>(p, q, pl, w_map, idle_sms, st) : launch_mx<TY, 1, true>(p, q, pl, w_map, idle_sms, st);
   return pl.mb == 3 ? launch_mx<TY, 3, false>(p, q, pl, w_map, idle_sms, st) : launch_mx<TY, 1, false>(p, q, pl, w_map, idle_sms, st);
 }
