@@ -334,10 +334,11 @@ def test_gpt_oss_120b_layer_benchmark_configuration_against_oracle(device):
     _sampled_layer_check(lw, 128, 16384, device, seed=0, skew=True)
 
 
-@pytest.mark.parametrize("tokens", [1, 16, 64, 300])
+@pytest.mark.parametrize("tokens", [1, 16, 64, 300, 1200])
 def test_gpt_oss_120b_layer_decode_path_against_oracle(tokens, device):
-    """Decode-sized steps of the 128-expert layer take the block-scaled kernel (its own copy of the weights); 300 tokens
-    (more than 24 rows per expert on average would switch kernels, 9 do not) still do."""
+    """Steps of the 128-expert layer with up to 48 rows per expert on average take the block-scaled kernel (its own copy of
+    the weights): 1 to 64 tokens in 16-row token blocks (four e2m1 terms), 300 and 1200 tokens (9 and 38 rows per expert) in
+    32-row blocks (two e4m3 terms)."""
     from triton_b200.testing import make_synthetic_layer
     lw = make_synthetic_layer(128, 2880, 2880, device, seed=1000, keep_canonical=True, block_scaled=True)
     assert lw.use_block_scaled(tokens * 4)

@@ -710,8 +710,12 @@ MxPlan mx_plan(const MoeGemmArgs& a) {
   if (a.tile_m == 16 || a.tile_m == 32 || a.tile_m == 64 || a.tile_m == 128) {
     tb = a.tile_m;
   } else {
+    // bf16 tokens: 16 rows up to 8 rows per expert on average, 32 beyond (64-row blocks were slower than two 32-row
+    // blocks at every size measured: 32 rows per expert 294 against 226 us on a 32-expert layer, 911 against 698 us on
+    // a 128-expert one); fp8 tokens grow to 128
     const int64_t per = a.slice_sizes ? (a.M + a.E - 1) / a.E : a.M;      // mean rows per expert
-    while (tb < tb_max && tb < 2 * per) tb *= 2;
+    const int tb_auto = bf16 ? (tb_max < 32 ? tb_max : 32) : tb_max;
+    while (tb < tb_auto && tb < 2 * per) tb *= 2;
   }
   if (tb > tb_max) tb = tb_max;
   pl.tb = tb;
