@@ -50,22 +50,24 @@ def test_reduce(shape, dim, mask_mode, device):
     torch.testing.assert_close(y.cpu().float(), ref.float(), atol=1e-2, rtol=1e-2)
 
 
-def test_gather_rows_over_peer_buffers(device):
+@pytest.mark.parametrize("n_out, d", [(500, 96), (5000, 2880), (40000, 64), (700001, 32)])
+def test_gather_rows_over_peer_buffers(n_out, d, device):
     """moe_gather_rows_peers with three buffers on one device standing in for three ranks: -1 writes zeros, -2 leaves
-    the row untouched."""
+    the row untouched.  The sizes walk the kernel's rows-per-warp batches from 1 (few rows) to 32 (many)."""
     import ctypes
     from triton_b200 import _lib
     torch.manual_seed(0)
-    rows_per_peer, d = 37, 96
+    rows_per_peer = 37
     bufs = [torch.randn(rows_per_peer, d, device=device).bfloat16() for _ in range(3)]
     allrows = torch.cat(bufs)
-    idx = torch.randint(0, 3 * rows_per_peer, (500,), device=device, dtype=torch.int32)
+    idx = torch.randint(0, 3 * rows_per_peer, (n_out,), device=device, dtype=torch.int32)
     idx[::7] = -1
     idx[3::11] = -2
-    out = torch.full((500, d), 7.0, device=device).bfloat16()
+    idx[torch.rand(n_out, device=device) < 0.6] = -2          # most rows belong to other ranks
+    out = torch.full((n_out, d), 7.0, device=device).bfloat16()
     lib = _lib.load()
     ptrs = (ctypes.c_void_p * 3)(*[b.data_ptr() for b in bufs])
-    _lib.check(lib.moe_gather_rows_peers(ptrs, 3, rows_per_peer, d * 2, _lib.ptr(idx), 500, d * 2, _lib.ptr(out), d * 2,
+    _lib.check(lib.moe_gather_rows_peers(ptrs, 3, rows_per_peer, d * 2, _lib.ptr(idx), n_out, d * 2, _lib.ptr(out), d * 2,
                                          _lib.stream()), "moe_gather_rows_peers")
     want = allrows[idx.long().clamp_min(0)]
     want[idx == -1] = 0
