@@ -184,6 +184,7 @@ class SymmetricMemoryPool:
         included) is complete before any rank's later work starts."""
         if self.mesh.world_size <= 1:
             return
+        self.n_barriers = getattr(self, "n_barriers", 0) + 1       # lets a caller see that a barrier followed its writes
         if self.peer_ok:
             from .matmul import _status_word
             lib = _lib.load()

@@ -226,13 +226,14 @@ class HostStreamingLayer:
         torch.cuda.current_stream(self.dev).wait_stream(self.s_in)
 
 
-def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer, mark=None):
+def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer, mark=None, tokens_published=False):
     """Expert-parallel layer over peer-mapped buffers: the dispatch is one gather kernel that pulls every routed token
     row from its home rank's buffer into expert-sorted order (the layout fc1's TMA loads want); fc2 writes its rows
     into this rank's symmetric output buffer, and the combine is one kernel in which every token reads its k rows from
     the owners' buffers and sums them.  Both transfers are row-wise (512-byte warp accesses over NVLink; stores of
-    16 bytes from the GEMM epilogue into peer memory ran at a seventh of that) and two stream-ordered barriers
-    replace the two all-to-alls."""
+    16 bytes from the GEMM epilogue into peer memory ran at a seventh of that) and stream-ordered barriers replace the
+    two all-to-alls: one before the dispatch (shared with the all-gather of the routing outputs when the caller put the
+    tokens into the pool's buffer ahead of it: `tokens_published`) and one before the combine."""
     from . import _lib
     lib = _lib.load()
     mesh = pool.mesh
@@ -276,9 +277,10 @@ def _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_t
                                              _lib.ptr(table), n, k, _lib.ptr(rows_c), _lib.ptr(gammas), _lib.stream()),
                        "moe_ep_pull_index")
             plan.append((rows_c, remap_ragged_tensor_metadata(meta_global, table), lo_e, hi_e))
-    if x_local.data_ptr() != pool.xbuf.data_ptr():                     # a caller may keep its tokens in the pool's buffer
-        pool.xbuf.copy_(x_local)
-    pool.barrier()                                                     # every rank's tokens are in its buffer
+    if not tokens_published:                                           # (the caller did both ahead of the routing barrier)
+        if x_local.data_ptr() != pool.xbuf.data_ptr():                 # a caller may keep its tokens in the pool's buffer
+            pool.xbuf.copy_(x_local)
+        pool.barrier()                                                 # every rank's tokens are in its buffer
     mark("pull index + token barrier")
     x_sorted = torch.empty((n, d), dtype=x_local.dtype, device=dev)
     ptrs = (ctypes.c_void_p * W)(*pool.x_ptrs)
@@ -382,18 +384,28 @@ def moe_layer_forward_ep(x_local, logits_local, lw_local: MoeLayerWeights, k: in
                               make_exchange_plan_cuda)
     rank = pool.mesh.local_rank
     T_local = x_local.shape[0]
+    peer_fit = pool.peer_ok and pool.peer_shape == (T_local, x_local.shape[1], lw_local.w2.shape[-1], k, x_local.dtype)
+    if exchange == "peer" and not peer_fit:
+        raise RuntimeError(f"peer exchange is not available: {pool.peer_error}")
+    tokens_at = None
+    if exchange in ("auto", "peer") and peer_fit:
+        # this rank's tokens go into its peer-mapped buffer BEFORE the routing outputs are published: the barrier of that
+        # all-gather then also tells every rank that the tokens are in place, and the dispatch needs no barrier of its own.
+        # (Overwriting the buffer here is safe: every peer finished pulling the previous step's tokens before it arrived
+        # at that step's last barrier.)
+        if x_local.data_ptr() != pool.xbuf.data_ptr():
+            pool.xbuf.copy_(x_local)
+        tokens_at = getattr(pool, "n_barriers", 0)
     keep_bm, pool.gather_bitmatrix = pool.gather_bitmatrix, False     # the layer never reads the mask bits themselves
     try:
         sparse = topk(logits_local, k, apply_softmax=True, all_gather=True, symm_mem_pool=pool)
     finally:
         pool.gather_bitmatrix = keep_bm
-    peer_fit = pool.peer_ok and pool.peer_shape == (T_local, x_local.shape[1], lw_local.w2.shape[-1], k, x_local.dtype)
-    if exchange == "peer" and not peer_fit:
-        raise RuntimeError(f"peer exchange is not available: {pool.peer_error}")
     if mark is not None:
         mark("routing + all-gather + expert sort")
     if exchange in ("auto", "peer") and peer_fit:
-        return _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer, mark)
+        published = tokens_at is not None and getattr(pool, "n_barriers", 0) > tokens_at
+        return _forward_ep_peer(x_local, sparse, lw_local, k, expt_assignment, pool, gemm_timer, mark, tokens_published=published)
     md = sparse.mask_metadata
     n_entries = md.row_sorted_indx.shape[0]
     meta_global = make_ragged_tensor_metadata(md.col_sum, n_entries)
