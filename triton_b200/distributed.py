@@ -200,8 +200,9 @@ class SymmetricMemoryPool:
                           n_expts_tot=n_expts_tot, dtype=dtype, device=device)
         self._is_initialized = True
 
-    def all_gather_routing(self, y_vals, y_indx, bm_store, T_local, rank):
-        """In-place all-gather of the routing outputs: rank r's rows are [r * T_local, (r+1) * T_local)."""
+    def all_gather_routing(self, y_vals, y_indx, bm_store, T_local, rank, published=False):
+        """In-place all-gather of the routing outputs: rank r's rows are [r * T_local, (r+1) * T_local).  `published`:
+        this rank's rows are already in the pool's peer-mapped routing buffers (the top-k kernel wrote them there)."""
         g = self.mesh.process_group
         W = self.mesh.world_size
         k = y_vals.shape[1]
@@ -210,8 +211,9 @@ class SymmetricMemoryPool:
                 and y_vals.is_contiguous() and y_indx.is_contiguous()):
             # no collective: publish this rank's rows in its symmetric buffers, barrier, read every rank's rows
             lib = _lib.load()
-            self.route_vals.copy_(y_vals[rank * T_local:(rank + 1) * T_local])
-            self.route_indx.copy_(y_indx[rank * T_local:(rank + 1) * T_local])
+            if not published:
+                self.route_vals.copy_(y_vals[rank * T_local:(rank + 1) * T_local])
+                self.route_indx.copy_(y_indx[rank * T_local:(rank + 1) * T_local])
             self.barrier()
             pv = (ctypes.c_void_p * W)(*self.rv_ptrs)
             pi = (ctypes.c_void_p * W)(*self.ri_ptrs)
@@ -220,6 +222,9 @@ class SymmetricMemoryPool:
             peer_done = True
         else:
             peer_done = False
+            if published:                      # the rows sit in the routing buffers only: bring them home first
+                y_vals[rank * T_local:(rank + 1) * T_local].copy_(self.route_vals)
+                y_indx[rank * T_local:(rank + 1) * T_local].copy_(self.route_indx)
 
         def gather_rows(buf):
             # byte views: NCCL has no 16-bit integer type

@@ -49,12 +49,19 @@ def topk_forward(x, k, apply_softmax=True, dim=1, y_indx=None, n_rows=None, all_
             n_rows_dev = torch.tensor([int(n_rows)], dtype=torch.int32, device=dev)
     r0 = rank * T
     vals_loc, indx_loc, bm_loc = y_vals[r0:r0 + T], y_indx_full[r0:r0 + T], bm[r0:r0 + T]
+    # with peer-mapped routing buffers the kernel writes this rank's rows straight into them: the all-gather then reads
+    # every rank's rows (this one's included) from there and no copy runs in between
+    direct = (all_gather and world > 1 and not use_provided and getattr(symm_mem_pool, "peer_ok", False)
+              and x.dtype == torch.float32 and symm_mem_pool.peer_shape[0] == T and symm_mem_pool.peer_shape[3] == k
+              and not symm_mem_pool.gather_bitmatrix)
+    if direct:
+        vals_loc, indx_loc = symm_mem_pool.route_vals, symm_mem_pool.route_indx
     _lib.check(lib.moe_topk_fwd(_lib.ptr(x), _lib.dtype_code(x.dtype), T, E, k, int(bool(apply_softmax)), x.stride(0),
-                                _lib.ptr(vals_loc), y_vals.stride(0), _lib.ptr(indx_loc), y_indx_full.stride(0),
+                                _lib.ptr(vals_loc), vals_loc.stride(0), _lib.ptr(indx_loc), indx_loc.stride(0),
                                 _lib.ptr(bm_loc), bm.stride(0), bm.stride(1), _lib.ptr(n_rows_dev), int(use_provided),
                                 _lib.stream()), "moe_topk_fwd")
     if all_gather and world > 1:
-        symm_mem_pool.all_gather_routing(y_vals, None if use_provided else y_indx_full, bm_store, T, rank)
+        symm_mem_pool.all_gather_routing(y_vals, None if use_provided else y_indx_full, bm_store, T, rank, published=direct)
     shape0 = (n_rows if n_rows is not None else T)
     if all_gather and world > 1:
         shape0 = T_out
